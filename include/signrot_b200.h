@@ -1,0 +1,212 @@
+/* signrot_b200 -- C ABI of the B200 (sm_100a) implementation of SignRot's online
+ * quantized-linear path.
+ *
+ * One shared library, libsignrot_b200.so, exports the functions below.  They are what
+ * a binding for this path has to call: each comment names the reference interface
+ * (file:line inside HYU-ARK-Lab/SignRot) that the entry point replaces.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer into memory owned by the caller; inputs are
+ *    borrowed, outputs are written in place; tensors are dense and row-major;
+ *  - nothing is allocated, nothing is synchronised and no device memory is read on
+ *    the host, so every call may be captured in a CUDA graph;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *  - activations are IEEE fp16 unless a dtype tag says otherwise; 4-bit codes are
+ *    packed two per byte, element 2j in the low nibble of byte j
+ *    (signrot/functional/quantization.py:45-53, signrot/kernels/include/int4.h:79-99);
+ *  - the return value is SR_OK or an SR_ERR_* code; sr_last_error() then returns a
+ *    message for the calling thread.  Argument errors are detected on the host
+ *    before anything is launched.
+ */
+#ifndef SIGNROT_B200_H_
+#define SIGNROT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SR_VERSION 100
+
+#define SR_OK 0
+#define SR_ERR_INVALID 1      /* bad argument (the reference raises RuntimeError via TORCH_CHECK) */
+#define SR_ERR_CUDA 2         /* the CUDA runtime or driver reported an error */
+#define SR_ERR_UNSUPPORTED 3  /* valid request that this build has no kernel for */
+
+/* dtype tags */
+#define SR_F16 0
+#define SR_BF16 1
+#define SR_F32 2
+
+const char *sr_last_error(void);
+int sr_version(void);
+
+/* Device-side status word: 0, or the code of the first bounded wait that expired
+ * inside a kernel (such a kernel stops early, its output is undefined).  This call
+ * synchronises with the device; it is meant for tests and health checks. */
+int sr_device_status(int *status, int clear);
+
+/* ------------------------------------------------------------------ int4 GEMM */
+
+/* C[M,N] int32 = A[M,K] * B[N,K]^T, A packed s4 (a_unsigned = 0) or u4 (1), B packed s4.
+ * K % 32 == 0.  Replaces signrot._CUDA.matmul / matmul_ui4_si4
+ * (signrot/kernels/bindings.cpp:13-47, gemm.cu:7-85; Python: functional/kernel.py:67-81). */
+int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned, void *C,
+                 void *stream);
+
+/* out[M,N] fp16 = dequant(A * W^T): the whole of Linear4bit.forward for a packed input
+ * (signrot/nn/linear.py:36-50): GEMM, optional asymmetric correction
+ * acc -= a_zero[m] * w_sum[n] (a_zero int8 [M], w_sum int32 [N]; both NULL for symmetric
+ * activations, in which case A holds signed codes, otherwise unsigned codes), dequant
+ * rn_h((float(acc) * a_scale[m]) * w_scale[n]) (signrot/kernels/quant.cu:84-87) and optional
+ * fp16 bias add.  The int32 matrix never reaches memory. */
+int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                   const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream);
+
+/* P problems C_p = A_p * B_p^T in one launch.  problem_sizes int32 [P,3] rows (m, n, k);
+ * ptr_* int64 [P] device addresses; ld* int64 [P] leading dimensions in elements.  All of
+ * these arrays live in device memory and are never read on the host.  max_k > 0 promises
+ * k_p <= max_k for every problem (lets more CTAs share an SM); 0 = unknown.  A problem with
+ * k % 32 != 0 or k beyond the promise is skipped and recorded in the device status word.
+ * Replaces signrot._CUDA.matmul_grouped (bindings.cpp:49-91, gemm_grouped.cu:19-120). */
+int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const void *ptr_a, const void *ptr_b,
+                      const void *ptr_c, const void *lda, const void *ldb, const void *ldc, int signed_a,
+                      int64_t max_k, void *stream);
+
+/* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
+ * 2 = tcgen05 kernel.  For tests and tuning; no counterpart in the reference. */
+int sr_set_gemm_kernel(int which);
+
+/* ------------------------------------------------------------------ quantizers */
+
+/* Per-row amax -> scale = rn_h(amax/7) (* clip) -> codes clamp(rint(x/scale), -8, 7).
+ * q: uint8 [rows, ceil(cols/2)], scale: fp16 [rows].
+ * Replaces _CUDA.sym_quant_dynamic (bindings.cpp:316-335, fused.cu:68-138). */
+int sr_sym_quant_dynamic(const void *x, int64_t rows, int64_t cols, float clip_ratio, void *q, void *scale,
+                         void *stream);
+
+/* Per-row min/max -> scale, zero (fp16 [rows] each) -> unsigned codes 0..15.
+ * Replaces _CUDA.asym_quant_dynamic (bindings.cpp:337-360, fused.cu:143-208). */
+int sr_asym_quant_dynamic(const void *x, int64_t rows, int64_t cols, float clip_ratio, void *q, void *scale,
+                          void *zero, void *stream);
+
+/* The two quantizers above with row r first multiplied by sign[expert_ids[r]] (sign: int8
+ * [E, cols] of +-1 or NULL; expert_ids: int32 [rows]).
+ * Replaces _CUDA.sym/asym_quant_dynamic_moe (bindings.cpp:111-168, moe.cu:60-199). */
+int sr_sym_quant_dynamic_moe(const void *x, const void *sign, const void *expert_ids, int64_t rows, int64_t cols,
+                             float clip_ratio, void *q, void *scale, void *stream);
+int sr_asym_quant_dynamic_moe(const void *x, const void *sign, const void *expert_ids, int64_t rows, int64_t cols,
+                              float clip_ratio, void *q, void *scale, void *zero, void *stream);
+
+/* Quantize with given per-row scale (and zero).  Replaces _CUDA.sym_quant,
+ * asym_quant_f16_si4, asym_quant_f16_ui4 (bindings.cpp:215-314, quant.cu:13-231). */
+int sr_sym_quant(const void *x, const void *scale, int64_t rows, int64_t cols, void *q, void *stream);
+int sr_asym_quant_f16_si4(const void *x, const void *scale, const void *zero, int64_t rows, int64_t cols, void *q,
+                          void *stream);
+int sr_asym_quant_f16_ui4(const void *x, const void *scale, const void *zero, int64_t rows, int64_t cols, void *q,
+                          void *stream);
+
+/* out fp16 [rows, cols] = rn_h((float(q) * scale_row[r]) * scale_col[c]), q int32.
+ * Replaces _CUDA.sym_dequant (bindings.cpp:233-276, quant.cu:66-131). */
+int sr_sym_dequant(const void *q, const void *scale_row, const void *scale_col, int64_t rows, int64_t cols,
+                   void *out, void *stream);
+
+/* Expert-indexed dequant with the asymmetric correction fused in; w_scales fp16 [E, cols],
+ * w_sum int32 [E, cols], zero_row int8 [rows] (zero_row and w_sum both NULL or both set).
+ * Replaces _CUDA.sym_dequant_moe (bindings.cpp:170-213, moe.cu:202-238). */
+int sr_sym_dequant_moe(const void *q, const void *scale_row, const void *w_scales, const void *expert_ids,
+                       const void *zero_row, const void *w_sum, int64_t rows, int64_t cols, void *out,
+                       void *stream);
+
+/* out int32 [rows] = sum of the 2*packed_cols 4-bit values of each row.
+ * Replaces _CUDA.sum_i4 (bindings.cpp:436-449, quant.cu:233-350). */
+int sr_sum_i4(const void *x, int64_t rows, int64_t packed_cols, int is_signed, void *out, void *stream);
+
+/* out int32 [rows, cols] = a_col[r] (int8) * b_row[c] (int32).
+ * Replaces _CUDA.matmul_colrow_i8_i32 (bindings.cpp:451-476, quant.cu:352-383). */
+int sr_matmul_colrow_i8_i32(const void *a_col, const void *b_row, int64_t rows, int64_t cols, void *out,
+                            void *stream);
+
+/* ------------------------------------------------------------------ online rotation */
+
+/* y = ((hadK (x) H_{n/K}) x) * scale over the last dimension, Sylvester order, flat index
+ * k*(n/K)+j; then y *= sign (int8 [n] or NULL).  dtype/out_dtype are SR_F16, SR_BF16 or
+ * SR_F32.  The Walsh-Hadamard sums are fp32 and rounded to `dtype`, the had-K stage (hadk:
+ * K x K matrix in fp16, or fp32 when fp32_mode) rounds again, unless fp32_mode is set (then
+ * only the final cast rounds).  Replaces fast_hadamard_transform.hadamard_transform + the
+ * had-K matmul + the sign multiply: signrot/functional/hadamard.py:78-87,
+ * signrot/nn/hadamard.py:26-42, signrot/transformers/kv_cache.py:70-73. */
+int sr_hadamard(const void *x, int dtype, int64_t rows, int64_t n, const void *hadk, int64_t K, float scale,
+                const void *sign, int fp32_mode, void *out, int out_dtype, void *stream);
+
+/* Head-wise Hadamard (H_heads (x) I_head_dim) on rows of heads*head_dim values: the o_proj
+ * input rotation, fake_quant/quant_utils.py:287-291 without the two transposes. */
+int sr_hadamard_heads(const void *x, int dtype, int64_t rows, int64_t heads, int64_t head_dim, float scale,
+                      int fp32_mode, void *out, int out_dtype, void *stream);
+
+/* Rotation fused with the per-token quantizer: everything ActQuantWrapper.kernel_quantize
+ * does (fake_quant/quant_utils.py:278-292) in one pass over the row.  x is fp16 or bf16
+ * (bf16 is first rounded to fp16, quant_utils.py:284).  heads > 0 selects the head-wise
+ * transform (then K must be 1); expert_ids (int32 [rows]) selects a row of sign [E, n].
+ * asym = 0: signed codes + q_scale; asym = 1: unsigned codes + q_scale + q_zero (fp16).
+ * `rotated` (fp16 [rows, n]) optionally receives the rotated row. */
+int sr_rotate_quant(const void *x, int dtype, int64_t rows, int64_t n, const void *hadk, int64_t K, float scale,
+                    const void *sign, const void *expert_ids, int64_t heads, float clip_ratio, int asym, void *q,
+                    void *q_scale, void *q_zero, void *rotated, void *stream);
+
+/* ------------------------------------------------------------------ adjacent fused ops */
+
+/* Replaces _CUDA.rmsnorm (bindings.cpp:420-434, fused.cu:278-309). */
+int sr_rmsnorm(const void *x, int64_t rows, int64_t cols, float eps, int64_t mean_dim, void *out, void *stream);
+/* In-place rotary embedding on q [B,T,Hq,D], k [B,T,Hk,D]; cos/sin [cos_seqs,T,D].
+ * Replaces _CUDA.rope_qk (bindings.cpp:383-409, fused.cu:316-362). */
+int sr_rope_qk(void *q, void *k, const void *cosv, const void *sinv, int64_t n_seqs, int64_t seq_len,
+               int64_t cos_seqs, int64_t n_q_heads, int64_t n_k_heads, int64_t head_dim, void *stream);
+/* Replaces _CUDA.swiglu (bindings.cpp:411-418, fused.cu:367-390). */
+int sr_swiglu(const void *gate, const void *up, int64_t numel, void *out, void *stream);
+/* q uint8 [rows, cols/2], param fp16 [rows, 2] = (scale, zero).
+ * Replaces _CUDA.kv_quant_pack (bindings.cpp:362-381, fused.cu:214-273). */
+int sr_kv_quant_pack(const void *x, int64_t rows, int64_t cols, void *q, void *param, void *stream);
+
+/* ------------------------------------------------------------------ int4 paged KV cache
+ * kv_data uint8 [pages, layers, 2, heads, page_size, 64], kv_param fp16 [.., page_size, 2],
+ * kv_indptr int32 [batch+1], kv_indices int32 [*], last_page_offset int32 [batch]
+ * (signrot/transformers/kv_cache.py:185-196, 417-433).  head_dim must be 128. */
+
+/* One already-quantized token per request into its slot.  Replaces _CUDA.append_kv_i4
+ * (bindings.cpp:604-644, include/flashinfer/page.cuh:119-164). */
+int sr_append_kv_i4(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                    const void *last_page_offset, const void *k, const void *v, const void *k_param,
+                    const void *v_param, int64_t num_layers, int64_t layer_idx, int64_t num_heads, int64_t page_size,
+                    int64_t head_dim, int64_t batch_size, void *stream);
+/* A whole prompt per request; seqlen_indptr int32 [batch+1].  Replaces _CUDA.init_kv_i4
+ * (bindings.cpp:561-602, page.cuh:166-219). */
+int sr_init_kv_i4(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                  const void *last_page_offset, const void *k, const void *v, const void *k_param,
+                  const void *v_param, const void *seqlen_indptr, int64_t total_tokens, int64_t num_layers,
+                  int64_t layer_idx, int64_t num_heads, int64_t page_size, int64_t head_dim, int64_t batch_size,
+                  void *stream);
+/* k, v fp16 [batch, new_tokens, heads, 128]: Hadamard on K (hadamard_k), quantize both and
+ * write the slots of the last new_tokens positions of every request, in one launch.
+ * Replaces the chain matmul_had_cuda -> kv_quant_pack x2 -> init/append_kv_i4 of
+ * MultiLayerPagedKVCache4Bit.update (signrot/transformers/kv_cache.py:308-415). */
+int sr_kv_append_quant(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                       const void *last_page_offset, const void *k, const void *v, int64_t batch_size,
+                       int64_t new_tokens, int64_t num_layers, int64_t layer_idx, int64_t num_heads,
+                       int64_t page_size, int64_t head_dim, int hadamard_k, void *stream);
+/* o, q fp16 [batch, num_qo_heads, 128]; one new token per request attends to its cached
+ * sequence.  num_qo_heads is a multiple (1, 2, 4, 8) of num_kv_heads: q head h reads KV head
+ * h / (num_qo_heads / num_kv_heads).  tmp fp32 [batch, num_qo_heads, num_chunks, 132] is the
+ * split-KV workspace (NULL or num_chunks <= 1: no split).  hadamard_q applies H_128/sqrt(128)
+ * to q first (kv_cache.py:157-158).  Replaces _CUDA.batch_decode_i4 (bindings.cpp:508-559,
+ * flashinfer.cu:11-55, include/flashinfer/decode.cuh:481-751). */
+int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                       const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
+                       int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                       int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIGNROT_B200_H_ */

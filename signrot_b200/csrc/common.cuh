@@ -1,0 +1,100 @@
+// Shared helpers for the signrot_b200 CUDA library (sm_100a only).
+//
+// Everything exported from this library is a plain C function that takes
+// device pointers, sizes and a CUDA stream, returns an int status and never
+// allocates, synchronises or reads device memory on the host, so every entry
+// point can be captured in a CUDA graph.
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/signrot_b200.h"
+
+namespace sr {
+
+// ---------------------------------------------------------------- errors
+
+// Thread-local message of the last failing call; read by sr_last_error().
+char *last_error_buffer();
+int fail(int code, const char *fmt, ...);
+
+#define SR_REQUIRE(cond, code, ...)                    \
+    do {                                               \
+        if (!(cond)) return ::sr::fail((code), __VA_ARGS__); \
+    } while (0)
+
+// Checks the launch (not the execution) of the kernel just enqueued.
+inline int check_launch(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(SR_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return SR_OK;
+}
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+template <typename T>
+__host__ __device__ __forceinline__ T cdiv(T a, T b) { return (a + b - 1) / b; }
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+// ---------------------------------------------------------------- device math
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// rcp.approx.ftz.f32: the reciprocal the toolkit's device __hdiv() uses.  Hoisted
+// out of per-element loops, so that  q = rn_h(float(x) * rcp)  reproduces
+// __hdiv(x, s) for every quotient that can change a 4-bit code (the FMA fix-up
+// __hdiv applies to results below 2^-17 cannot move a value across +-0.5).
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ int clampi(int v, int lo, int hi) { return max(lo, min(hi, v)); }
+
+// Symmetric code of one fp16 value: clamp(half2int_rn(x / s), -8, 7).
+__device__ __forceinline__ int sym_code(__half x, float rcp) {
+    __half v = __float2half_rn(__half2float(x) * rcp);
+    return clampi(__half2int_rn(v), -8, 7);
+}
+// Asymmetric code: clamp(half2int_rn(x / s) + zero, lo, hi).
+__device__ __forceinline__ int asym_code(__half x, float rcp, int zero, int lo, int hi) {
+    __half v = __float2half_rn(__half2float(x) * rcp);
+    return clampi(__half2int_rn(v) + zero, lo, hi);
+}
+
+// bf16 -> fp16 goes through fp32, the same single rounding torch's .to(float16) does.
+__device__ __forceinline__ __half to_half(__half v) { return v; }
+__device__ __forceinline__ __half to_half(__nv_bfloat16 v) { return __float2half_rn(__bfloat162float(v)); }
+
+union Vec16 {
+    uint4 u;
+    __half h[8];
+    __nv_bfloat16 b[8];
+    __half2 h2[4];
+    uint32_t w[4];
+};
+
+}  // namespace sr

@@ -1,0 +1,79 @@
+// C ABI of the dense W4A4 GEMM: regime selection between the weight-streaming
+// kernel (few rows) and the tcgen05 kernel, argument validation.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include <cstdlib>
+#include <cstring>
+
+namespace sr {
+
+// 0 = by shape, 1 = always the few-rows kernel, 2 = always the tensor-core kernel.
+// SIGNROT_B200_GEMM=small|tc pins one kernel (used by the parity tests to cover both
+// kernels at every shape); sr_set_gemm_kernel() does the same from code.
+static int g_force = -1;
+static int forced_kernel() {
+    if (g_force < 0) {
+        const char *e = getenv("SIGNROT_B200_GEMM");
+        g_force = 0;
+        if (e && !strcmp(e, "small")) g_force = 1;
+        if (e && !strcmp(e, "tc")) g_force = 2;
+    }
+    return g_force;
+}
+
+static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned,
+                    const Epilogue &ep, void *stream, const char *who) {
+    SR_REQUIRE(M >= 0 && N >= 0 && K >= 0, SR_ERR_INVALID, "%s: negative size", who);
+    SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "%s: A.shape[-1]: %lld must be multiplication of 32", who, (long long)K);
+    if (M == 0 || N == 0) return SR_OK;
+    SR_REQUIRE(K > 0, SR_ERR_INVALID, "%s: K must be positive", who);
+    SR_REQUIRE(A && B, SR_ERR_INVALID, "%s: null pointer", who);
+    SR_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K <= 131072, SR_ERR_UNSUPPORTED, "%s: size out of range", who);
+    SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "%s: operands must be 16-byte aligned", who);
+    const int f = forced_kernel();
+    const bool small = f == 1 || (f == 0 && M <= 32);
+    if (small)
+        return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
+                                 as_stream(stream));
+    return launch_gemm_tc((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
+}
+
+}  // namespace sr
+
+using namespace sr;
+
+extern "C" {
+
+int sr_set_gemm_kernel(int which) {
+    SR_REQUIRE(which >= 0 && which <= 2, SR_ERR_INVALID, "set_gemm_kernel: expected 0 (auto), 1 (few rows) or 2 (tcgen05)");
+    g_force = which;
+    return SR_OK;
+}
+
+int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned, void *C,
+                 void *stream) {
+    SR_REQUIRE(M == 0 || N == 0 || C != nullptr, SR_ERR_INVALID, "matmul: null output");
+    Epilogue ep = {};
+    ep.mode = 0;
+    ep.c = (int32_t *)C;
+    ep.ldc = N;
+    return run_gemm(A, B, M, N, K, a_unsigned, ep, stream, "matmul");
+}
+
+int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                   const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream) {
+    SR_REQUIRE(M == 0 || N == 0 || (out && a_scale && w_scale), SR_ERR_INVALID, "w4a4_linear: null pointer");
+    SR_REQUIRE(a_zero == nullptr || w_sum != nullptr, SR_ERR_INVALID,
+               "w4a4_linear: asymmetric activations need the int4 row sums of the weight");
+    Epilogue ep = {};
+    ep.mode = 1;
+    ep.out = (__half *)out;
+    ep.a_scale = (const __half *)a_scale;
+    ep.w_scale = (const __half *)w_scale;
+    ep.a_zero = (const int8_t *)a_zero;
+    ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
+    ep.bias = (const __half *)bias;
+    return run_gemm(A, W, M, N, K, a_zero != nullptr, ep, stream, "w4a4_linear");
+}
+
+}  // extern "C"

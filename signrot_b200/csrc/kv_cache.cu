@@ -1,0 +1,472 @@
+// int4 paged KV cache: append, prefill scatter, fused Hadamard+quantize+append, and
+// GQA-native split-KV decode attention with in-register dequantisation.
+//
+// Cache layout (signrot/transformers/kv_cache.py:185-196, kernels/include/flashinfer/page.cuh:60-95):
+//   data  uint8 [pages, layers, 2 (k,v), heads, page_size, head_dim/2]   two 4-bit codes per byte
+//   param fp16  [pages, layers, 2,       heads, page_size, 2]            (scale, zero) per vector
+//   dequant: float(code) * scale - zero                                  (quantization.cuh:76)
+// Request b owns pages indices[indptr[b] .. indptr[b+1]); its last page holds
+// last_page_offset[b] valid entries.
+//
+// Replaces kernels/flashinfer.cu:11-106 + include/flashinfer/decode.cuh:481-751 and
+// page.cuh:119-219.  Differences in design, not in results:
+//  * one CTA serves all q heads that share a KV head, so a GQA cache is stored once
+//    (the reference repeats every KV head group_size times, kv_cache.py:346-353);
+//  * the dot products use  sum_d q_d (c_d s - z) = s sum_d q_d c_d - z sum_d q_d,
+//    so codes are consumed as integers and the affine part is applied per vector;
+//  * quantisation of new K/V (with the Hadamard on K) happens in the kernel that
+//    writes the page slot.
+#include "common.cuh"
+#include <cfloat>
+
+namespace sr {
+
+struct PagedKV {
+    uint8_t *data;
+    __half2 *param;
+    const int32_t *indptr, *indices, *last_page_offset;
+    uint32_t num_layers, layer, heads, page_size;  // head_dim fixed to 128
+
+    __device__ __forceinline__ size_t vec_index(uint32_t page, uint32_t kv, uint32_t head, uint32_t entry) const {
+        return ((((size_t)page * num_layers + layer) * 2 + kv) * heads + head) * page_size + entry;
+    }
+    __device__ __forceinline__ uint32_t seq_len(uint32_t b) const {
+        return (uint32_t)(indptr[b + 1] - indptr[b] - 1) * page_size + (uint32_t)last_page_offset[b];
+    }
+};
+
+constexpr int HD = 128;
+
+// ------------------------------------------------------------------ scatter of pre-quantised vectors
+
+// One warp per (token, head): lanes 0-3 copy K (64 B), 4-7 copy V, 8/9 the params.
+// k/v: [tokens, heads, 64] uint8, k_param/v_param: [tokens, heads] half2.
+// seqlen_indptr == nullptr: decode append, one token per request (page.cuh:119-164);
+// otherwise prefill, request b appends tokens seqlen_indptr[b]..seqlen_indptr[b+1] (page.cuh:166-219).
+__global__ void __launch_bounds__(256)
+kv_scatter_kernel(PagedKV kv, const uint8_t *__restrict__ k, const uint8_t *__restrict__ v,
+                  const __half2 *__restrict__ k_param, const __half2 *__restrict__ v_param,
+                  const int32_t *__restrict__ seqlen_indptr, uint32_t batch, uint32_t total_tokens) {
+    const uint32_t w = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= total_tokens * kv.heads) return;
+    const uint32_t tok = w / kv.heads, head = w % kv.heads;
+    uint32_t b, pos;
+    if (seqlen_indptr == nullptr) {
+        b = tok;
+        pos = kv.seq_len(b) - 1;
+    } else {
+        b = 0;
+        while (b + 1 < batch && (uint32_t)seqlen_indptr[b + 1] <= tok) ++b;
+        const uint32_t n_app = (uint32_t)(seqlen_indptr[b + 1] - seqlen_indptr[b]);
+        pos = kv.seq_len(b) - n_app + (tok - (uint32_t)seqlen_indptr[b]);
+    }
+    const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
+    const uint32_t entry = pos % kv.page_size;
+    const size_t src = ((size_t)tok * kv.heads + head);
+    if (lane < 8) {
+        const uint32_t which = lane >> 2, part = lane & 3;
+        const uint4 val = *reinterpret_cast<const uint4 *>((which ? v : k) + src * 64 + part * 16);
+        *reinterpret_cast<uint4 *>(kv.data + kv.vec_index(page, which, head, entry) * 64 + part * 16) = val;
+    } else if (lane == 8) {
+        kv.param[kv.vec_index(page, 0, head, entry)] = k_param[src];
+    } else if (lane == 9) {
+        kv.param[kv.vec_index(page, 1, head, entry)] = v_param[src];
+    }
+}
+
+// ------------------------------------------------------------------ fused Hadamard + quantise + append
+
+__device__ __forceinline__ void kv_params_dev(float vmin, float vmax, __half &scale, __half &zero) {
+    // signrot/kernels/fused.cu:236-247
+    const __half hmin = __float2half(vmin), hmax = __float2half(vmax);
+    __half diff = __float2half(__half2float(hmax) - __half2float(hmin));
+    diff = __float2half(fmaxf(__half2float(diff), 1e-5f));
+    scale = __float2half(__half2float(diff) / 15.f);
+    zero = __hneg(hmin);
+}
+
+// One warp per (token, head, k|v) vector of 128: lane holds 4 consecutive values.
+// k, v: [B, T, heads, 128] fp16.  K goes through H_128 / sqrt(128) (fp32 butterflies,
+// rounded to fp16: kv_cache.py:70-73,308-309) when had_k is set, then both are
+// quantised (fused.cu:214-265) straight into their page slots.
+__global__ void __launch_bounds__(256)
+kv_append_quant_kernel(PagedKV kv, const __half *__restrict__ k, const __half *__restrict__ v, uint32_t batch,
+                       uint32_t T, int had_k, float had_scale) {
+    const uint32_t w = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const uint32_t total = batch * T * kv.heads * 2;
+    if (w >= total) return;
+    const uint32_t which = w & 1;
+    const uint32_t vec = w >> 1;  // (b, t, head)
+    const uint32_t head = vec % kv.heads;
+    const uint32_t t = (vec / kv.heads) % T, b = vec / (kv.heads * T);
+    const __half *src = (which ? v : k) + (size_t)vec * HD + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2 *>(src);
+    const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+    float a[4] = {__half2float(h01.x), __half2float(h01.y), __half2float(h23.x), __half2float(h23.y)};
+    if (which == 0 && had_k) {
+        float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
+        a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float o = __shfl_xor_sync(0xffffffffu, a[j], m);
+                a[j] = (lane & m) ? (o - a[j]) : (a[j] + o);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
+    }
+    float vmax = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+    float vmin = fminf(fminf(a[0], a[1]), fminf(a[2], a[3]));
+    vmax = warp_max(vmax);
+    vmin = warp_min(vmin);
+    __half scale, zero;
+    kv_params_dev(vmin, vmax, scale, zero);
+    const float fs = __half2float(scale), fz = __half2float(zero);
+    uint32_t code = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __half shifted = __float2half(a[j] + fz);
+        const __half scaled = __float2half(__half2float(shifted) / fs);
+        code |= (uint32_t)clampi((int)nearbyintf(__half2float(scaled)), 0, 15) << (4 * j);
+    }
+    const uint32_t pos = kv.seq_len(b) - T + t;
+    const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
+    const uint32_t entry = pos % kv.page_size;
+    const size_t vi = kv.vec_index(page, which, head, entry);
+    reinterpret_cast<uint16_t *>(kv.data + vi * 64)[lane] = (uint16_t)code;
+    if (lane == 0) {
+        __half2 p;
+        p.x = scale;
+        p.y = zero;
+        kv.param[vi] = p;
+    }
+}
+
+// ------------------------------------------------------------------ decode attention
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// grid (batch, kv_heads, chunks), 128 threads.  G = q heads per KV head.  Eight lanes
+// share one cached token (16 dims each); a warp covers four tokens per step, the CTA 16.
+template <int G>
+__global__ void __launch_bounds__(128)
+decode_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
+              uint32_t num_chunks, int had_q, float had_scale) {
+    const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
+    const uint32_t hq_total = gridDim.y * G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane & 7;        // which 16-dim slice
+    const int slot = (warp << 2) | (lane >> 3);  // token slot 0..15
+
+    __shared__ float sh_q[G][HD];
+    __shared__ float sh_o[4][G][HD];
+    __shared__ float sh_md[4][G][2];
+
+    // ---- load q (optionally Hadamard-rotated, kv_cache.py:157-158), one warp per q head
+    const float sm_scale = 1.44269504088896340736f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+    for (int g = warp; g < G; g += 4) {
+        const uint32_t hq = hk * G + g;
+        const __half *qp = q + ((size_t)b * hq_total + hq) * HD + lane * 4;
+        const uint2 raw = *reinterpret_cast<const uint2 *>(qp);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+        float a[4] = {__half2float(h01.x), __half2float(h01.y), __half2float(h23.x), __half2float(h23.y)};
+        if (had_q) {
+            float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
+            a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float ot = __shfl_xor_sync(0xffffffffu, a[j], m);
+                    a[j] = (lane & m) ? (ot - a[j]) : (a[j] + ot);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sh_q[g][lane * 4 + j] = a[j];
+    }
+    __syncthreads();
+
+    float qv[G][16], qsum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            qv[g][j] = sh_q[g][sub * 16 + j] * sm_scale;
+            s += qv[g][j];
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        qsum[g] = s;
+    }
+
+    // ---- this chunk's token range
+    const uint32_t page_begin = (uint32_t)kv.indptr[b], page_end = (uint32_t)kv.indptr[b + 1];
+    const uint32_t pages_total = page_end - page_begin;
+    const uint32_t per_chunk = (pages_total + num_chunks - 1) / num_chunks;
+    const uint32_t cp_begin = min(chunk * per_chunk, pages_total), cp_end = min(cp_begin + per_chunk, pages_total);
+    const uint32_t last_valid = (uint32_t)kv.last_page_offset[b];
+
+    float m[G], d[G], acc[G][16], accz[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -5e4f;
+        d[g] = 0.f;
+        accz[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[g][j] = 0.f;
+    }
+
+    for (uint32_t pi = cp_begin; pi < cp_end; ++pi) {
+        const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
+        const uint32_t valid = (pi == pages_total - 1) ? last_valid : kv.page_size;
+        const size_t kbase = kv.vec_index(page, 0, hk, 0), vbase = kv.vec_index(page, 1, hk, 0);
+        for (uint32_t e = slot; e < valid; e += 16) {
+            const uint2 kc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (kbase + e) * 64) + sub);
+            const uint2 vc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (vbase + e) * 64) + sub);
+            const float2 kp = __half22float2(kv.param[kbase + e]);
+            const float2 vp = __half22float2(kv.param[vbase + e]);
+            float kf[16], vf[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                kf[j] = (float)((kc.x >> (4 * j)) & 15u);
+                kf[8 + j] = (float)((kc.y >> (4 * j)) & 15u);
+                vf[j] = (float)((vc.x >> (4 * j)) & 15u);
+                vf[8 + j] = (float)((vc.y >> (4 * j)) & 15u);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float dot = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) dot = fmaf(qv[g][j], kf[j], dot);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+                const float x = dot * kp.x - kp.y * qsum[g];
+                const float m_new = fmaxf(m[g], x);
+                const float alpha = ex2(m[g] - m_new);
+                const float p = ex2(x - m_new);
+                m[g] = m_new;
+                d[g] = d[g] * alpha + p;
+                const float ps = p * vp.x;
+                accz[g] = accz[g] * alpha + p * vp.y;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[g][j] = fmaf(ps, vf[j], acc[g][j] * alpha);
+            }
+        }
+    }
+
+    // ---- merge the 16 token slots (same dim slice `sub`)
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[g][j] -= accz[g];
+        // within the warp: lanes sub, sub+8, sub+16, sub+24
+#pragma unroll
+        for (int off = 8; off < 32; off <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m[g], off);
+            const float d_o = __shfl_xor_sync(0xffffffffu, d[g], off);
+            const float m_new = fmaxf(m[g], m_o);
+            const float a = ex2(m[g] - m_new), bsc = ex2(m_o - m_new);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float o_o = __shfl_xor_sync(0xffffffffu, acc[g][j], off);
+                acc[g][j] = acc[g][j] * a + o_o * bsc;
+            }
+            d[g] = d[g] * a + d_o * bsc;
+            m[g] = m_new;
+        }
+    }
+    // across warps through shared memory (warp w's lanes 0..7 hold its merged state)
+    float *so = &sh_o[0][0][0];
+    if (lane < 8) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) so[((warp * G + g) * HD) + sub * 16 + j] = acc[g][j];
+            if (sub == 0) {
+                sh_md[warp][g][0] = m[g];
+                sh_md[warp][g][1] = d[g];
+            }
+        }
+    }
+    __syncthreads();
+    // thread t finalises dim t (HD == blockDim) for every g
+    for (int g = 0; g < G; ++g) {
+        float mm = sh_md[0][g][0];
+#pragma unroll
+        for (int w = 1; w < 4; ++w) mm = fmaxf(mm, sh_md[w][g][0]);
+        float dd = 0.f, oo = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float sc = ex2(sh_md[w][g][0] - mm);
+            dd += sh_md[w][g][1] * sc;
+            oo += so[((w * G + g) * HD) + tid] * sc;
+        }
+        const uint32_t hq = hk * G + g;
+        if (num_chunks == 1) {
+            o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+        } else {
+            float *dst = tmp + (((size_t)b * hq_total + hq) * num_chunks + chunk) * (HD + 4);
+            dst[tid] = oo;
+            if (tid == 0) {
+                dst[HD] = mm;
+                dst[HD + 1] = dd;
+            }
+        }
+    }
+}
+
+// grid (batch, q heads), 128 threads: combine the per-chunk states (decode.cuh:726-751).
+__global__ void __launch_bounds__(128)
+decode_merge_kernel(const float *__restrict__ tmp, __half *__restrict__ o, uint32_t num_chunks) {
+    const uint32_t b = blockIdx.x, h = blockIdx.y, H = gridDim.y;
+    const int tid = threadIdx.x;
+    const float *src = tmp + ((size_t)b * H + h) * num_chunks * (HD + 4);
+    float mm = -5e4f;
+    for (uint32_t c = 0; c < num_chunks; ++c) mm = fmaxf(mm, src[c * (HD + 4) + HD]);
+    float dd = 0.f, oo = 0.f;
+    for (uint32_t c = 0; c < num_chunks; ++c) {
+        const float sc = ex2(src[c * (HD + 4) + HD] - mm);
+        dd += src[c * (HD + 4) + HD + 1] * sc;
+        oo += src[c * (HD + 4) + tid] * sc;
+    }
+    o[((size_t)b * H + h) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+}
+
+}  // namespace sr
+
+using namespace sr;
+
+static int fill_kv(PagedKV &kv, void *kv_data, void *kv_param, const void *indptr, const void *indices,
+                   const void *last_page_offset, int64_t num_layers, int64_t layer_idx, int64_t heads,
+                   int64_t page_size, const char *who) {
+    SR_REQUIRE(kv_data && kv_param && indptr && indices && last_page_offset, SR_ERR_INVALID, "%s: null pointer", who);
+    SR_REQUIRE(num_layers > 0 && layer_idx >= 0 && layer_idx < num_layers, SR_ERR_INVALID, "%s: bad layer index", who);
+    SR_REQUIRE(heads > 0 && page_size > 0, SR_ERR_INVALID, "%s: bad cache geometry", who);
+    SR_REQUIRE(aligned16(kv_data) && aligned4(kv_param), SR_ERR_INVALID, "%s: cache buffers are misaligned", who);
+    kv.data = (uint8_t *)kv_data;
+    kv.param = (__half2 *)kv_param;
+    kv.indptr = (const int32_t *)indptr;
+    kv.indices = (const int32_t *)indices;
+    kv.last_page_offset = (const int32_t *)last_page_offset;
+    kv.num_layers = (uint32_t)num_layers;
+    kv.layer = (uint32_t)layer_idx;
+    kv.heads = (uint32_t)heads;
+    kv.page_size = (uint32_t)page_size;
+    return SR_OK;
+}
+
+extern "C" {
+
+int sr_append_kv_i4(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                    const void *last_page_offset, const void *k, const void *v, const void *k_param,
+                    const void *v_param, int64_t num_layers, int64_t layer_idx, int64_t num_heads, int64_t page_size,
+                    int64_t head_dim, int64_t batch_size, void *stream) {
+    SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "append_kv_i4: CHECK_EQ(head_dim, 128) failed. %lld vs 128", (long long)head_dim);
+    if (batch_size == 0) return SR_OK;
+    PagedKV kv;
+    int rc = fill_kv(kv, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx, num_heads,
+                     page_size, "append_kv_i4");
+    if (rc) return rc;
+    SR_REQUIRE(k && v && k_param && v_param, SR_ERR_INVALID, "append_kv_i4: null pointer");
+    const uint32_t warps = (uint32_t)(batch_size * num_heads);
+    kv_scatter_kernel<<<cdiv<uint32_t>(warps, 8), 256, 0, as_stream(stream)>>>(
+        kv, (const uint8_t *)k, (const uint8_t *)v, (const __half2 *)k_param, (const __half2 *)v_param, nullptr,
+        (uint32_t)batch_size, (uint32_t)batch_size);
+    return check_launch("append_kv_i4");
+}
+
+int sr_init_kv_i4(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                  const void *last_page_offset, const void *k, const void *v, const void *k_param,
+                  const void *v_param, const void *seqlen_indptr, int64_t total_tokens, int64_t num_layers,
+                  int64_t layer_idx, int64_t num_heads, int64_t page_size, int64_t head_dim, int64_t batch_size,
+                  void *stream) {
+    SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "init_kv_i4: CHECK_EQ(head_dim, 128) failed. %lld vs 128", (long long)head_dim);
+    if (batch_size == 0 || total_tokens == 0) return SR_OK;
+    PagedKV kv;
+    int rc = fill_kv(kv, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx, num_heads,
+                     page_size, "init_kv_i4");
+    if (rc) return rc;
+    SR_REQUIRE(k && v && k_param && v_param && seqlen_indptr, SR_ERR_INVALID, "init_kv_i4: null pointer");
+    const int64_t warps = total_tokens * num_heads;
+    SR_REQUIRE(warps < (1ll << 31), SR_ERR_UNSUPPORTED, "init_kv_i4: too many tokens");
+    kv_scatter_kernel<<<(unsigned)cdiv<int64_t>(warps, 8), 256, 0, as_stream(stream)>>>(
+        kv, (const uint8_t *)k, (const uint8_t *)v, (const __half2 *)k_param, (const __half2 *)v_param,
+        (const int32_t *)seqlen_indptr, (uint32_t)batch_size, (uint32_t)total_tokens);
+    return check_launch("init_kv_i4");
+}
+
+int sr_kv_append_quant(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                       const void *last_page_offset, const void *k, const void *v, int64_t batch_size,
+                       int64_t new_tokens, int64_t num_layers, int64_t layer_idx, int64_t num_heads,
+                       int64_t page_size, int64_t head_dim, int hadamard_k, void *stream) {
+    SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "kv_append_quant: head_dim must be 128, got %lld", (long long)head_dim);
+    if (batch_size == 0 || new_tokens == 0) return SR_OK;
+    PagedKV kv;
+    int rc = fill_kv(kv, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx, num_heads,
+                     page_size, "kv_append_quant");
+    if (rc) return rc;
+    SR_REQUIRE(k && v, SR_ERR_INVALID, "kv_append_quant: null pointer");
+    const int64_t warps = batch_size * new_tokens * num_heads * 2;
+    SR_REQUIRE(warps < (1ll << 31), SR_ERR_UNSUPPORTED, "kv_append_quant: too many tokens");
+    const float had_scale = (float)(1.0 / sqrt(128.0));
+    kv_append_quant_kernel<<<(unsigned)cdiv<int64_t>(warps, 8), 256, 0, as_stream(stream)>>>(
+        kv, (const __half *)k, (const __half *)v, (uint32_t)batch_size, (uint32_t)new_tokens, hadamard_k, had_scale);
+    return check_launch("kv_append_quant");
+}
+
+int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                       const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
+                       int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                       int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream) {
+    SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "batch_decode_i4: CHECK_EQ(head_dim, 128) failed. %lld vs 128", (long long)head_dim);
+    if (batch_size == 0) return SR_OK;
+    PagedKV kv;
+    int rc = fill_kv(kv, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                     num_kv_heads, page_size, "batch_decode_i4");
+    if (rc) return rc;
+    SR_REQUIRE(o && q, SR_ERR_INVALID, "batch_decode_i4: null pointer");
+    SR_REQUIRE(num_qo_heads > 0 && num_qo_heads % num_kv_heads == 0, SR_ERR_INVALID,
+               "batch_decode_i4: %lld q heads cannot share %lld kv heads", (long long)num_qo_heads, (long long)num_kv_heads);
+    const int64_t G = num_qo_heads / num_kv_heads;
+    SR_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, SR_ERR_UNSUPPORTED, "batch_decode_i4: group size %lld not supported", (long long)G);
+    if (tmp == nullptr || num_chunks < 1) num_chunks = 1;
+    SR_REQUIRE(num_chunks <= 65535, SR_ERR_INVALID, "batch_decode_i4: too many chunks");
+    SR_REQUIRE(aligned4(q) && aligned4(o), SR_ERR_INVALID, "batch_decode_i4: q/o misaligned");
+    cudaStream_t st = as_stream(stream);
+    dim3 grid((unsigned)batch_size, (unsigned)num_kv_heads, (unsigned)num_chunks);
+    const float had_scale = (float)(1.0 / sqrt(128.0));
+    const __half *qp = (const __half *)q;
+    __half *op = (__half *)o;
+    float *tp = (float *)tmp;
+    const uint32_t nc = (uint32_t)num_chunks;
+    switch (G) {
+        case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
+        case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
+        case 4: decode_kernel<4><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
+        default: decode_kernel<8><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
+    }
+    rc = check_launch("batch_decode_i4");
+    if (rc) return rc;
+    if (num_chunks > 1) {
+        dim3 mgrid((unsigned)batch_size, (unsigned)num_qo_heads);
+        decode_merge_kernel<<<mgrid, 128, 0, st>>>(tp, op, nc);
+        rc = check_launch("batch_decode_i4 (merge)");
+    }
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,346 @@
+"""int4 paged KV cache with the interface of `signrot.transformers.kv_cache`
+(signrot/transformers/kv_cache.py:12-521).
+
+Layout (same as the reference): `pages` uint8 [pages, layers, 2, heads, page_size, head_dim/2],
+`scales` fp16 [pages, layers, 2, heads, page_size, 2] = (scale, zero); the physical page of
+(request b, logical page j) is j * batch_size + b.
+
+What differs from the reference is how the work is done, not what is stored or returned:
+  * `update` runs ONE kernel per layer that rotates K (Hadamard over head_dim), quantizes K
+    and V and writes their page slots (the reference chains a Hadamard, two quantizers and an
+    append/init kernel, kv_cache.py:308-415);
+  * a GQA cache keeps its `num_heads` KV heads once; the decode kernel serves all the query
+    heads of a group from one read (the reference repeats every KV head `group_size` times,
+    kv_cache.py:346-353).  `group_size` is therefore only the q-per-kv ratio here.
+"""
+from __future__ import annotations
+
+import functools
+import math
+from typing import Any, Dict, Optional
+
+import torch
+
+from .. import _lib
+from .._lib import ptr, require_cuda, run
+from ..functional import kernel as _kernel
+from ..functional.quantization import get_minq_maxq
+
+try:  # the cache only needs the base class to be accepted by HF model code
+    from transformers.cache_utils import Cache as _HFCache
+except Exception:  # pragma: no cover - transformers is optional for the kernels
+    class _HFCache:  # type: ignore
+        def __init__(self, *a, **k):
+            pass
+
+
+# ----------------------------------------------------------------------------- torch references
+
+def asym_quantize_and_pack_i4(x, clip_factor_a_max=torch.tensor(1.0), clip_factor_a_min=torch.tensor(1.0),
+                              lac: bool = False, quantize: bool = True):
+    """Torch statement of the KV quantizer (kv_cache.py:12-58); the non-`lac` branch is what
+    `kv_quant_pack` computes."""
+    _, maxq = get_minq_maxq(bits=4, sym=False)
+    xmax = torch.amax(x, dim=-1, keepdim=True)
+    xmin = torch.amin(x, dim=-1, keepdim=True)
+    if lac:
+        zeros = torch.zeros_like(xmax)
+        xmax, xmin = torch.maximum(xmax, zeros) * clip_factor_a_max, torch.minimum(xmin, zeros) * clip_factor_a_min
+        both_zero = (xmin == 0) & (xmax == 0)
+        xmin = torch.where(both_zero, torch.full_like(xmin, -1.0), xmin)
+        xmax = torch.where(both_zero, torch.full_like(xmax, 1.0), xmax)
+        scale = (xmax - xmin) / maxq
+        zero = torch.round((-1.0 * xmin) / scale)
+        q = torch.clamp((x / scale).round() + zero, 0, maxq)
+    else:
+        scale = (xmax - xmin).clamp(min=1e-5) / maxq
+        zero = -xmin
+        q = torch.clamp(torch.round((x + zero) / scale), 0, maxq)
+    if not quantize:
+        return scale * (q - zero), scale, zero
+    q = q.to(dtype=torch.uint8)
+    return q[..., 0::2] | (q[..., 1::2] << 4), scale, zero
+
+
+def unpack_i4_and_asym_dequantize(q, scale, zero, lac: bool = False):
+    assert q.dtype == torch.uint8
+    q = torch.stack((q & 0x0F, (q >> 4) & 0x0F), dim=-1).view(*q.shape[:-1], q.shape[-1] * 2)
+    return scale * (q - zero) if lac else q * scale - zero
+
+
+def matmul_had_cuda(X, dtype):
+    """Hadamard over the last dimension in `dtype`, cast back (kv_cache.py:70-73)."""
+    n = X.shape[-1]
+    y = _kernel.hadamard(X.to(dtype), None, 1, scale=float(1 / math.sqrt(n)))
+    return y.to(X.dtype).view(X.shape)
+
+
+# ----------------------------------------------------------------------------- kernel wrappers
+
+def _geometry(kv_data):
+    if kv_data.dim() != 6:
+        raise RuntimeError("kv_data must be a 6D tensor")
+    return kv_data.size(1), kv_data.size(3), kv_data.size(4), kv_data.size(5) * 2
+
+
+def init_kv_i4(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, k, v, k_param, v_param,
+               seqlen_indptr, layer_idx):
+    """Scatter a whole quantized prompt per request into its pages (kv_cache.py:76-86)."""
+    dev = require_cuda("init_kv_i4", kv_data, kv_indptr, kv_indices, last_page_offset, k, v, seqlen_indptr)
+    L, H, P, D = _geometry(kv_data)
+    batch = last_page_offset.size(0)
+    if kv_indptr.size(0) != batch + 1 or seqlen_indptr.size(0) != batch + 1:
+        raise RuntimeError("CHECK_EQ(kv_indptr.size(0), batch_size + 1) failed.")
+    run(dev, "sr_init_kv_i4", ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices), ptr(last_page_offset),
+        ptr(k), ptr(v), ptr(k_param.contiguous()), ptr(v_param.contiguous()), ptr(seqlen_indptr), k.size(0), L,
+        int(layer_idx), H, P, D, batch)
+
+
+def append_kv_i4(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, k, v, k_param, v_param, layer_idx):
+    """Write one quantized token per request into its slot (kv_cache.py:89-99)."""
+    dev = require_cuda("append_kv_i4", kv_data, kv_indptr, kv_indices, last_page_offset, k, v)
+    L, H, P, D = _geometry(kv_data)
+    batch = k.size(0)
+    if kv_indptr.size(0) != batch + 1 or last_page_offset.size(0) != batch:
+        raise RuntimeError("CHECK_EQ(kv_indptr.size(0), batch_size + 1) failed.")
+    run(dev, "sr_append_kv_i4", ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices), ptr(last_page_offset),
+        ptr(k), ptr(v), ptr(k_param.contiguous()), ptr(v_param.contiguous()), L, int(layer_idx), H, P, D, batch)
+
+
+def batch_decode_i4(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, layer_idx, tmp=None,
+                    num_chunks=1, hadamard_q=False):
+    """Decode attention of one new token per request over the int4 cache (kv_cache.py:101-107).
+    o, q: fp16 [batch, q_heads, 128]; q_heads may be a multiple of the cache's head count."""
+    dev = require_cuda("batch_decode_i4", o, q, kv_data, kv_indptr, kv_indices, last_page_offset, tmp)
+    if o.dim() != 3 or q.dim() != 3 or o.shape != q.shape:
+        raise RuntimeError("o and q must be [B, N, D] tensors of the same shape")
+    if kv_data.dtype != torch.uint8 or kv_param.dtype != torch.float16:
+        raise RuntimeError("kv_data must be uint8 and kv_param fp16")
+    L, H, P, D = _geometry(kv_data)
+    batch, hq = o.size(0), o.size(1)
+    if kv_indptr.size(0) != batch + 1 or last_page_offset.size(0) != batch:
+        raise RuntimeError("CHECK_EQ(kv_indptr.size(0), batch_size + 1) failed.")
+    if tmp is not None and num_chunks > 1:
+        if tmp.dtype != torch.float32 or tmp.numel() != batch * hq * num_chunks * (D + 4):
+            raise RuntimeError("tmp must be fp32 [batch, heads, chunks, head_dim + 4]")
+    else:
+        tmp, num_chunks = None, 1
+    run(dev, "sr_batch_decode_i4", ptr(o), ptr(q), ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices),
+        ptr(last_page_offset), L, int(layer_idx), hq, H, P, D, batch, ptr(tmp), int(num_chunks), int(bool(hadamard_q)))
+
+
+def kv_append_quant(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, k, v, layer_idx, hadamard_k=True):
+    """k, v fp16 [batch, new_tokens, heads, 128] -> rotate K, quantize both, write the slots of
+    the last `new_tokens` positions of every request."""
+    dev = require_cuda("kv_append_quant", kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, k, v)
+    L, H, P, D = _geometry(kv_data)
+    if k.dtype != torch.float16 or v.dtype != torch.float16 or k.shape != v.shape or k.dim() != 4:
+        raise RuntimeError("kv_append_quant expects fp16 [B, T, H, D] k and v of the same shape")
+    if k.size(2) != H or k.size(3) != D:
+        raise RuntimeError("kv_append_quant: k/v heads or head_dim do not match the cache")
+    run(dev, "sr_kv_append_quant", ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices),
+        ptr(last_page_offset), ptr(k), ptr(v), k.size(0), k.size(1), L, int(layer_idx), H, P, D,
+        int(bool(hadamard_k)))
+
+
+# ----------------------------------------------------------------------------- cache object
+
+class _AttentionStub:
+    """Decode-time attention over the cache; returned (bound) by `update` (kv_cache.py:144-170)."""
+
+    def __init__(self, hadamard_dtype):
+        self.hadamard_dtype = hadamard_dtype
+        self.num_chunks = 1
+        self.tmp = None
+
+    def forward(self, q, num_kv_heads, attention_kwargs, layer_idx):
+        bsz, q_len, hq, hd = q.shape
+        assert q_len == 1
+        q = q.reshape(bsz, hq, hd)
+        if q.dtype != torch.float16:
+            q = q.to(torch.float16)
+        q = q.contiguous()
+        out = torch.empty_like(q)
+        # the Hadamard on q (kv_cache.py:157-158) is applied inside the decode kernel
+        batch_decode_i4(out, q, **attention_kwargs, layer_idx=layer_idx, tmp=self.tmp, num_chunks=self.num_chunks,
+                        hadamard_q=self.hadamard_dtype is not None)
+        return out.unsqueeze(1)
+
+
+class MultiLayerPagedKVCache4Bit(_HFCache):
+    def __init__(self, batch_size, page_size, max_seq_len, device, n_layers, num_heads, head_dim,
+                 disable_quant=False, hadamard_dtype=torch.float16, group_size=1, lac=False):
+        if disable_quant:
+            raise NotImplementedError("the unquantized fp16 cache (a baseline knob of the reference) is not built")
+        if lac:
+            raise NotImplementedError("learned activation clipping is unused in the reference and not built")
+        if head_dim != 128:
+            raise RuntimeError(f"CHECK_EQ(head_dim, 128) failed. {head_dim} vs 128")
+        self.lac = lac
+        self.disable_quant = False
+        self.page_size = page_size
+        self.batch_size = batch_size
+        self.max_seq_len = max_seq_len
+        self.device = torch.device(device)
+        self.hadamard_dtype = hadamard_dtype
+        self.group_size = group_size
+        self.num_heads = num_heads
+        self.head_dim = head_dim
+        self.length = 0
+        max_pages = self.page_cnt_from_length(max_seq_len)
+        self.pages = torch.empty((max_pages * batch_size, n_layers, 2, num_heads, page_size, head_dim // 2),
+                                 dtype=torch.uint8, device=device)
+        self.scales = torch.empty((max_pages * batch_size, n_layers, 2, num_heads, page_size, 2),
+                                  dtype=torch.float16, device=device)
+        self._needs_init = [True] * n_layers
+        self._stub = _AttentionStub(hadamard_dtype)
+
+        # index tensors: allocated once, refreshed in place, so addresses captured by a CUDA
+        # graph stay valid for the whole decode
+        self._kv_indices_full = torch.empty(self.pages.shape[0], device=device, dtype=torch.int32)
+        self._spec_page_cnt = None
+        self._last_page_offset = torch.empty(batch_size, device=device, dtype=torch.int32)
+        self._indptr_base = torch.arange(batch_size + 1, device=device, dtype=torch.int32)
+        self._kv_indptr_buf = torch.empty(batch_size + 1, device=device, dtype=torch.int32)
+        self._specs_frozen = False
+        self._spec_cache = {"kv_data": self.pages, "kv_param": self.scales, "kv_indptr": self._kv_indptr_buf,
+                            "kv_indices": self._kv_indices_full, "last_page_offset": self._last_page_offset}
+        self._configure_decode_split(max_pages)
+
+    def _configure_decode_split(self, max_pages):
+        """Fixed number of sequence chunks per (request, KV head) so that about two CTAs per SM
+        are in flight; bounded by the page count (a chunk is a page range)."""
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        ctas = self.batch_size * self.num_heads
+        chunks = max(1, -(-2 * sms // ctas))
+        chunks = min(chunks, max(1, max_pages))
+        self._stub.num_chunks = chunks
+        if chunks > 1:
+            self._stub.tmp = torch.empty((self.batch_size, self.num_heads * self.group_size, chunks,
+                                          self.head_dim + 4), dtype=torch.float32, device=self.device)
+
+    def page_cnt_from_length(self, length):
+        return (length + self.page_size - 1) // self.page_size
+
+    def _ensure_page_cnt_per_batch(self, pages_per_request):
+        need = pages_per_request * self.batch_size
+        have = self.pages.shape[0]
+        if need <= have:
+            return
+        # a pool that grows re-lays every request's pages (physical page = j * batch + b needs no
+        # move: new pages get higher j), but the tensors move, so captured graphs become invalid
+        grow_to = max(need, have * 2)
+        extra = grow_to - have
+        self.pages = torch.cat([self.pages, torch.empty((extra, *self.pages.shape[1:]), dtype=self.pages.dtype,
+                                                        device=self.device)], dim=0)
+        self.scales = torch.cat([self.scales, torch.empty((extra, *self.scales.shape[1:]), dtype=self.scales.dtype,
+                                                          device=self.device)], dim=0)
+        self._kv_indices_full = torch.empty(self.pages.shape[0], device=self.device, dtype=torch.int32)
+        self._spec_page_cnt = None
+        self._spec_cache.update(kv_data=self.pages, kv_param=self.scales, kv_indices=self._kv_indices_full)
+
+    @property
+    def seen_tokens(self):
+        return self.length
+
+    def update(self, key_states, value_states, layer_idx: int, cache_kwargs: Optional[Dict[str, Any]] = None):
+        """key/value_states [B, T, kv_heads, 128].  Prefill (first call per layer) returns the
+        original K/V for the caller's dense attention; decode returns a callable that attends a
+        query [B, 1, q_heads, 128] to the cache (kv_cache.py:295-415)."""
+        bsz, added, heads, hd = key_states.shape
+        assert bsz == self.batch_size
+        cache_kwargs = cache_kwargs or {}
+        if cache_kwargs.get("attention_mask") is not None:
+            raise NotImplementedError("padded (masked) prefill is not supported by the fused append")
+        if layer_idx == 0:
+            new_len = self.length + added
+            self._ensure_page_cnt_per_batch(self.page_cnt_from_length(new_len))
+            self.length = new_len
+        specs = self.get_cache_specs_for_flash_infer(None)
+        first = self._needs_init[layer_idx]
+        if first:
+            self._needs_init[layer_idx] = False
+        else:
+            assert added == 1
+        k16 = key_states if key_states.dtype == torch.float16 else key_states.to(torch.float16)
+        v16 = value_states if value_states.dtype == torch.float16 else value_states.to(torch.float16)
+        kv_append_quant(**specs, k=k16.contiguous(), v=v16.contiguous(), layer_idx=layer_idx,
+                        hadamard_k=self.hadamard_dtype is not None)
+        if first:
+            return key_states, value_states
+        return functools.partial(self._stub.forward, num_kv_heads=heads, attention_kwargs=specs,
+                                 layer_idx=layer_idx)
+
+    def _set_page_cnt(self, page_cnt: int):
+        torch.mul(self._indptr_base, page_cnt, out=self._kv_indptr_buf)
+        if self._spec_page_cnt == page_cnt:
+            return
+        self._spec_page_cnt = page_cnt
+        j = torch.arange(page_cnt, device=self.device, dtype=torch.int32) * self.batch_size
+        b = torch.arange(self.batch_size, device=self.device, dtype=torch.int32)
+        self._kv_indices_full[: page_cnt * self.batch_size].copy_((j.unsqueeze(0) + b.unsqueeze(1)).reshape(-1))
+
+    def refresh_specs(self, length: int | None = None):
+        """Rewrites the index tensors for a uniform-length batch from the host-side length: two
+        small in-place writes, no device->host sync.  A CUDA-graph runner calls this between
+        replays (the graph itself must not contain these writes)."""
+        if length is None:
+            length = self.length
+        page_cnt = self.page_cnt_from_length(length)
+        last = length % self.page_size
+        if length != 0 and last == 0:
+            last = self.page_size
+        self._last_page_offset.fill_(last)
+        self._set_page_cnt(page_cnt)
+        return self._spec_cache
+
+    def freeze_specs(self, frozen=True):
+        """While frozen, `update` does not touch the index tensors (graph capture/replay)."""
+        self._specs_frozen = frozen
+
+    def get_cache_specs_for_flash_infer(self, attention_mask):
+        if attention_mask is not None:
+            raise NotImplementedError("padded (masked) prefill is not supported")
+        return self._spec_cache if self._specs_frozen else self.refresh_specs()
+
+    def reset(self):
+        """Rewind to empty without reallocating; captured graphs stay valid."""
+        self.length = 0
+        self._needs_init = [True] * len(self._needs_init)
+
+    def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
+        return self.length
+
+    def get_max_length(self) -> Optional[int]:
+        return None
+
+    def to_legacy_cache(self):
+        return self
+
+
+class HFCacheAdapter(_HFCache):
+    """Thin adapter that lets HF model code drive the paged cache (kv_cache.py:500-521)."""
+
+    def __init__(self, inner):
+        try:
+            super().__init__()
+        except Exception:
+            pass
+        self.inner = inner
+
+    def get_usable_length(self, kv_seq_len: int, layer_idx: int) -> int:
+        return self.inner.get_usable_length(kv_seq_len, layer_idx)
+
+    def get_seq_length(self, layer_idx: Optional[int] = 0) -> int:
+        return self.inner.get_seq_length()
+
+    def get_max_length(self):
+        return self.inner.get_max_length()
+
+    def update(self, key_states, value_states, layer_idx: int, cache_kwargs=None):
+        return self.inner.update(key_states, value_states, layer_idx, cache_kwargs)
+
+    def to_legacy_cache(self):
+        if hasattr(self.inner, "to_legacy_cache"):
+            return self.inner.to_legacy_cache()
+        return self
