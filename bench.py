@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("qlinear-8b-m4096"): one step = the three Llama-3-8B linear shapes
+(K, N) in {(4096, 4096), (4096, 14336), (14336, 4096)} at M = 4096 tokens, each as
+sign-adjusted online Hadamard rotation + per-token int4 quantization (one fused kernel on
+bf16 activations) followed by the W4A4 GEMM with fused dequant epilogue (fp16 output).
+Inputs are seeded synthetic tensors (activations ~N(0,1) with 0.1 % of channels x100, uniform
+int4 weight codes, fp16 scales).  Metric: TOP/s = 2*M*N*K summed over the three linears /
+device time.  With N > 1 every rank runs the same step on its own token rows (the path is
+row-parallel: no data-path collective); the timed region is bracketed by a barrier and a
+device synchronise and the slowest rank's time is used.
+
+The JSON line also carries: `roofline` (the tcgen05 GEMM against the int8 tensor peak,
+measured here with torch._int_mm), `rotate_quant` (the fused kernel against the HBM copy
+peak), `e2e` (the same step through the public API from pinned host buffers, copies timed),
+`cpu_baseline` (the CPU oracle's fake-quant statement of the same step on a bounded row
+sample), `clocks` (NVML samples taken during the timed region) and `gpu_launches`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M_TOKENS = 4096
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]  # (K, N)
+NBUF = 2  # activation/output buffer sets rotated between steps (each set alone exceeds L2)
+
+
+def ops_per_step(m=M_TOKENS):
+    return sum(2 * m * n * k for k, n in SHAPES)
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.period = period_s
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s), "power_w_max": round(max(self.power), 1) if self.power else None}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+def cpu_fake_quant_step(rows: int, cases, threads: int):
+    """One pass of the oracle's fake-quant statement of the step on `rows` tokens: rotation in
+    bf16 with fp32 butterflies, sign, per-token fake-quant, F.linear on dequantized bf16 weights
+    (fake_quant/quant_utils.py:322-386)."""
+    import oracle
+    from oracle import fake_quant as fq
+    torch.set_num_threads(threads)
+    t0 = time.perf_counter()
+    for c in cases:
+        y = oracle.rotate(c["x"][:rows], c["hadK"], c["K"], c["sign"])
+        y = fq.act_fake_quant(y, 1.0, True)
+        torch.nn.functional.linear(y, c["w_deq"])
+    return time.perf_counter() - t0
+
+
+def make_cpu_cases(rows: int):
+    import oracle
+    from oracle import fake_quant as fq
+    from signrot_b200.functional.hadamard import get_hadK
+    cases = []
+    for k, n in SHAPES:
+        c = fq.make_linear_case(rows, k, n, seed=0)
+        hadK, K = get_hadK(k)
+        w = (oracle.unpack_i4(c["w_packed"]).float() * c["w_scale"].float()).to(torch.bfloat16)
+        cases.append({"x": c["x"], "sign": c["sign"], "hadK": hadK, "K": K, "w_deq": w})
+    return cases
+
+
+def cpu_baseline(budget_s: float = 12.0, rows: int = 256):
+    threads = os.cpu_count() or 1
+    cases = make_cpu_cases(rows)
+    cpu_fake_quant_step(min(rows, 32), cases, threads)  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < 20):
+        times.append(cpu_fake_quant_step(rows, cases, threads))
+    best = sorted(times)[len(times) // 2]
+    return {"value": round(ops_per_step(rows) / best / 1e12, 4), "unit": "TOP/s", "cores": threads, "kind": "port",
+            "sample": f"{rows} of {M_TOKENS} token rows per linear, {len(times)} passes, median; "
+                      "oracle fake-quant (rotation + sign + fake-quant + bf16 F.linear)"}
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path = its Python fake-quant code.  That code
+    cannot travel to the GPU box, so the oracle port (validated against it, tests/golden/) is
+    timed on all host threads; each step is a bounded row sample of the workload."""
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    # bounded sample: rows per step sized so that K steps take roughly 20 s of CPU time
+    rows = max(32, min(1024, (76000 // steps) // 32 * 32))
+    threads = os.cpu_count() or 1
+    cases = make_cpu_cases(rows)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_fake_quant_step(rows, cases, threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_fake_quant_step(rows, cases, threads)
+    dt = time.perf_counter() - t0
+    val = ops_per_step(rows) * steps / dt / 1e12
+    sample = f"{rows} of {M_TOKENS} token rows per linear per step, {steps} steps (bounded sample)"
+    print(json.dumps({
+        "impl": "reference", "metric": "w4a4_qlinear_tops", "value": round(val, 4), "unit": "TOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt / steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 fake-quant (cpu)",
+        "data": "synthetic", "config": {"workload": "qlinear-8b-m4096", "shapes_KN": SHAPES, "M": M_TOKENS},
+        "cpu_baseline": {"value": round(val, 4), "unit": "TOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(val, 4), "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def make_linear_case(M, K, N, seed=0):
+    """Seeded synthetic inputs of one linear: activations ~N(0,1) in bf16 with 0.1 % of the
+    channels x100, int4 weight codes uniform in [-8, 7], fp16 weight scales ~U(0.001, 0.01), a
+    random +-1 sign vector."""
+    import math
+    from signrot_b200.functional import pack_i4
+    g = torch.Generator().manual_seed(seed * 1000003 + K * 31 + N)
+    x = torch.randn((M, K), generator=g, dtype=torch.float32)
+    gc = torch.Generator().manual_seed(1234 + K)
+    ch = torch.randperm(K, generator=gc)[: max(1, math.ceil(K / 1000))]
+    x[:, ch] *= 100.0
+    codes = torch.randint(-8, 8, (N, K), generator=g, dtype=torch.int8)
+    w_scale = (torch.rand((N, 1), generator=g) * 0.009 + 0.001).to(torch.float16)
+    sign = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).to(torch.int8)
+    return {"x": x.to(torch.bfloat16), "w_packed": pack_i4(codes), "w_scale": w_scale, "sign": sign}
+
+
+def measure_int8_peak(dev):
+    """Dense int8 tensor-core rate of cuBLASLt on this GPU (torch._int_mm 8192^3, best of 10)."""
+    n = 8192
+    a = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev)
+    b = torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev)
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return 2 * n ** 3 / (best * 1e-3) / 1e12
+
+
+def run_ours(args, rank, world, local_rank):
+    import signrot_b200  # noqa: F401  (fails loudly when the library is missing)
+    from signrot_b200 import _lib
+    from signrot_b200.functional import kernel
+    from signrot_b200.functional.hadamard import get_hadK
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    M = M_TOKENS
+    sets = []
+    weights = []
+    for k, n in SHAPES:
+        c = make_linear_case(M, k, n, seed=rank)
+        hadK, K = get_hadK(k)
+        weights.append({"w": c["w_packed"].to(dev), "ws": c["w_scale"].to(dev), "sign": c["sign"].to(dev),
+                        "hadK": hadK.to(dev, torch.float16) if hadK is not None else None, "K": K, "k": k, "n": n,
+                        "x_host": c["x"].pin_memory()})
+    for b in range(NBUF):
+        s = []
+        for w in weights:
+            x = w["x_host"].to(dev)
+            if b:
+                x = x.roll(b, 0).contiguous()
+            s.append({"x": x, "q": torch.empty((M, w["k"] // 2), dtype=torch.uint8, device=dev),
+                      "s": torch.empty((M, 1), dtype=torch.float16, device=dev),
+                      "out": torch.empty((M, w["n"]), dtype=torch.float16, device=dev)})
+        sets.append(s)
+    out_host = [torch.empty((M, w["n"]), dtype=torch.float16).pin_memory() for w in weights]
+
+    ptr, lib = _lib.ptr, _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    scale = {w["k"]: kernel.had_scale(w["k"]) for w in weights}
+
+    def launch_rotate(w, b):
+        rc = lib.sr_rotate_quant(ptr(b["x"]), _lib.SR_BF16, M, w["k"], ptr(w["hadK"]), w["K"], scale[w["k"]],
+                                 ptr(w["sign"]), None, 0, 1.0, 0, ptr(b["q"]), ptr(b["s"]), None, None, stream)
+        if rc:
+            raise RuntimeError(lib.sr_last_error().decode())
+
+    def launch_gemm(w, b):
+        rc = lib.sr_w4a4_linear(ptr(b["q"]), ptr(b["s"]), None, ptr(w["w"]), ptr(w["ws"]), None, None, M, w["n"],
+                                w["k"], ptr(b["out"]), stream)
+        if rc:
+            raise RuntimeError(lib.sr_last_error().decode())
+
+    def step(i, ev=None):
+        bufs = sets[i % NBUF]
+        for j, (w, b) in enumerate(zip(weights, bufs)):
+            if ev is not None:
+                ev[j][0].record()
+            launch_rotate(w, b)
+            if ev is not None:
+                ev[j][1].record()
+            launch_gemm(w, b)
+            if ev is not None:
+                ev[j][2].record()
+
+    int8_peak = measure_int8_peak(dev) if rank == 0 else None
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during warm-up")
+
+    # ---- timed region: exactly `steps` steps, device time, per-kernel events inside
+    evs = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SHAPES] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as clk:
+        e0.record()
+        for i in range(args.steps):
+            step(i, evs[i])
+        e1.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = t.item()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during the timed region")
+
+    rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in range(args.steps)) / args.steps for j in range(3)]
+    gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in range(args.steps)) / args.steps for j in range(3)]
+
+    # ---- end to end through the public API from pinned host memory
+    def e2e_step():
+        for w, oh in zip(weights, out_host):
+            x = w["x_host"].to(dev, non_blocking=True)
+            pk = kernel.rotate_quant(x, w["hadK"], w["K"], sign=w["sign"])
+            y = kernel.w4a4_linear(pk, w["w"], w["ws"])
+            oh.copy_(y, non_blocking=True)
+    e2e_steps = max(2, min(args.steps, 10))
+    e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_s = t.item()
+
+    if rank != 0:
+        return
+    pk_ = peaks()
+    ops = ops_per_step()
+    value = world * ops * args.steps / (ms * 1e-3) / 1e12
+    gemm_ops = [2 * M * n * k for k, n in SHAPES]
+    gemm_ach = sum(gemm_ops) / (sum(gemm_ms) * 1e-3) / 1e12
+    rot_bytes = [M * k * 2 + M * k // 2 + M * 2 + k for k, _ in SHAPES]
+    rot_ach = sum(rot_bytes) / (sum(rot_ms) * 1e-3) / 1e9
+    out = {
+        "metric": "w4a4_qlinear_tops", "value": round(value, 2), "unit": "TOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, int8 tensor-core MMA, int32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "qlinear-8b-m4096", "M": M, "shapes_KN": SHAPES, "activations": "bf16",
+                   "output": "fp16", "parallelism": f"rows x{world} (no collective)",
+                   "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB"},
+        "roofline": {"kernel": "gemm_tc_kernel (tcgen05 kind::i8, fused dequant)", "bound": "tensor",
+                     "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
+                     "frac": round(gemm_ach / int8_peak, 4),
+                     "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",
+                     "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "traffic": None,
+                     "per_shape_ms": [round(v, 4) for v in gemm_ms],
+                     "per_shape_tops": [round(o / (t * 1e-3) / 1e12, 1) for o, t in zip(gemm_ops, gemm_ms)]},
+        "rotate_quant": {"kernel": "fused rotate+sign+quant", "bound": "hbm", "achieved": round(rot_ach, 1),
+                         "peak": pk_["hbm_gbs"], "unit": "GB/s", "frac": round(rot_ach / pk_["hbm_gbs"], 4),
+                         "peak_source": pk_["source"], "per_shape_ms": [round(v, 4) for v in rot_ms],
+                         "per_shape_gbs": [round(b / (t * 1e-3) / 1e9, 1) for b, t in zip(rot_bytes, rot_ms)]},
+        "e2e": {"value": round(world * ops * e2e_steps / e2e_s / 1e12, 3), "unit": "TOP/s",
+                "h2d_bytes_per_step": sum(M * k * 2 for k, _ in SHAPES),
+                "d2h_bytes_per_step": sum(M * n * 2 for _, n in SHAPES), "steps": e2e_steps},
+        "gpu_launches": 6 * args.steps,
+        "clocks": clk.summary(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,151 @@
+"""int4 GEMM kernels (few-rows dp4a kernel and tcgen05 kernel) against the integer oracle:
+int32 accumulators bit-exact, fused dequant epilogue bit-exact."""
+import pytest
+import torch
+
+import oracle
+from signrot_b200 import _lib
+from signrot_b200.functional import kernel
+from signrot_b200 import nn as snn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _codes(rows, K, seed, lo=-8, hi=8):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi, (rows, K), generator=g, dtype=torch.int32)
+
+
+@pytest.fixture(autouse=True)
+def _auto_kernel():
+    yield
+    _lib.call_nostream("sr_set_gemm_kernel", 0)
+    assert _lib.device_status() == 0
+
+
+SHAPES = [(1, 4096, 4096), (16, 4096, 4096), (3, 64, 40), (33, 256, 96), (128, 4096, 512), (256, 4096, 4096),
+          (200, 1024, 300), (129, 14336, 264), (512, 2048, 14336), (64, 14336, 256), (16, 14336, 4096)]
+
+
+@pytest.mark.parametrize("which", [1, 2], ids=["few_rows", "tcgen05"])
+@pytest.mark.parametrize("M,K,N", SHAPES)
+def test_matmul_si4_bit_exact(which, M, K, N):
+    if which == 1 and M * N * K > 16 * 14336 * 4096 * 4:
+        pytest.skip("few-rows kernel is not meant for this size")
+    a, b = _codes(M, K, M + K), _codes(N, K, N + 7)
+    A, B = oracle.pack_i4(a), oracle.pack_i4(b)
+    _lib.call_nostream("sr_set_gemm_kernel", which)
+    C = kernel.matmul_si4_si4(A.to(DEV), B.to(DEV)).cpu()
+    assert _lib.device_status() == 0
+    assert torch.equal(C, oracle.matmul_i4(A, B))
+
+
+@pytest.mark.parametrize("which", [1, 2], ids=["few_rows", "tcgen05"])
+def test_matmul_ui4_and_extremes(which):
+    _lib.call_nostream("sr_set_gemm_kernel", which)
+    M, K, N = 130, 1024, 257 + 7
+    a, b = _codes(M, K, 1, 0, 16), _codes(N, K, 2)
+    A, B = oracle.pack_codes(a), oracle.pack_i4(b)
+    C = kernel.matmul_ui4_si4(A.to(DEV), B.to(DEV)).cpu()
+    assert torch.equal(C, oracle.matmul_i4(A, B, a_unsigned=True))
+    # worst-case magnitudes: every product 64 (signed) / -120 (unsigned x -8)
+    A = oracle.pack_i4(torch.full((5, 4096), -8, dtype=torch.int32))
+    B = oracle.pack_i4(torch.full((40, 4096), -8, dtype=torch.int32))
+    C = kernel.matmul_si4_si4(A.to(DEV), B.to(DEV)).cpu()
+    assert int(C.min()) == int(C.max()) == 64 * 4096
+    A = oracle.pack_codes(torch.full((5, 4096), 15, dtype=torch.int32))
+    C = kernel.matmul_ui4_si4(A.to(DEV), B.to(DEV)).cpu()
+    assert int(C.min()) == int(C.max()) == -120 * 4096
+
+
+def test_matmul_leading_dims_and_empty():
+    a, b = _codes(6, 128, 1), _codes(10, 128, 2)
+    A, B = oracle.pack_i4(a).view(2, 3, 64), oracle.pack_i4(b)
+    C = kernel.matmul_si4_si4(A.to(DEV), B.to(DEV))
+    assert C.shape == (2, 3, 10)
+    assert torch.equal(C.cpu().view(6, 10), oracle.matmul_i4(A.view(6, 64), B))
+    E = kernel.matmul_si4_si4(torch.empty((0, 64), dtype=torch.uint8, device=DEV), B.to(DEV))
+    assert E.shape == (0, 10)
+
+
+@pytest.mark.parametrize("which", [1, 2], ids=["few_rows", "tcgen05"])
+@pytest.mark.parametrize("M,K,N,asym,bias", [(16, 4096, 4096, False, False), (200, 1024, 264, False, True),
+                                             (130, 2048, 512, True, False), (7, 256, 40, True, True)])
+def test_w4a4_linear_fused_epilogue(which, M, K, N, asym, bias):
+    _lib.call_nostream("sr_set_gemm_kernel", which)
+    g = torch.Generator().manual_seed(M)
+    a = _codes(M, K, 3, 0 if asym else -8, 16 if asym else 8)
+    w = _codes(N, K, 4)
+    A, W = oracle.pack_codes(a), oracle.pack_i4(w)
+    sa = (torch.rand((M, 1), generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand((N, 1), generator=g) * 0.009 + 0.001).half()
+    za = torch.randint(0, 16, (M, 1), generator=g).to(torch.int8) if asym else None
+    bs = torch.randn((N,), generator=g).half() if bias else None
+    wsum = oracle.sum_i4(W)
+    want = oracle.w4a4_linear(A, sa, W, sw, za, wsum if asym else None, bs)
+    lin = snn.Linear4bit(K, N, bias=bias).to(DEV)
+    lin.weight.copy_(W)
+    lin.weight_scales = sw.to(DEV)
+    if bias:
+        lin.bias.copy_(bs)
+    pk = kernel.PackedQuantizedTensor(A.to(DEV), sa.to(DEV), za.to(DEV) if asym else None)
+    got = lin(pk)
+    assert torch.equal(got.cpu(), want)
+    # the reference's operator chain (matmul -> colrow -> dequant -> bias) gives the same bits
+    assert torch.equal(lin.forward_unfused(pk).cpu(), want)
+
+
+def test_asym_symm_linear():
+    M, K, N = 9, 256, 48
+    g = torch.Generator().manual_seed(0)
+    a, w = _codes(M, K, 5), _codes(N, K, 6)
+    A, W = oracle.pack_i4(a), oracle.pack_i4(w)
+    sa = torch.rand((M, 1), generator=g).half() + 0.1
+    sw = (torch.rand((N, 1), generator=g) * 0.01).half()
+    za = torch.randint(-8, 8, (M, 1), generator=g).to(torch.int8)
+    lin = snn.AsymSymmLinear4bit(K, N).to(DEV)
+    lin.weight.copy_(W)
+    lin.weight_scales = sw.to(DEV)
+    lin.weight_sum = oracle.sum_i4(W).to(DEV)
+    got = lin(kernel.PackedQuantizedTensor(A.to(DEV), sa.to(DEV), za.to(DEV))).cpu()
+    acc = oracle.matmul_i4(A, W) - oracle.matmul_colrow(za, oracle.sum_i4(W).view(1, -1))
+    assert torch.equal(got, oracle.sym_dequant(acc, sa, sw))
+
+
+def test_determinism():
+    a, b = _codes(300, 4096, 1), _codes(520, 4096, 2)
+    A, B = oracle.pack_i4(a).to(DEV), oracle.pack_i4(b).to(DEV)
+    c1 = kernel.matmul_si4_si4(A, B)
+    c2 = kernel.matmul_si4_si4(A, B)
+    assert torch.equal(c1, c2)
+
+
+def test_grouped_matches_dense():
+    """Grouped GEMM == per-problem dense GEMM, incl. empty problems, skew, M=1, M=513
+    (benchmarks/test_grouped_gemm.py:76-91)."""
+    for ms, n, k, signed in [([5, 0, 17, 1], 96, 256, True), ([4096, 3, 0, 1], 64, 128, True), ([1], 40, 64, True),
+                             ([513, 7], 72, 512, False), ([0, 0], 32, 64, True)]:
+        P = len(ms)
+        a_all = _codes(sum(ms), k, 1, -8 if signed else 0, 8 if signed else 16)
+        A = oracle.pack_codes(a_all).to(DEV)
+        Bs = [oracle.pack_i4(_codes(n, k, 10 + i)) for i in range(P)]
+        B = torch.stack(Bs).to(DEV)
+        C = torch.full((sum(ms), n), -777, dtype=torch.int32, device=DEV)
+        off = torch.tensor([sum(ms[:i]) for i in range(P)], dtype=torch.int64)
+        ps = torch.tensor([[m, n, k] for m in ms], dtype=torch.int32, device=DEV)
+        ptr_a = (A.data_ptr() + off * (k // 2)).to(DEV)
+        ptr_b = (B.data_ptr() + torch.arange(P, dtype=torch.int64) * B.stride(0)).to(DEV)
+        ptr_c = (C.data_ptr() + off * (n * 4)).to(DEV)
+        ld_ab = torch.full((P,), k, dtype=torch.int64, device=DEV)
+        ld_c = torch.full((P,), n, dtype=torch.int64, device=DEV)
+        for max_k in (0, k):
+            C.fill_(-777)
+            kernel.matmul_grouped(ps, ptr_a, ptr_b, ptr_c, ld_ab, ld_ab, ld_c, signed_a=signed, max_k=max_k)
+            got = C.cpu()
+            row = 0
+            for i, m in enumerate(ms):
+                want = oracle.matmul_i4(oracle.pack_codes(a_all[row:row + m]), Bs[i], a_unsigned=not signed)
+                assert torch.equal(got[row:row + m], want)
+                row += m
+        assert _lib.device_status() == 0

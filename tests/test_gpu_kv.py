@@ -1,0 +1,120 @@
+"""int4 paged KV cache and decode attention against the oracle; cases follow
+benchmarks/test_split_decode.py:57-92 (T in {1024, 1000, 513, 256, 2048}, page 128/256)."""
+import math
+
+import pytest
+import torch
+
+import oracle
+from signrot_b200.functional import kernel
+from signrot_b200.transformers import kv_cache as kvc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _fill(B, L, Hkv, page, T, seed, hadamard=True):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn((B, T, Hkv, 128), generator=g).half()
+    v = torch.randn((B, T, Hkv, 128), generator=g).half()
+    pages = (T + 1 + page - 1) // page + 1
+    ref = oracle.PagedCacheRef(B, L, Hkv, page, pages, hadamard=hadamard)
+    return k, v, ref, pages
+
+
+@pytest.mark.parametrize("T,page,Hq,Hkv", [(1024, 128, 8, 8), (1000, 256, 8, 2), (513, 128, 32, 8), (256, 256, 4, 4),
+                                           (2048, 256, 32, 8), (1, 16, 8, 8), (17, 16, 16, 2)])
+def test_fused_append_and_decode(T, page, Hq, Hkv):
+    B, L, layer = 3, 2, 1
+    k, v, ref, pages = _fill(B, L, Hkv, page, T, T)
+    ref.append(layer, k, v)
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, L, Hkv, 128, group_size=Hq // Hkv)
+    # prefill through the cache object (layer 0 first: it advances the length)
+    cache.update(k.to(DEV), v.to(DEV), 0)
+    out = cache.update(k.to(DEV), v.to(DEV), layer)
+    assert isinstance(out, tuple)
+    indptr, indices, last = ref.specs(layer)
+    P = indptr[1].item()
+    got_data = cache.pages[: P * B, layer].cpu()
+    got_param = cache.scales[: P * B, layer].cpu()
+    # compare only written slots
+    for b in range(B):
+        for pos in (0, T // 2, T - 1):
+            pg, e = (pos // page) * B + b, pos % page
+            assert torch.equal(got_data[pg, :, :, e], ref.data[pg, layer, :, :, e])
+            assert torch.equal(got_param[pg, :, :, e], ref.param[pg, layer, :, :, e])
+    # decode one token
+    g = torch.Generator().manual_seed(5)
+    k1 = torch.randn((B, 1, Hkv, 128), generator=g).half()
+    v1 = torch.randn((B, 1, Hkv, 128), generator=g).half()
+    q = torch.randn((B, 1, Hq, 128), generator=g).half()
+    ref.append(layer, k1, v1)
+    cache.update(k1.to(DEV), v1.to(DEV), 0)
+    attend = cache.update(k1.to(DEV), v1.to(DEV), layer)
+    o = attend(q.to(DEV)).cpu().view(B, Hq, 128)
+    kf, vf = ref.dense(layer)
+    want = oracle.decode_attention_ref(q.view(B, Hq, 128), kf, vf, hadamard_q=True)
+    assert (o.float() - want).abs().max().item() <= 3e-2
+    # split-KV vs unsplit (2e-3), through the module-level entry point
+    specs = cache.refresh_specs()
+    qd = q.view(B, Hq, 128).to(DEV).contiguous()
+    o1 = torch.empty_like(qd)
+    kvc.batch_decode_i4(o1, qd, **specs, layer_idx=layer, hadamard_q=True)
+    for chunks in (2, 3, 7):
+        tmp = torch.empty((B, Hq, chunks, 132), dtype=torch.float32, device=DEV)
+        o2 = torch.empty_like(qd)
+        kvc.batch_decode_i4(o2, qd, **specs, layer_idx=layer, tmp=tmp, num_chunks=chunks, hadamard_q=True)
+        assert (o1.float() - o2.float()).abs().max().item() <= 2e-3
+
+
+def test_prequantized_init_append_roundtrip():
+    """init_kv_i4 / append_kv_i4 with codes from kv_quant_pack (the reference's unfused chain)."""
+    B, L, H, page, T = 2, 1, 4, 16, 37
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn((B, T, H, 128), generator=g).half().to(DEV)
+    v = torch.randn((B, T, H, 128), generator=g).half().to(DEV)
+    kq, kp = kernel.kv_quant_pack(k)
+    vq, vp = kernel.kv_quant_pack(v)
+    pages = (T + 1 + page - 1) // page
+    data = torch.zeros((pages * B, L, 2, H, page, 64), dtype=torch.uint8, device=DEV)
+    param = torch.zeros((pages * B, L, 2, H, page, 2), dtype=torch.float16, device=DEV)
+    def specs(n):
+        pc = (n + page - 1) // page
+        last = n % page or page
+        idx = (torch.arange(pc, dtype=torch.int32) * B).unsqueeze(0) + torch.arange(B, dtype=torch.int32).unsqueeze(1)
+        return dict(kv_indptr=(torch.arange(B + 1, dtype=torch.int32) * pc).to(DEV), kv_indices=idx.reshape(-1).to(DEV),
+                    last_page_offset=torch.full((B,), last, dtype=torch.int32, device=DEV))
+    seq = (torch.arange(B + 1, dtype=torch.int32) * T).to(DEV)
+    kvc.init_kv_i4(data, param, **specs(T), k=kq.view(-1, H, 64), v=vq.view(-1, H, 64), k_param=kp.view(-1, H, 2),
+                   v_param=vp.view(-1, H, 2), seqlen_indptr=seq, layer_idx=0)
+    k1 = torch.randn((B, 1, H, 128), generator=g).half().to(DEV)
+    k1q, k1p = kernel.kv_quant_pack(k1)
+    kvc.append_kv_i4(data, param, **specs(T + 1), k=k1q.view(B, H, 64), v=k1q.view(B, H, 64), k_param=k1p.view(B, H, 2),
+                     v_param=k1p.view(B, H, 2), layer_idx=0)
+    for b in range(B):
+        for pos in (0, 15, 16, T - 1):
+            pg, e = (pos // page) * B + b, pos % page
+            assert torch.equal(data[pg, 0, 0, :, e], kq[b, pos]) and torch.equal(data[pg, 0, 1, :, e], vq[b, pos])
+            assert torch.equal(param[pg, 0, 0, :, e], kp[b, pos]) and torch.equal(param[pg, 0, 1, :, e], vp[b, pos])
+        pg, e = (T // page) * B + b, T % page
+        assert torch.equal(data[pg, 0, 0, :, e], k1q[b, 0]) and torch.equal(param[pg, 0, 1, :, e], k1p[b, 0])
+    # the fused path writes the same bytes
+    data2, param2 = torch.zeros_like(data), torch.zeros_like(param)
+    kvc.kv_append_quant(data2, param2, **specs(T), k=k, v=v, layer_idx=0, hadamard_k=False)
+    kvc.kv_append_quant(data2, param2, **specs(T + 1), k=k1, v=k1, layer_idx=0, hadamard_k=False)
+    assert torch.equal(data2, data) and torch.equal(param2, param)
+
+
+def test_cache_reset_and_graph_friendly_specs():
+    B, page, H = 2, 16, 2
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, 64, DEV, 1, H, 128)
+    ptrs = {k: v.data_ptr() for k, v in cache.refresh_specs().items()}
+    k = torch.randn((B, 20, H, 128), device=DEV).half()
+    cache.update(k, k, 0)
+    assert cache.get_seq_length() == 20 and cache.seen_tokens == 20
+    cache.update(k[:, :1], k[:, :1], 0)
+    assert cache.get_seq_length() == 21
+    assert {k_: v.data_ptr() for k_, v in cache.refresh_specs().items()} == ptrs
+    cache.reset()
+    assert cache.get_seq_length() == 0
+    assert isinstance(cache.update(k, k, 0), tuple)

@@ -1,0 +1,141 @@
+"""Online rotation (+ sign + quantizer) against the oracle.  The rotated fp16 row may differ
+from the oracle by one fp16 ulp where two fp32 summation orders round differently; codes may
+differ only by +-1 in at most 1e-4 of the elements."""
+import pytest
+import torch
+
+import oracle
+from conftest import assert_codes_close
+from signrot_b200.functional import kernel
+from signrot_b200.functional.hadamard import get_hadK, matmul_hadU_cuda
+from signrot_b200 import nn as snn
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _x(rows, n, seed, dtype=torch.float16, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((rows, n), generator=g)
+    if outliers:
+        x[:, 3] *= 100.0
+        x[rows // 2, :] *= 30.0
+    return x.to(dtype)
+
+
+def _ulp_close(got, want, ulps=1.0):
+    g, w = got.float(), want.float()
+    tol = (w.abs() * 2 ** -10).clamp_min(2 ** -24) * ulps
+    bad = (g - w).abs() > tol
+    assert not bool(bad.any()), f"{int(bad.sum())} values differ by more than {ulps} ulp"
+    return (g != w).float().mean().item()
+
+
+@pytest.mark.parametrize("n", [32, 128, 512, 768, 1024, 4096, 8192, 14336, 2560])
+@pytest.mark.parametrize("rows", [1, 19])
+def test_hadamard_f16(n, rows):
+    x = _x(rows, n, n + rows)
+    hadK, K = get_hadK(n)
+    got = matmul_hadU_cuda(x.to(DEV), hadK, K).cpu()
+    want = oracle.rotate(x, hadK, K)
+    frac = _ulp_close(got, want)
+    assert frac < 2e-2
+
+
+@pytest.mark.parametrize("n,dtype", [(4096, torch.bfloat16), (768, torch.float32), (14336, torch.float32), (128, torch.bfloat16)])
+def test_hadamard_other_dtypes(n, dtype):
+    x = _x(5, n, n, dtype)
+    hadK, K = get_hadK(n)
+    got = matmul_hadU_cuda(x.to(DEV), hadK, K).cpu()
+    want = oracle.rotate(x, hadK, K)
+    if dtype == torch.float32:
+        assert torch.allclose(got, want, atol=1e-5 * want.abs().max().item(), rtol=1e-5)
+    else:
+        g, w = got.float(), want.float()
+        assert bool(((g - w).abs() <= w.abs() * 2 ** -7 + 1e-30).all())
+
+
+@pytest.mark.parametrize("n", [768, 4096, 14336])
+@pytest.mark.parametrize("fp32", [False, True])
+def test_online_hadamard_module_with_sign(n, fp32):
+    g = torch.Generator().manual_seed(n)
+    x = _x(9, n, 1)
+    sign = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8)
+    mod = snn.OnlineHadamard(n, force_fp32=fp32, had_adj=True).to(DEV)
+    mod.had_adj_sign = sign.to(DEV)
+    got = mod(x.to(DEV)).cpu()
+    hadK, K = get_hadK(n)
+    want = oracle.rotate(x, hadK, K, sign, fp32_mode=fp32)
+    assert got.dtype == torch.float16
+    _ulp_close(got, want)
+
+
+def test_online_hadamard_rejects_unset_sign():
+    mod = snn.OnlineHadamard(128, had_adj=True).to(DEV)
+    mod.had_adj_sign.zero_()
+    with pytest.raises(RuntimeError, match="not implemented"):
+        mod(torch.zeros(2, 128, dtype=torch.float16, device=DEV))
+
+
+@pytest.mark.parametrize("heads,dim", [(32, 128), (4, 64), (8, 16)])
+def test_hadamard_heads(heads, dim):
+    x = _x(7, heads * dim, heads)
+    got = kernel.hadamard_heads(x.to(DEV), heads).cpu()
+    _ulp_close(got, oracle.rotate_heads(x, heads))
+
+
+@pytest.mark.parametrize("M,n", [(1, 4096), (16, 4096), (256, 4096), (1, 14336), (16, 14336), (200, 14336),
+                                 (33, 768), (64, 128), (5, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rotate_quant(M, n, dtype):
+    """The fused kernel on the op-sweep input distribution (bf16 ~N(0,1), 0.1 % channels x100)."""
+    from oracle import fake_quant as fq
+    case = fq.make_linear_case(M, n, 8, seed=M)
+    x, sign = case["x"].to(dtype), case["sign"]
+    hadK, K = get_hadK(n)
+    pk, rot = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), return_rotated=True)
+    want_rot = oracle.rotate(x, hadK, K, sign, cast_in_to_f16=True, out_dtype=torch.float16)
+    _ulp_close(rot.cpu(), want_rot)
+    codes, scale = oracle.sym_quant_dynamic(want_rot)
+    # scale = rn_h(amax/7): identical unless the row maximum itself sits on an fp16 rounding boundary
+    assert (pk.scales_x.cpu() != scale).float().mean().item() <= 0.02
+    same = (pk.scales_x.cpu() == scale).view(-1)
+    assert_codes_close(oracle.unpack_i4(pk.quantized_x.cpu())[same], codes[same])
+    # self-consistency: codes are exactly the quantizer applied to the kernel's own rotated rows
+    q2, s2 = kernel.sym_quant_dynamic(rot)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+
+
+def test_rotate_quant_asym_heads_and_clip():
+    x = _x(12, 4096, 5, torch.bfloat16)
+    pk, rot = kernel.rotate_quant(x.to(DEV), heads=32, asym=True, clip_ratio=0.9, return_rotated=True)
+    want_rot = oracle.rotate_heads(x, 32, cast_in_to_f16=True)
+    _ulp_close(rot.cpu(), want_rot)
+    q2, s2, z2 = kernel.asym_quant_dynamic(rot, 0.9)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    assert torch.equal(z2.to(torch.int8), pk.zeros_x)
+
+
+def test_rotate_quant_expert_signs():
+    g = torch.Generator().manual_seed(2)
+    E, rows, n = 4, 21, 768
+    x = _x(rows, n, 9)
+    sign = (torch.randint(0, 2, (E, n), generator=g) * 2 - 1).to(torch.int8)
+    eid = torch.randint(0, E, (rows,), generator=g).to(torch.int32)
+    hadK, K = get_hadK(n)
+    pk = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), expert_ids=eid.to(DEV))
+    h = kernel.hadamard(x.to(DEV), hadK, K)
+    q2, s2 = kernel.sym_quant_dynamic_moe(h, sign.to(DEV), eid.to(DEV))
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+
+
+def test_rotation_is_orthogonal_at_full_size():
+    """Size-independent property at the benchmark size: ||H x|| = ||x|| and H(H x) = x
+    (had28 is symmetric, so the Kronecker transform is an involution as well)."""
+    for n in (4096, 14336):
+        x = _x(4096, n, 3, outliers=False).to(DEV)
+        hadK, K = get_hadK(n)
+        y = kernel.hadamard(x.float(), hadK, K)
+        assert torch.allclose(y.norm(dim=-1), x.float().norm(dim=-1), rtol=1e-4)
+        z = kernel.hadamard(y, hadK, K)
+        assert torch.allclose(z, x.float(), atol=2e-3)
