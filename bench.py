@@ -375,6 +375,47 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+def run_kernel_case(name: str):
+    """A few launches of ONE kernel on a real-size shape, for `ncu -k ... -c ...` captures
+    (device memory stays below 1 GB, every launch works on buffers larger than L2 in total)."""
+    import signrot_b200  # noqa: F401
+    from signrot_b200.functional import kernel
+    from signrot_b200.functional.hadamard import get_hadK
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    M = M_TOKENS
+    if name in ("gemm", "gemm_small"):
+        k, n = 4096, 14336
+        m = M if name == "gemm" else 16
+        c = make_linear_case(m, k, n)
+        pk = kernel.rotate_quant(c["x"].to(dev), None, 1, sign=c["sign"].to(dev))
+        w, ws = c["w_packed"].to(dev), c["w_scale"].to(dev)
+        for _ in range(5):
+            kernel.w4a4_linear(pk, w, ws)
+    elif name in ("rotate4096", "rotate14336"):
+        k = 4096 if name == "rotate4096" else 14336
+        c = make_linear_case(M, k, 8)
+        hadK, K = get_hadK(k)
+        x, sg = c["x"].to(dev), c["sign"].to(dev)
+        for _ in range(5):
+            kernel.rotate_quant(x, hadK, K, sign=sg)
+    elif name == "decode":
+        from signrot_b200.transformers import kv_cache as kvc
+        B, Hq, Hkv, T, page = 16, 32, 8, 4096, 256
+        cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 64, dev, 1, Hkv, 128, group_size=Hq // Hkv)
+        g = torch.Generator().manual_seed(0)
+        kk = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
+        cache.update(kk, kk, 0)
+        q = torch.randn((B, 1, Hq, 128), generator=g).half().to(dev)
+        for _ in range(5):
+            attend = cache.update(kk[:, :1].contiguous(), kk[:, :1].contiguous(), 0)
+            attend(q)
+    else:
+        raise SystemExit(f"unknown kernel case {name}")
+    torch.cuda.synchronize()
+    print(f"kernel case {name}: done")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,7 +423,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-case", default=None,
+                    help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | "
+                         "rotate14336 | decode")
     args = ap.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args.kernel_case)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -26,5 +26,6 @@ int launch_rotate_generic(const RotateArgs &a, cudaStream_t st);
 // Returns SR_OK when a specialised kernel took the call, SR_ERR_UNSUPPORTED when the
 // shape has none (the caller then uses the generic kernel).
 int launch_rotate_fast(const RotateArgs &a, cudaStream_t st);
+int launch_rotate_had28(const RotateArgs &a, cudaStream_t st);
 
 }  // namespace sr

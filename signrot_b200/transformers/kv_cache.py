@@ -26,12 +26,29 @@ from .._lib import ptr, require_cuda, run
 from ..functional import kernel as _kernel
 from ..functional.quantization import get_minq_maxq
 
-try:  # the cache only needs the base class to be accepted by HF model code
-    from transformers.cache_utils import Cache as _HFCache
-except Exception:  # pragma: no cover - transformers is optional for the kernels
-    class _HFCache:  # type: ignore
-        def __init__(self, *a, **k):
-            pass
+import sys as _sys
+
+
+class _PlainCache:
+    def __init__(self, *a, **k):
+        pass
+
+
+def _hf_cache_base():
+    """Hugging Face's `Cache` when the application has already imported transformers (so that
+    `isinstance(cache, Cache)` checks in HF model code pass), else a plain base class.  The
+    kernels never need transformers, and importing it here would cost seconds on every start."""
+    mod = _sys.modules.get("transformers.cache_utils")
+    if mod is None and "transformers" in _sys.modules:
+        try:
+            import importlib
+            mod = importlib.import_module("transformers.cache_utils")
+        except Exception:
+            mod = None
+    return getattr(mod, "Cache", _PlainCache) if mod is not None else _PlainCache
+
+
+_HFCache = _hf_cache_base()
 
 
 # ----------------------------------------------------------------------------- torch references
