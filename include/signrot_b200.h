@@ -75,7 +75,8 @@ int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const vo
                       int64_t max_k, void *stream);
 
 /* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
- * 2 = tcgen05 kernel.  For tests and tuning; no counterpart in the reference. */
+ * 2 = tcgen05 kernel fed by TMA-staged packed tiles, 3 = persistent tcgen05 kernel with
+ * register-path unpack.  For tests and tuning; no counterpart in the reference. */
 int sr_set_gemm_kernel(int which);
 
 /* ------------------------------------------------------------------ quantizers */

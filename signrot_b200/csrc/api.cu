@@ -19,6 +19,7 @@ int fail(int code, const char *fmt, ...) {
 
 int tc_device_status(int *out, bool clear);
 int grouped_device_status(int *out, bool clear);
+int tc2_device_status(int *out, bool clear);
 
 }  // namespace sr
 
@@ -35,7 +36,10 @@ int sr_device_status(int *status, int clear) {
     if (rc) return rc;
     rc = sr::grouped_device_status(&b, clear != 0);
     if (rc) return rc;
-    *status = a ? a : b;
+    int c = 0;
+    rc = sr::tc2_device_status(&c, clear != 0);
+    if (rc) return rc;
+    *status = a ? a : (b ? b : c);
     return SR_OK;
 }
 

@@ -39,9 +39,59 @@ struct Epilogue {
     }
 };
 
+// int32 -> fp32 without the conversion pipe: exact for |x| < 2^22 (magic-number add on the
+// integer and floating-point pipes); larger magnitudes take the ordinary conversion.
+__device__ __forceinline__ float int_to_float_fast(int x, bool small) {
+    return small ? (__int_as_float(0x4B400000 + x) - 12582912.f) : (float)x;
+}
+
+// Stores one lane's 32 consecutive accumulator columns (values still carry the factor 256).
+// `small` = every |acc >> 8| of this problem is below 2^22.
+__device__ __forceinline__ void store_acc_chunk(const Epilogue &ep, uint32_t row, uint32_t col0, const int (&v)[32],
+                                                uint32_t M, uint32_t N, bool small) {
+    if (row >= M || col0 >= N) return;
+    const bool full = (col0 + 32 <= N);
+    if (ep.mode == 0) {
+        int32_t *dst = ep.c + (size_t)row * ep.ldc + col0;
+        if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<int4 *>(dst + j) = make_int4(v[j] >> 8, v[j + 1] >> 8, v[j + 2] >> 8, v[j + 3] >> 8);
+        } else {
+            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = v[j] >> 8;
+        }
+        return;
+    }
+    __half *dst = ep.out + (size_t)row * N + col0;
+    const size_t e = ep.expert_ids ? (size_t)ep.expert_ids[row] * N : 0;
+    const __half *ws = ep.w_scale + e + col0;
+    const bool vec = full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && (reinterpret_cast<uintptr_t>(ws) & 15u) == 0 &&
+                     !ep.a_zero && !ep.bias;
+    if (vec) {
+        const float sr_ = __half2float(ep.a_scale[row]);
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            Vec16 s, o;
+            s.u = __ldg(reinterpret_cast<const uint4 *>(ws + j));
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float2 sc = __half22float2(s.h2[t]);
+                const float a = (int_to_float_fast(v[j + 2 * t] >> 8, small) * sr_) * sc.x;
+                const float b = (int_to_float_fast(v[j + 2 * t + 1] >> 8, small) * sr_) * sc.y;
+                o.h2[t] = __floats2half2_rn(a, b);
+            }
+            *reinterpret_cast<uint4 *>(dst + j) = o.u;
+        }
+    } else {
+        for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = ep.dequant(row, col0 + j, v[j] >> 8, N);
+    }
+}
+
 int launch_gemm_small(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                       const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                    const Epilogue &ep, cudaStream_t st);
+int launch_gemm_tc2(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                    const Epilogue &ep, cudaStream_t st);
 
 }  // namespace sr

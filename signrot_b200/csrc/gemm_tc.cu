@@ -138,43 +138,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Epilogue for one lane's row segment of 32 consecutive columns.
-__device__ __forceinline__ void store_chunk(const Epilogue &ep, uint32_t row, uint32_t col0, const int (&v)[32],
-                                            uint32_t M, uint32_t N) {
-    if (row >= M || col0 >= N) return;
-    const bool full = (col0 + 32 <= N);
-    if (ep.mode == 0) {
-        int32_t *dst = ep.c + (size_t)row * ep.ldc + col0;
-        if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<int4 *>(dst + j) = make_int4(v[j] >> 8, v[j + 1] >> 8, v[j + 2] >> 8, v[j + 3] >> 8);
-        } else {
-            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = v[j] >> 8;
-        }
-        return;
-    }
-    __half *dst = ep.out + (size_t)row * N + col0;
-    const size_t e = ep.expert_ids ? (size_t)ep.expert_ids[row] * N : 0;
-    const __half *ws = ep.w_scale + e + col0;
-    const bool vec = full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && (reinterpret_cast<uintptr_t>(ws) & 15u) == 0 &&
-                     !ep.a_zero && !ep.bias;
-    if (vec) {
-        const float sr_ = __half2float(ep.a_scale[row]);
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-            Vec16 s, o;
-            s.u = __ldg(reinterpret_cast<const uint4 *>(ws + j));
-#pragma unroll
-            for (int t = 0; t < 8; ++t)
-                o.h[t] = __float2half_rn(((float)(v[j + t] >> 8) * sr_) * __half2float(s.h[t]));
-            *reinterpret_cast<uint4 *>(dst + j) = o.u;
-        }
-    } else {
-        for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = ep.dequant(row, col0 + j, v[j] >> 8, N);
-    }
-}
-
 template <bool A_UNSIGNED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
@@ -195,6 +158,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t acc_full = bars + 8u * (2 * SP + 2 * SU);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool small = (A_UNSIGNED ? 120u : 64u) * (uint64_t)K < (1u << 22);
     const uint32_t n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const uint32_t num_kb = (K + BK - 1) / BK;
 
@@ -304,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int c = 0; c < BN / 32; ++c) {
                     int v[32];
                     tmem_ld32(tmem_acc + ((quarter * 32u) << 16) + (uint32_t)(c * 32), v);
-                    store_chunk(ep, row, n0 + c * 32, v, M, N);
+                    store_acc_chunk(ep, row, n0 + c * 32, v, M, N, small);
                 }
             }
         }

@@ -154,6 +154,9 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// 4-bit code -> fp32 without the conversion pipe (2^23 + n has n in its low mantissa bits).
+__device__ __forceinline__ float nib2f(uint32_t w) { return __uint_as_float(0x4B000000u | (w & 15u)) - 8388608.f; }
+
 // grid (batch, kv_heads, chunks), 128 threads.  G = q heads per KV head.  Eight lanes
 // share one cached token (16 dims each); a warp covers four tokens per step, the CTA 16.
 template <int G>
@@ -233,18 +236,26 @@ decode_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, 
         const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
         const uint32_t valid = (pi == pages_total - 1) ? last_valid : kv.page_size;
         const size_t kbase = kv.vec_index(page, 0, hk, 0), vbase = kv.vec_index(page, 1, hk, 0);
-        for (uint32_t e = slot; e < valid; e += 16) {
-            const uint2 kc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (kbase + e) * 64) + sub);
-            const uint2 vc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (vbase + e) * 64) + sub);
-            const float2 kp = __half22float2(kv.param[kbase + e]);
-            const float2 vp = __half22float2(kv.param[vbase + e]);
+        // the trip count is uniform across the warp (the shuffles below need every lane);
+        // lanes whose token slot is past the end of the page compute on zeros and skip the update
+        for (uint32_t e0 = 0; e0 < valid; e0 += 16) {
+            const uint32_t e = e0 + slot;
+            const bool live = e < valid;
+            uint2 kc = make_uint2(0, 0), vc = make_uint2(0, 0);
+            float2 kp = make_float2(0.f, 0.f), vp = make_float2(0.f, 0.f);
+            if (live) {
+                kc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (kbase + e) * 64) + sub);
+                vc = __ldg(reinterpret_cast<const uint2 *>(kv.data + (vbase + e) * 64) + sub);
+                kp = __half22float2(kv.param[kbase + e]);
+                vp = __half22float2(kv.param[vbase + e]);
+            }
             float kf[16], vf[16];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                kf[j] = (float)((kc.x >> (4 * j)) & 15u);
-                kf[8 + j] = (float)((kc.y >> (4 * j)) & 15u);
-                vf[j] = (float)((vc.x >> (4 * j)) & 15u);
-                vf[8 + j] = (float)((vc.y >> (4 * j)) & 15u);
+                kf[j] = nib2f(kc.x >> (4 * j));
+                kf[8 + j] = nib2f(kc.y >> (4 * j));
+                vf[j] = nib2f(vc.x >> (4 * j));
+                vf[8 + j] = nib2f(vc.y >> (4 * j));
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
@@ -254,16 +265,18 @@ decode_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, 
                 dot += __shfl_xor_sync(0xffffffffu, dot, 1);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 2);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-                const float x = dot * kp.x - kp.y * qsum[g];
-                const float m_new = fmaxf(m[g], x);
-                const float alpha = ex2(m[g] - m_new);
-                const float p = ex2(x - m_new);
-                m[g] = m_new;
-                d[g] = d[g] * alpha + p;
-                const float ps = p * vp.x;
-                accz[g] = accz[g] * alpha + p * vp.y;
+                if (live) {
+                    const float x = dot * kp.x - kp.y * qsum[g];
+                    const float m_new = fmaxf(m[g], x);
+                    const float alpha = ex2(m[g] - m_new);
+                    const float p = ex2(x - m_new);
+                    m[g] = m_new;
+                    d[g] = d[g] * alpha + p;
+                    const float ps = p * vp.x;
+                    accz[g] = accz[g] * alpha + p * vp.y;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[g][j] = fmaf(ps, vf[j], acc[g][j] * alpha);
+                    for (int j = 0; j < 16; ++j) acc[g][j] = fmaf(ps, vf[j], acc[g][j] * alpha);
+                }
             }
         }
     }

@@ -5,24 +5,29 @@
 // (signrot/functional/hadamard.py:81, signrot/nn/hadamard.py:39, signrot/kernels/fused.cu:68-112)
 // and touches HBM once: 2 bytes in and 0.5 bytes out per value.
 //
-// Layout.  A row is owned by 64 threads (two warps); a thread keeps 64 fp32 values.
+// Layout.  A row is owned by 64 threads (two warps); a thread keeps 64 fp32 values as 32
+// register pairs and transforms them with packed fp32 adds (add.f32x2 / sub.f32x2).
 //   phase 1: thread t loads eight 16-byte vectors, vector c at element 512*c + 8*t, so each
 //            warp-wide load covers 512 contiguous bytes.  Its 64 values span index bits
-//            {0,1,2} (inside a vector) and {9,10,11} (the vector number): a 64-point
-//            Walsh-Hadamard transform in registers takes care of those six bits.
-//   exchange: a 64 x 64 fp32 transpose through shared memory (row pitch 65 words: both the
-//            write and the read touch 32 distinct banks).
-//   phase 2: thread t' = (c, b) now holds the 64 values with index bits {3..8} varying:
-//            element 512*c + b + 8*j, j = 0..63.  Second 64-point transform in registers.
-// The sums are fp32 throughout (the butterfly order differs from any other implementation
-// only by fp32 rounding), scaled by 1/sqrt(n), rounded to fp16 once, then the sign is applied
-// and the row maximum reduced over the 64 threads.
+//            {0,1,2} (inside a vector) and {9,10,11} (the vector number): one 64-point
+//            Walsh-Hadamard transform in registers.
+//   exchange: a 64 x 64 fp32 transpose through shared memory; scalar stores (row pitch 68
+//            words), 128-bit loads, both bank-conflict free.  Inside a group of eight the
+//            values are stored in the order 0,4,1,5,2,6,3,7 so that a register pair holds
+//            values i and i+4: their 4-bit codes then drop into an output word with one
+//            shift-add each.
+//   phase 2: thread t' = (c, b) holds element 512*c + b + 8*j, j = 0..63 (index bits {3..8}):
+//            second 64-point transform.
+// Sums are fp32 throughout, scaled by 1/sqrt(n) and rounded to fp16 once (the dtype the
+// reference's transform returns); sign, row maximum and the code decision run on packed fp16
+// pairs.  No instruction of the inner loops uses the conversion unit: roundings are packed
+// cvt.rn.f16x2.f32, fp16->fp32 is an exact widening, and round-to-nearest-even of the quotient is
+// the fp16 addition of 1536 (whose low mantissa bits then hold the integer).
 //   output: thread (c, b) owns every 8th value of the 512-value block c, so the eight lanes
-//            b = 0..7 together hold whole output words.  Each lane packs its codes eight per
-//            register, an 8 x 8 nibble transpose across the eight lanes (three shuffle rounds
-//            per register) turns them into output words, and each store instruction writes
-//            32 contiguous bytes per block.
-// CTAs are persistent over rows, so the 64 sign bits a thread needs stay in two registers.
+//            b = 0..7 together hold whole output words: an 8 x 8 nibble transpose across those
+//            lanes (three shuffle rounds per register), then every store instruction writes 32
+//            contiguous bytes per block.
+// CTAs are persistent over rows; a thread's sign masks live in its own shared-memory row.
 #include "rotate.cuh"
 #include <cfloat>
 #include <type_traits>
@@ -32,17 +37,55 @@ namespace sr {
 namespace {
 
 constexpr int ROWS_PER_CTA = 4;      // 256 threads
-constexpr int PITCH = 65;            // words per transposed row
+constexpr int PITCH = 68;            // words per transposed row (16-byte aligned, bank-conflict free)
+constexpr int SPITCH = 33;           // words per thread in the sign-mask table
+constexpr int XCH_WORDS = 64 * PITCH;
+constexpr int SGN_WORDS = 64 * SPITCH;
+constexpr size_t SMEM_BYTES = (size_t)ROWS_PER_CTA * (XCH_WORDS + SGN_WORDS) * 4;
 
-__device__ __forceinline__ void fwht64(float (&v)[64]) {
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+    u64 r;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+    u64 r;
+    asm("sub.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+    u64 r;
+    asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// 64-point Walsh-Hadamard transform of 32 register pairs: one stage inside the pairs, five
+// stages between pairs.  Which index bit the in-pair stage stands for is the caller's business.
+__device__ __forceinline__ void fwht64_pairs(u64 (&v)[32]) {
 #pragma unroll
-    for (int h = 1; h < 64; h <<= 1) {
+    for (int a = 0; a < 32; ++a) {
+        float lo, hi;
+        unpack2(v[a], lo, hi);
+        v[a] = pack2(lo + hi, lo - hi);
+    }
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            if ((i & h) == 0) {
-                const float a = v[i], b = v[i + h];
-                v[i] = a + b;
-                v[i + h] = a - b;
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int a = 0; a < 32; ++a) {
+            if ((a & h) == 0) {
+                const u64 x = v[a], y = v[a + h];
+                v[a] = add2(x, y);
+                v[a + h] = sub2(x, y);
             }
         }
     }
@@ -52,6 +95,9 @@ __device__ __forceinline__ void team_sync(int team) {
     asm volatile("bar.sync %0, 64;" ::"r"(team + 1) : "memory");
 }
 
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t w) { return *reinterpret_cast<__half2 *>(&w); }
+
 template <typename InT, bool ASYM>
 __global__ void __launch_bounds__(ROWS_PER_CTA * 64, 2)
 rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ sign,
@@ -59,76 +105,102 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
                          uint8_t *__restrict__ q, __half *__restrict__ q_scale, __half *__restrict__ q_zero,
                          __half *__restrict__ rotated) {
     constexpr int N = 4096;
-    extern __shared__ float xch[];   // [ROWS_PER_CTA][64 * PITCH]
+    extern __shared__ __align__(16) float smem_f[];
     __shared__ float red[ROWS_PER_CTA][2][2];
 
     const int tid = threadIdx.x;
     const int team = tid >> 6;        // row slot inside the CTA
     const int t = tid & 63;           // thread inside the team
     const int lane = tid & 31;
-    float *buf = xch + team * (64 * PITCH);
-    // phase-2 identity: block c, offset b
+    float *buf = smem_f + team * XCH_WORDS;
+    uint32_t *sgn = reinterpret_cast<uint32_t *>(smem_f + ROWS_PER_CTA * XCH_WORDS) + team * SGN_WORDS + t * SPITCH;
+    // phase-2 identity: block c2, offset b2; slot a = 4g + m holds j = 8g + m (low) and 8g + m + 4 (high)
     const int c2 = t >> 3, b2 = t & 7;
+    // where this thread's phase-1 values go inside a transposed row: position of j' = t
+    const int wpos = (t & ~7) | (((t & 3) << 1) | ((t >> 2) & 1));
 
-    // sign bits of this thread's phase-2 elements (bit j <-> element 512*c2 + b2 + 8*j)
-    uint64_t neg_static = 0;
     const bool per_row_sign = sign != nullptr && expert_ids != nullptr;
-    if (sign != nullptr && !per_row_sign) {
-#pragma unroll 8
-        for (int j = 0; j < 64; ++j)
-            if (sign[512 * c2 + b2 + 8 * j] < 0) neg_static |= (1ull << j);
-    }
+    auto fill_sign = [&](const int8_t *sg) {
+#pragma unroll 4
+        for (int a = 0; a < 32; ++a) {
+            const int j = 8 * (a >> 2) + (a & 3);
+            uint32_t m = 0;
+            if (sg != nullptr) {
+                if (sg[512 * c2 + b2 + 8 * j] < 0) m |= 0x00008000u;
+                if (sg[512 * c2 + b2 + 8 * (j + 4)] < 0) m |= 0x80000000u;
+            }
+            sgn[a] = m;
+        }
+    };
+    if (!per_row_sign) fill_sign(sign);  // thread-private rows: no synchronisation needed
+
+    const __half2 magic = __floats2half2_rn(1536.f, 1536.f);
+    const u64 scale2 = pack2(scale, scale);
 
     for (uint32_t row = blockIdx.x * ROWS_PER_CTA + team; row < rows; row += gridDim.x * ROWS_PER_CTA) {
         // ---- phase 1: load + 64-point transform over bits {0,1,2,9,10,11}
-        float v[64];
+        u64 v[32];
         const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * N);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             Vec16 ld;
             ld.u = __ldg(xr + c * 64 + t);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (sizeof(InT) == 2 && std::is_same<InT, __half>::value)
-                    v[c * 8 + j] = __half2float(ld.h[j]);
-                else
-                    v[c * 8 + j] = __half2float(__float2half_rn(__bfloat162float(ld.b[j])));  // x.to(float16)
+            for (int p = 0; p < 4; ++p) {
+                float2 f;
+                if (std::is_same<InT, __half>::value) {
+                    f = __half22float2(ld.h2[p]);
+                } else {
+                    // bf16 -> fp32 is a shift; x.to(float16) is one packed rounding; widening is exact
+                    const float a = __uint_as_float(ld.w[p] << 16), b = __uint_as_float(ld.w[p] & 0xFFFF0000u);
+                    f = __half22float2(__floats2half2_rn(a, b));
+                }
+                v[c * 4 + p] = pack2(f.x, f.y);
             }
         }
-        fwht64(v);
-        // ---- exchange: buf[t][j] -> buf[j'][t']
+        fwht64_pairs(v);
+        // ---- exchange: value j of thread t goes to row j, position wpos
 #pragma unroll
-        for (int j = 0; j < 64; ++j) buf[t * PITCH + j] = v[j];
+        for (int a = 0; a < 32; ++a) {
+            float lo, hi;
+            unpack2(v[a], lo, hi);
+            buf[(2 * a) * PITCH + wpos] = lo;
+            buf[(2 * a + 1) * PITCH + wpos] = hi;
+        }
         team_sync(team);
+        {
+            const uint4 *rowp = reinterpret_cast<const uint4 *>(buf + t * PITCH);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) v[j] = buf[j * PITCH + t];
-        // ---- phase 2: bits {3..8}
-        fwht64(v);
-
-        uint64_t neg = neg_static;
-        if (per_row_sign) {
-            const int8_t *sg = sign + (size_t)expert_ids[row] * N;
-            neg = 0;
-#pragma unroll 8
-            for (int j = 0; j < 64; ++j)
-                if (sg[512 * c2 + b2 + 8 * j] < 0) neg |= (1ull << j);
-        }
-        // scale, round to fp16 (the dtype the reference's transform returns), sign, range
-        __half hv[64];
-        float vmax = ASYM ? -FLT_MAX : 0.f, vmin = FLT_MAX;
-#pragma unroll
-        for (int j = 0; j < 64; ++j) {
-            __half h = __float2half_rn(v[j] * scale);
-            if ((neg >> j) & 1ull) h = __hneg(h);
-            hv[j] = h;
-            const float f = __half2float(h);
-            if (ASYM) {
-                vmax = fmaxf(vmax, f);
-                vmin = fminf(vmin, f);
-            } else {
-                vmax = fmaxf(vmax, fabsf(f));
+            for (int m = 0; m < 16; ++m) {
+                const uint4 w = rowp[m];  // positions 4m..4m+3 hold (j, j+4), (j+1, j+5) of group m/2
+                v[2 * m] = ((u64)w.y << 32) | w.x;
+                v[2 * m + 1] = ((u64)w.w << 32) | w.z;
             }
         }
+        // ---- phase 2: bits {3..8}
+        fwht64_pairs(v);
+
+        if (per_row_sign) fill_sign(sign + (size_t)expert_ids[row] * N);
+
+        // scale, one rounding to fp16, sign, range
+        __half2 hv[32];
+        __half2 hmaxv = __floats2half2_rn(ASYM ? -65504.f : 0.f, ASYM ? -65504.f : 0.f);
+        __half2 hminv = __floats2half2_rn(65504.f, 65504.f);
+#pragma unroll
+        for (int a = 0; a < 32; ++a) {
+            float lo, hi;
+            unpack2(mul2(v[a], scale2), lo, hi);
+            const __half2 h = bits_h2(h2_bits(__floats2half2_rn(lo, hi)) ^ sgn[a]);
+            hv[a] = h;
+            if (ASYM) {
+                hmaxv = __hmax2(hmaxv, h);
+                hminv = __hmin2(hminv, h);
+            } else {
+                hmaxv = __hmax2(hmaxv, __habs2(h));
+            }
+        }
+        float vmax = fmaxf(__low2float(hmaxv), __high2float(hmaxv));
+        float vmin = fminf(__low2float(hminv), __high2float(hminv));
         vmax = warp_max(vmax);
         if (ASYM) vmin = warp_min(vmin);
         if (lane == 0) {
@@ -140,12 +212,15 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
         vmin = fminf(red[team][0][1], red[team][1][1]);
 
         float rcp;
-        int zero_i = 0;
+        uint32_t zero_u = 0;
+        __half2 lo_c, hi_c;
         if (!ASYM) {
             __half s = __float2half(vmax / 7.f);
             if (clip != 1.f) s = __float2half(__half2float(s) * clip);
             if (t == 0) q_scale[row] = s;
             rcp = rcp_approx_ftz(__half2float(s));
+            lo_c = __floats2half2_rn(-8.f, -8.f);
+            hi_c = __floats2half2_rn(7.f, 7.f);
         } else {
             __half hmin = __float2half(vmin), hmax = __float2half(vmax);
             if (clip != 1.f) {
@@ -160,25 +235,43 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
                 q_scale[row] = s;
                 q_zero[row] = zero;
             }
-            zero_i = __half2int_rn(zero);
+            const int zi = __half2int_rn(zero);
+            zero_u = (uint32_t)(zi & 15) * 0x00010001u;  // only the code's low nibble matters
+            // clamp(rint(v) + z, 0, 15) = rint(clamp(v, -z, 15 - z)) + z for an integer z
+            lo_c = __floats2half2_rn(-(float)zi, -(float)zi);
+            hi_c = __floats2half2_rn(15.f - (float)zi, 15.f - (float)zi);
             rcp = rcp_approx_ftz(__half2float(s));
         }
+        // a zero scale gives rcp = inf and 0 * inf = NaN, which the reference turns into code 0;
+        // a huge finite factor gives the same codes (x != 0 still saturates) without the NaN
+        rcp = fminf(rcp, 3.0e38f);
+        const u64 rcp2 = pack2(rcp, rcp);
 
         if (rotated != nullptr) {
             __half *orow = rotated + (size_t)row * N + 512 * c2 + b2;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) orow[8 * j] = hv[j];
+            for (int a = 0; a < 32; ++a) {
+                const int j = 8 * (a >> 2) + (a & 3);
+                orow[8 * j] = __low2half(hv[a]);
+                orow[8 * (j + 4)] = __high2half(hv[a]);
+            }
         }
 
-        // ---- codes, eight per register: P[g] nibble i = code of j = 8g + i
+        // ---- codes: P[g] nibble i = code of j = 8g + i; slot 4g + m carries nibbles m and m + 4
         uint32_t P[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             uint32_t w = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int code = ASYM ? asym_code(hv[g * 8 + i], rcp, zero_i, 0, 15) : sym_code(hv[g * 8 + i], rcp);
-                w |= (uint32_t)(code & 15) << (4 * i);
+            for (int m = 0; m < 4; ++m) {
+                const float2 f = __half22float2(hv[4 * g + m]);
+                float lo, hi;
+                unpack2(mul2(pack2(f.x, f.y), rcp2), lo, hi);
+                __half2 qh = __floats2half2_rn(lo, hi);  // rn_h(x * rcp): the quotient __hdiv returns
+                qh = __hmin2(__hmax2(qh, lo_c), hi_c);
+                // fp16 addition of 1536 rounds to the nearest even integer; its low mantissa bits are the code
+                const uint32_t r = ((h2_bits(__hadd2(qh, magic)) & 0x000F000Fu) + zero_u) & 0x000F000Fu;
+                w += r << (4 * m);
             }
             P[g] = w;
         }
@@ -186,12 +279,12 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
         // nibble b, the code lane b had at position i (i.e. output word j = 8g + i)
 #pragma unroll
         for (int k = 4; k >= 1; k >>= 1) {
-            const uint32_t m = k == 4 ? 0xFFFF0000u : (k == 2 ? 0xFF00FF00u : 0xF0F0F0F0u);
+            const uint32_t msk = k == 4 ? 0xFFFF0000u : (k == 2 ? 0xFF00FF00u : 0xF0F0F0F0u);
             const bool upper = (b2 & k) != 0;
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
                 const uint32_t r = __shfl_xor_sync(0xffffffffu, P[g], k);
-                P[g] = upper ? ((P[g] & m) | ((r >> (4 * k)) & ~m)) : ((P[g] & ~m) | ((r << (4 * k)) & m));
+                P[g] = upper ? ((P[g] & msk) | ((r >> (4 * k)) & ~msk)) : ((P[g] & ~msk) | ((r << (4 * k)) & msk));
             }
         }
         uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (N / 2)) + c2 * 64 + b2;
@@ -215,15 +308,15 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
         if (sm_count <= 0) sm_count = 148;
     }
     const uint32_t ctas_needed = cdiv<uint32_t>(a.rows, ROWS_PER_CTA);
-    const uint32_t grid = ctas_needed < (uint32_t)(sm_count * 3) ? ctas_needed : (uint32_t)(sm_count * 3);
-    constexpr size_t smem = (size_t)ROWS_PER_CTA * 64 * PITCH * sizeof(float);
+    const uint32_t grid = ctas_needed < (uint32_t)(sm_count * 2) ? ctas_needed : (uint32_t)(sm_count * 2);
 #define SR_RQ(T, ASYM)                                                                                     \
     do {                                                                                                   \
         auto kfn = rotate_quant_4096_kernel<T, ASYM>;                                                      \
-        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES); \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));         \
-        kfn<<<grid, ROWS_PER_CTA * 64, smem, st>>>((const T *)a.x, a.sign, a.expert_ids, a.rows, a.scale,   \
-                                                   a.clip, a.q, a.q_scale, a.q_zero, (__half *)a.out);     \
+        kfn<<<grid, ROWS_PER_CTA * 64, SMEM_BYTES, st>>>((const T *)a.x, a.sign, a.expert_ids, a.rows,      \
+                                                         a.scale, a.clip, a.q, a.q_scale, a.q_zero,        \
+                                                         (__half *)a.out);                                 \
     } while (0)
     if (a.in_dtype == SR_F16) {
         if (a.asym) SR_RQ(__half, true);

@@ -125,9 +125,17 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                 Vec16 ld;
                 ld.u = __ldg(xr + c * 16);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (std::is_same<InT, __half>::value) v[c * 8 + j] = __half2float(ld.h[j]);
-                    else v[c * 8 + j] = __half2float(__float2half_rn(__bfloat162float(ld.b[j])));
+                for (int p = 0; p < 4; ++p) {
+                    float2 f;
+                    if (std::is_same<InT, __half>::value) {
+                        f = __half22float2(ld.h2[p]);
+                    } else {
+                        // bf16 -> fp32 is a shift; x.to(float16) is one packed rounding; widening is exact
+                        const float lo = __uint_as_float(ld.w[p] << 16), hi = __uint_as_float(ld.w[p] & 0xFFFF0000u);
+                        f = __half22float2(__floats2half2_rn(lo, hi));
+                    }
+                    v[c * 8 + 2 * p] = f.x;
+                    v[c * 8 + 2 * p + 1] = f.y;
                 }
             }
         }
@@ -150,7 +158,12 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
             for (int r = 0; r < 2; ++r) {
                 const int c = (u >> 3) + 2 * r, b = u & 7;
 #pragma unroll
-                for (int uu = 0; uu < 16; ++uu) zr[zcol(c * 128 + uu * 8 + b)] = __float2half_rn(v[r * 16 + uu] * scale);
+                for (int uu = 0; uu < 16; uu += 2) {
+                    // packed rounding (keeps the conversion unit out of the loop)
+                    const __half2 h = __floats2half2_rn(v[r * 16 + uu] * scale, v[r * 16 + uu + 1] * scale);
+                    zr[zcol(c * 128 + uu * 8 + b)] = __low2half(h);
+                    zr[zcol(c * 128 + (uu + 1) * 8 + b)] = __high2half(h);
+                }
             }
             // rows 28..31 are the zero padding of the k dimension
             if (tid < 4 * PZ / 8) reinterpret_cast<uint4 *>(zbuf + KH * PZ)[tid] = make_uint4(0, 0, 0, 0);
@@ -161,7 +174,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
         uint64_t neg = neg_static;
         if (per_row_sign) neg = load_sign(sign + (size_t)expert_ids[row] * N);
         __half2 y[5][2][2];  // [tile][mt][half: rows g / g+8] = columns (2qd, 2qd+1)
-        float amax = 0.f;
+        __half2 amax2 = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
         for (int ti = 0; ti < 5; ++ti) {
             if (ti < n_tiles) {
@@ -194,12 +207,11 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                     hi = *reinterpret_cast<__half2 *>(&hw_);
                     y[ti][mt][0] = lo;
                     y[ti][mt][1] = hi;
-                    const float2 fl = __half22float2(lo), fh = __half22float2(hi);
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(fl.x), fabsf(fl.y)), fmaxf(fabsf(fh.x), fabsf(fh.y))));
+                    amax2 = __hmax2(amax2, __hmax2(__habs2(lo), __habs2(hi)));
                 }
             }
         }
-        amax = warp_max(amax);
+        float amax = warp_max(fmaxf(__low2float(amax2), __high2float(amax2)));
         if (lane == 0) red[warp] = amax;
         __syncthreads();
         amax = red[0];
@@ -208,7 +220,11 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
         __half s = __float2half(amax / 7.f);
         if (clip != 1.f) s = __float2half(__half2float(s) * clip);
         if (tid == 0) q_scale[row] = s;
-        const float rcp = rcp_approx_ftz(__half2float(s));
+        // a zero scale would give 0 * inf = NaN (code 0 in the reference): a huge finite factor
+        // yields the same codes without the NaN
+        const float rcp = fminf(rcp_approx_ftz(__half2float(s)), 3.0e38f);
+        const __half2 lo_c = __floats2half2_rn(-8.f, -8.f), hi_c = __floats2half2_rn(7.f, 7.f);
+        const __half2 magic = __floats2half2_rn(1536.f, 1536.f);
 
         // ---- 4. codes -> staging bytes -> one 16-byte store per thread
 #pragma unroll
@@ -222,8 +238,13 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                         const int kp = 16 * mt + g + 8 * hh;
                         if (kp < KH) {
                             const __half2 p = y[ti][mt][hh];
-                            const int lo = sym_code(p.x, rcp), hi = sym_code(p.y, rcp);
-                            obuf[kp * OUTP + 4 * nt + qd] = (uint8_t)((lo & 15) | ((hi & 15) << 4));
+                            // rn_h(x * rcp), clamp, round to nearest even by the fp16 addition of 1536
+                            const float2 f = __half22float2(p);
+                            __half2 qh = __floats2half2_rn(f.x * rcp, f.y * rcp);
+                            qh = __hmin2(__hmax2(qh, lo_c), hi_c);
+                            qh = __hadd2(qh, magic);
+                            const uint32_t r = *reinterpret_cast<uint32_t *>(&qh) & 0x000F000Fu;
+                            obuf[kp * OUTP + 4 * nt + qd] = (uint8_t)(r | (r >> 12));
                             if (rotated != nullptr)
                                 *reinterpret_cast<__half2 *>(rotated + (size_t)row * N + kp * SEG + 8 * nt + 2 * qd) = p;
                         }

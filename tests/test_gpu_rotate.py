@@ -24,8 +24,10 @@ def _x(rows, n, seed, dtype=torch.float16, outliers=True):
 
 
 def _ulp_close(got, want, ulps=1.0):
+    """One fp16 ulp of the value, or (for outputs that are tiny next to the row's largest ones)
+    the fp32 rounding noise of a different summation order: 2^-17 of the row maximum."""
     g, w = got.float(), want.float()
-    tol = (w.abs() * 2 ** -10).clamp_min(2 ** -24) * ulps
+    tol = (w.abs() * 2 ** -10).clamp_min(2 ** -24) * ulps + w.abs().amax(dim=-1, keepdim=True) * 2 ** -17
     bad = (g - w).abs() > tol
     assert not bool(bad.any()), f"{int(bad.sum())} values differ by more than {ulps} ulp"
     return (g != w).float().mean().item()
