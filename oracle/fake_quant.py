@@ -229,7 +229,8 @@ def _rope(x, cos, sin):
     return x * cos.unsqueeze(2) + rot * sin.unsqueeze(2)
 
 
-def decoder_layer_fake_quant(layer: dict, mode: str = "fake") -> torch.Tensor:
+def decoder_layer_fake_quant(layer: dict, mode: str = "fake", attn_fp32: bool = False,
+                             trace: dict | None = None) -> torch.Tensor:
     """Forward of the layer on layer['x'] with every linear fake-quantized (mode 'fake') or run
     through the integer path (mode 'real').  Derives the down_proj sign on first use
     (quant_utils.py:358-368).  Returns the layer output [1, T, hidden] in the model dtype."""
@@ -237,23 +238,29 @@ def decoder_layer_fake_quant(layer: dict, mode: str = "fake") -> torch.Tensor:
     dt = x.dtype
     Hh, Hk, D = layer["heads"], layer["kv_heads"], layer["head_dim"]
     T = x.shape[1]
-    run = (lambda lin, t: lin.fake(t)) if mode == "fake" else (lambda lin, t: lin.real(t))
+    def run(lin_name, t):
+        lin = layer[lin_name]
+        out = lin.fake(t) if mode == "fake" else lin.real(t)
+        if trace is not None:
+            trace[lin_name] = (t, out)
+        return out
     def norm(t):
         tf = t.float()
         return (tf * torch.rsqrt(tf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(dt)
     h = norm(x)
-    q = run(layer["q"], h).view(1, T, Hh, D)
-    k = run(layer["k"], h).view(1, T, Hk, D)
-    v = run(layer["v"], h).view(1, T, Hk, D)
+    q = run("q", h).view(1, T, Hh, D)
+    k = run("k", h).view(1, T, Hk, D)
+    v = run("v", h).view(1, T, Hk, D)
     cos, sin = _rope_tables(T, D, dt)
     q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+    adt = torch.float32 if attn_fp32 else dt  # prefill attention is dense and outside the path
     attn = torch.nn.functional.scaled_dot_product_attention(
-        q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(Hh // Hk, dim=1),
-        v.transpose(1, 2).repeat_interleave(Hh // Hk, dim=1), is_causal=True)
+        q.transpose(1, 2).to(adt), k.transpose(1, 2).repeat_interleave(Hh // Hk, dim=1).to(adt),
+        v.transpose(1, 2).repeat_interleave(Hh // Hk, dim=1).to(adt), is_causal=True)
     attn = attn.transpose(1, 2).reshape(1, T, Hh * D).to(dt)
-    x1 = x + run(layer["o"], attn)
+    x1 = x + run("o", attn)
     h2 = norm(x1)
-    g, u = run(layer["gate"], h2), run(layer["up"], h2)
+    g, u = run("gate", h2), run("up", h2)
     m = (torch.nn.functional.silu(g) * u).to(dt)
     if "down" not in layer:
         rot = layer["down_rot"]
@@ -261,4 +268,4 @@ def decoder_layer_fake_quant(layer: dict, mode: str = "fake") -> torch.Tensor:
         sign = derive_sign(m_rot)
         layer["down_sign"] = sign
         layer["down"] = FakeLinear(layer["down_W"], rot=rot, sign=sign)
-    return x1 + run(layer["down"], m)
+    return x1 + run("down", m)

@@ -37,7 +37,7 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     if (small)
         return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                  as_stream(stream));
-    if (f == 3)
+    if (f == 3 || f == 0)
         return launch_gemm_tc2((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
     return launch_gemm_tc((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
 }

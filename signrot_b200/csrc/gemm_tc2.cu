@@ -16,10 +16,11 @@
 //                tcgen05.mma from one lane; tcgen05.commit releases ring stages / publishes tiles
 //   warps 1..4   epilogue: tcgen05.ld of the finished accumulator while the next tile's MMAs
 //                run into the other one; exact shift by 8, dequant, fp16/int32 stores
-//   warps 5..12  unpack (256 threads, six 16-byte packed chunks each per k-block)
+//   warps 5..    unpack (512 threads by default: three 16-byte packed chunks each per k-block)
 // Every mbarrier wait is bounded by a cycle budget (abort flag + device status word).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
+#include <cstdlib>
 
 namespace sr {
 namespace tc2 {
@@ -29,9 +30,6 @@ constexpr int SU = 4;                    // int8 ring depth
 constexpr int UN_A = BM * BK;            // 16 KB
 constexpr int UN_B = BN * BK;            // 32 KB
 constexpr int STAGE = UN_A + UN_B;       // 48 KB
-constexpr int NUM_UNPACK = 256;
-constexpr int THREADS = 32 + 128 + NUM_UNPACK;  // 416
-constexpr int CHUNKS = (BM + BN) * 4 / NUM_UNPACK;  // 6 per thread per k-block
 constexpr int PF = 2;                    // k-blocks prefetched into registers
 constexpr long long WAIT_BUDGET = 1500000000ll;
 constexpr int SMEM_BYTES = SU * STAGE + 256 + 1024;
@@ -107,8 +105,10 @@ struct Cursor {
     uint32_t tile, kb;  // tile index in the global tile list, k-block inside it
 };
 
-template <bool A_UNSIGNED>
-__global__ void __launch_bounds__(THREADS, 1)
+// NUM_UNPACK = number of unpack threads (256 or 512): more warps hide more of the L2 latency and
+// of the dependent-issue latency of the expand/store sequence.
+template <bool A_UNSIGNED, int NUM_UNPACK>
+__global__ void __launch_bounds__(160 + NUM_UNPACK, 1)
 gemm_tc2_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
                 Epilogue ep) {
     extern __shared__ uint8_t smem_raw[];
@@ -124,6 +124,7 @@ gemm_tc2_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, ui
     auto acc_full = [&](int b) { return bars + 8u * (2 * SU + b); };
     auto acc_empty = [&](int b) { return bars + 8u * (2 * SU + 2 + b); };
 
+    constexpr int CHUNKS = (BM + BN) * 4 / NUM_UNPACK;  // packed 16-byte chunks per thread per k-block
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool small = (A_UNSIGNED ? 120u : 64u) * (uint64_t)K < (1u << 22);
     const uint32_t tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
@@ -217,23 +218,33 @@ gemm_tc2_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, ui
             uint4 pf[PF][CHUNKS];
             Cursor ld = {blockIdx.x, 0};
             uint32_t issued = 0;
-            auto issue = [&](uint4 (&dst)[CHUNKS]) {
-                const uint32_t m0 = (ld.tile / tiles_n) * BM, n0 = (ld.tile % tiles_n) * BN;
-                const uint32_t colb = ld.kb * (BK / 2);
+            // per-tile row addresses (recomputed only when the load cursor enters a new tile)
+            const uint8_t *rowp[CHUNKS];
+            uint32_t colq[CHUNKS];
+            auto set_tile = [&](uint32_t tile) {
+                const uint32_t m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
 #pragma unroll
                 for (int i = 0; i < CHUNKS; ++i) {
                     const int id = i * NUM_UNPACK + t;
                     const bool is_a = id < BM * 4;
                     const int cid = is_a ? id : id - BM * 4;
                     const uint32_t r = (is_a ? m0 : n0) + (cid >> 2);
-                    const uint32_t cb = colb + (cid & 3) * 16;
-                    const bool live = r < (is_a ? M : N) && cb < kp;
+                    colq[i] = (cid & 3) * 16;
+                    rowp[i] = (r < (is_a ? M : N)) ? (is_a ? A : B) + (size_t)r * kp + colq[i] : nullptr;
+                }
+            };
+            set_tile(ld.tile);
+            auto issue = [&](uint4 (&dst)[CHUNKS]) {
+                const uint32_t colb = ld.kb * (BK / 2);
+#pragma unroll
+                for (int i = 0; i < CHUNKS; ++i) {
                     dst[i] = make_uint4(0, 0, 0, 0);
-                    if (live) dst[i] = __ldg(reinterpret_cast<const uint4 *>((is_a ? A : B) + (size_t)r * kp + cb));
+                    if (rowp[i] != nullptr && colb + colq[i] < kp) dst[i] = __ldg(reinterpret_cast<const uint4 *>(rowp[i] + colb));
                 }
                 if (++ld.kb == num_kb) {
                     ld.kb = 0;
                     ld.tile += gridDim.x;
+                    if (ld.tile < num_tiles) set_tile(ld.tile);
                 }
                 ++issued;
             };
@@ -310,10 +321,16 @@ int launch_gemm_tc2(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, in
     }
     const int64_t tiles = cdiv<int64_t>(N, BN) * cdiv<int64_t>(M, BM);
     const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
-    auto kfn = a_unsigned ? gemm_tc2_kernel<true> : gemm_tc2_kernel<false>;
+    static int unpack_threads = 0;
+    if (unpack_threads == 0) {
+        const char *env = getenv("SIGNROT_B200_TC2_UNPACK");  // tuning knob: 256 or 512 unpack threads
+        unpack_threads = (env && atoi(env) == 256) ? 256 : 512;
+    }
+    auto kfn = unpack_threads == 256 ? (a_unsigned ? gemm_tc2_kernel<true, 256> : gemm_tc2_kernel<false, 256>)
+                                     : (a_unsigned ? gemm_tc2_kernel<true, 512> : gemm_tc2_kernel<false, 512>);
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<grid, THREADS, SMEM_BYTES, st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep);
+    kfn<<<grid, 160 + unpack_threads, SMEM_BYTES, st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep);
     return check_launch("gemm_tc2");
 }
 

@@ -28,4 +28,54 @@ int launch_rotate_generic(const RotateArgs &a, cudaStream_t st);
 int launch_rotate_fast(const RotateArgs &a, cudaStream_t st);
 int launch_rotate_had28(const RotateArgs &a, cudaStream_t st);
 
+// ---- packed fp32 arithmetic on register pairs (add.f32x2 / sub.f32x2 / mul.f32x2, sm_100)
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+    u64 r;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+    u64 r;
+    asm("sub.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+    u64 r;
+    asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// Walsh-Hadamard transform of 2*NP values held as NP register pairs: one stage inside the
+// pairs, then stages between pairs at distances 1 .. HMAX/2 (HMAX = NP for a full transform).
+template <int NP, int HMAX>
+__device__ __forceinline__ void fwht_pairs(u64 (&v)[NP]) {
+#pragma unroll
+    for (int a = 0; a < NP; ++a) {
+        float lo, hi;
+        unpack2(v[a], lo, hi);
+        v[a] = pack2(lo + hi, lo - hi);
+    }
+#pragma unroll
+    for (int h = 1; h < HMAX; h <<= 1) {
+#pragma unroll
+        for (int a = 0; a < NP; ++a) {
+            if ((a & h) == 0) {
+                const u64 x = v[a], y = v[a + h];
+                v[a] = add2(x, y);
+                v[a + h] = sub2(x, y);
+            }
+        }
+    }
+}
+
 }  // namespace sr

@@ -43,54 +43,6 @@ constexpr int XCH_WORDS = 64 * PITCH;
 constexpr int SGN_WORDS = 64 * SPITCH;
 constexpr size_t SMEM_BYTES = (size_t)ROWS_PER_CTA * (XCH_WORDS + SGN_WORDS) * 4;
 
-typedef unsigned long long u64;
-
-__device__ __forceinline__ u64 pack2(float lo, float hi) {
-    u64 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(u64 v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ u64 add2(u64 a, u64 b) {
-    u64 r;
-    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
-    u64 r;
-    asm("sub.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
-    u64 r;
-    asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-
-// 64-point Walsh-Hadamard transform of 32 register pairs: one stage inside the pairs, five
-// stages between pairs.  Which index bit the in-pair stage stands for is the caller's business.
-__device__ __forceinline__ void fwht64_pairs(u64 (&v)[32]) {
-#pragma unroll
-    for (int a = 0; a < 32; ++a) {
-        float lo, hi;
-        unpack2(v[a], lo, hi);
-        v[a] = pack2(lo + hi, lo - hi);
-    }
-#pragma unroll
-    for (int h = 1; h < 32; h <<= 1) {
-#pragma unroll
-        for (int a = 0; a < 32; ++a) {
-            if ((a & h) == 0) {
-                const u64 x = v[a], y = v[a + h];
-                v[a] = add2(x, y);
-                v[a + h] = sub2(x, y);
-            }
-        }
-    }
-}
-
 __device__ __forceinline__ void team_sync(int team) {
     asm volatile("bar.sync %0, 64;" ::"r"(team + 1) : "memory");
 }
@@ -158,7 +110,7 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
                 v[c * 4 + p] = pack2(f.x, f.y);
             }
         }
-        fwht64_pairs(v);
+        fwht_pairs<32, 32>(v);
         // ---- exchange: value j of thread t goes to row j, position wpos
 #pragma unroll
         for (int a = 0; a < 32; ++a) {
@@ -178,7 +130,7 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
             }
         }
         // ---- phase 2: bits {3..8}
-        fwht64_pairs(v);
+        fwht_pairs<32, 32>(v);
 
         if (per_row_sign) fill_sign(sign + (size_t)expert_ids[row] * N);
 

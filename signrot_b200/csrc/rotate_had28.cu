@@ -37,30 +37,6 @@ constexpr int Z_BYTES = 32 * PZ * 2;
 
 __device__ __forceinline__ int zcol(int j) { return j + 16 * (j >> 7); }
 
-__device__ __forceinline__ void fwht32(float (&v)[32]) {
-#pragma unroll
-    for (int h = 1; h < 32; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if ((i & h) == 0) {
-                const float a = v[i], b = v[i + h];
-                v[i] = a + b;
-                v[i + h] = a - b;
-            }
-}
-
-__device__ __forceinline__ void fwht16x2(float (&v)[32]) {
-#pragma unroll
-    for (int h = 1; h < 16; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            if ((i & h) == 0) {
-                const float a = v[i], b = v[i + h];
-                v[i] = a + b;
-                v[i + h] = a - b;
-            }
-}
-
 template <typename InT>
 __global__ void __launch_bounds__(THREADS, 2)
 rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ hadk,
@@ -117,7 +93,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
 
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         // ---- 1. 512-point transform of segment `seg`
-        float v[32];
+        u64 vp[16];
         {
             const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * N) + seg * 64 + u;
 #pragma unroll
@@ -134,21 +110,29 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                         const float lo = __uint_as_float(ld.w[p] << 16), hi = __uint_as_float(ld.w[p] & 0xFFFF0000u);
                         f = __half22float2(__floats2half2_rn(lo, hi));
                     }
-                    v[c * 8 + 2 * p] = f.x;
-                    v[c * 8 + 2 * p + 1] = f.y;
+                    vp[c * 4 + p] = pack2(f.x, f.y);
                 }
             }
         }
-        fwht32(v);  // bits {0,1,2} (inside a vector) and {7,8} (vector number)
+        fwht_pairs<16, 16>(vp);  // bits {0,1,2} (inside a vector) and {7,8} (vector number)
         float *xs = xbuf + seg * XSEG;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) xs[j * 17 + u] = v[j];
+        for (int a = 0; a < 16; ++a) {
+            float lo, hi;
+            unpack2(vp[a], lo, hi);
+            xs[(2 * a) * 17 + u] = lo;
+            xs[(2 * a + 1) * 17 + u] = hi;
+        }
         __syncwarp();
 #pragma unroll
         for (int r = 0; r < 2; ++r)
 #pragma unroll
-            for (int uu = 0; uu < 16; ++uu) v[r * 16 + uu] = xs[(u + 16 * r) * 17 + uu];
-        fwht16x2(v);  // bits {3..6}
+            for (int uu = 0; uu < 16; uu += 2)
+                vp[r * 8 + uu / 2] = pack2(xs[(u + 16 * r) * 17 + uu], xs[(u + 16 * r) * 17 + uu + 1]);
+        fwht_pairs<16, 8>(vp);  // bits {3..6}: two independent 16-point transforms
+        float v[32];
+#pragma unroll
+        for (int a = 0; a < 16; ++a) unpack2(vp[a], v[2 * a], v[2 * a + 1]);
         __syncthreads();  // every half warp is done with the exchange buffer: Z may overwrite it
 
         // ---- 2. Z[k][j] = rn_h(sum * scale); element of (r, uu): c = (u >> 3) + 2r, b = u & 7
