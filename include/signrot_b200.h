@@ -207,6 +207,28 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
                        int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
                        int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream);
 
+/* sr_batch_decode_i4 for callers that cannot hand over a workspace.  It has no counterpart in
+ * the reference.  Some hosts of this library never get to call cudaMalloc: an inference
+ * server that plans all device memory up front and gives plug-ins no allocator, a latency-bound
+ * serving loop that cannot afford the device-wide synchronisation an allocation implies, or a
+ * binding from a language runtime that only passes tensors through.  For them the split-KV
+ * partial results go into a buffer that is part of the library image: 1,081,344 floats
+ * (4.1 MiB = batch 16 x 32 query heads x 16 chunks x 132), resident on every GPU that loads
+ * the library until the process ends.  Inputs, outputs and the cache are still the caller's.
+ *  - A call that needs more than that (batch_size * num_qo_heads * num_chunks * 132 floats)
+ *    is refused with SR_ERR_UNSUPPORTED and a message that states both numbers.
+ *  - The first call on each device looks up the buffer's device address (the device must be
+ *    current); make that first call before any stream capture begins.
+ *  - All calls share the one buffer.  It is overwritten, never read before being written, so
+ *    back-to-back calls on one stream are fine; two calls that can overlap on the GPU (different
+ *    streams, or different host threads) race on it and must be serialised by the caller.
+ *  - Nothing is allocated or freed here, by the CUDA runtime or any other library. */
+int sr_batch_decode_i4_static(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                              const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                              int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                              int64_t head_dim, int64_t batch_size, int64_t num_chunks, int hadamard_q,
+                              void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -55,6 +55,7 @@ _SIGNATURES = {
     "sr_init_kv_i4": [_P] * 10 + [_I64] * 7 + [_P],
     "sr_kv_append_quant": [_P] * 7 + [_I64] * 7 + [_I, _P],
     "sr_batch_decode_i4": [_P] * 7 + [_I64] * 7 + [_P, _I64, _I, _P],
+    "sr_batch_decode_i4_static": [_P] * 7 + [_I64] * 7 + [_I64, _I, _P],
 }
 
 

@@ -482,4 +482,61 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
     return rc;
 }
 
+// ------------------------------------------------------------------ decode without a caller workspace
+//
+// Built-in split-KV workspace for callers that have no way to allocate device memory: a
+// fixed array in the library's own data segment.  Every GPU that loads the library carries
+// these 4.1 MiB until the process exits.
+#define SR_DECODE_STATIC_FLOATS (16ll * 32 * 16 * 132)  /* batch 16 x 32 q heads x 16 chunks x (128 + 4) */
+static __device__ __align__(256) float g_decode_workspace[SR_DECODE_STATIC_FLOATS];
+
+// In host code `g_decode_workspace` is only a handle for the runtime, not an address a kernel
+// may dereference.  The device address is looked up once per device (with that device current).
+static float *decode_workspace_for_current_device(int *rc) {
+    static float *cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        *rc = fail(SR_ERR_CUDA, "batch_decode_i4_static: cudaGetDevice: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (cached[dev] == nullptr) {
+        float *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_decode_workspace);
+        if (e != cudaSuccess || p == nullptr) {
+            *rc = fail(SR_ERR_CUDA, "batch_decode_i4_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cached[dev] = p;
+    }
+    *rc = SR_OK;
+    return cached[dev];
+}
+
+int sr_batch_decode_i4_static(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                              const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                              int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                              int64_t head_dim, int64_t batch_size, int64_t num_chunks, int hadamard_q,
+                              void *stream) {
+    SR_REQUIRE(batch_size >= 0 && num_qo_heads >= 0, SR_ERR_INVALID, "batch_decode_i4_static: negative size");
+    if (num_chunks < 1) num_chunks = 1;
+    float *ws = nullptr;
+    if (num_chunks > 1 && batch_size > 0) {
+        const long long need = (long long)batch_size * num_qo_heads * num_chunks * (128 + 4);
+        SR_REQUIRE(need <= SR_DECODE_STATIC_FLOATS, SR_ERR_UNSUPPORTED,
+                   "batch_decode_i4_static: batch %lld x %lld q heads x %lld chunks needs %lld floats of workspace, "
+                   "the built-in one holds %lld; use fewer chunks or sr_batch_decode_i4 with your own buffer",
+                   (long long)batch_size, (long long)num_qo_heads, (long long)num_chunks, need,
+                   (long long)SR_DECODE_STATIC_FLOATS);
+        int rc = SR_OK;
+        ws = decode_workspace_for_current_device(&rc);
+        if (rc != SR_OK) return rc;
+    }
+    // Every chunk writes its whole record before the merge kernel reads it, so nothing in the
+    // workspace has to start at zero; what the previous call left there is simply overwritten.
+    return sr_batch_decode_i4(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                              num_qo_heads, num_kv_heads, page_size, head_dim, batch_size, ws, num_chunks, hadamard_q,
+                              stream);
+}
+
 }  // extern "C"
