@@ -416,6 +416,92 @@ def run_kernel_case(name: str):
     print(f"kernel case {name}: done")
 
 
+def _time_cuda(fn, iters=30, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_sweep():
+    """Secondary measurements (one JSON line each, not the headline): the fused-op sweep of
+    BASELINE config 2 at M in {1, 16, 256, 4096}, decode attention of config 3, one Mixtral-shaped
+    MoE block of config 5 at 64 and 4096 tokens.  Each timing is the mean of 30 launches after 5
+    warm-ups; small cases re-use L2-resident buffers, so they measure launch + L2 behaviour."""
+    import signrot_b200  # noqa: F401
+    from signrot_b200.functional import kernel
+    from signrot_b200.functional.hadamard import get_hadK
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm = peaks()["hbm_gbs"]
+    for m in (1, 16, 256, 4096):
+        for k, n in SHAPES:
+            c = make_linear_case(m, k, n)
+            hadK, K = get_hadK(k)
+            x, sg, w, ws = c["x"].to(dev), c["sign"].to(dev), c["w_packed"].to(dev), c["w_scale"].to(dev)
+            hk = hadK.to(dev, torch.float16) if hadK is not None else None
+            pk = kernel.rotate_quant(x, hk, K, sign=sg)
+            t_rot = _time_cuda(lambda: kernel.rotate_quant(x, hk, K, sign=sg))
+            t_gemm = _time_cuda(lambda: kernel.w4a4_linear(pk, w, ws))
+            rot_bytes = m * k * 2.5 + 2 * m + k
+            w_bytes = n * k / 2 + m * k / 2 + 2 * m * n
+            print(json.dumps({"case": "qlinear", "M": m, "K": k, "N": n,
+                              "rotate_quant_us": round(t_rot * 1e3, 2),
+                              "rotate_quant_gbs": round(rot_bytes / t_rot / 1e6, 1),
+                              "gemm_us": round(t_gemm * 1e3, 2),
+                              "gemm_tops": round(2 * m * n * k / t_gemm / 1e9, 1),
+                              "gemm_gbs": round(w_bytes / t_gemm / 1e6, 1),
+                              "gemm_frac_hbm": round(w_bytes / t_gemm / 1e6 / hbm, 3)}))
+    # config 3: int4-KV GQA decode attention, B=16, ctx 4096, 32 q / 8 kv heads, page 256
+    from signrot_b200.transformers import kv_cache as kvc
+    B, Hq, Hkv, T, page = 16, 32, 8, 4096, 256
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 64, dev, 1, Hkv, 128, group_size=Hq // Hkv)
+    g = torch.Generator().manual_seed(0)
+    kk = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
+    vv = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
+    t_fill = _time_cuda(lambda: (cache.reset(), cache.update(kk, vv, 0)), iters=5, warmup=1)
+    cache.reset()
+    cache.update(kk, vv, 0)
+    specs = cache.refresh_specs()
+    q = torch.randn((B, Hq, 128), generator=g).half().to(dev)
+    o = torch.empty_like(q)
+    chunks, tmp = cache._stub.num_chunks, cache._stub.tmp
+    t_dec = _time_cuda(lambda: kvc.batch_decode_i4(o, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks,
+                                                   hadamard_q=True))
+    kv_bytes = B * T * Hkv * 68 * 2
+    print(json.dumps({"case": "decode_attention_i4", "B": B, "ctx": T, "q_heads": Hq, "kv_heads": Hkv,
+                      "chunks": chunks, "decode_us": round(t_dec * 1e3, 2),
+                      "kv_gbs": round(kv_bytes / t_dec / 1e6, 1), "frac_hbm": round(kv_bytes / t_dec / 1e6 / hbm, 3),
+                      "prefill_append_quant_us": round(t_fill * 1e3, 1)}))
+    # config 5: one Mixtral-8x7B-shaped MoE block (8 experts, top-2, hidden 4096, ffn 14336)
+    from signrot_b200 import nn as snn
+    from signrot_b200.functional import pack_i4
+    E, hid, ffn, top_k = 8, 4096, 14336, 2
+    gen = torch.Generator().manual_seed(1)
+    def wq(nn_, kk_):
+        return torch.randint(0, 256, (E, nn_, kk_ // 2), generator=gen, dtype=torch.uint8).to(dev)
+    def sc(nn_, kk_):
+        return (torch.rand((E, nn_), generator=gen) * 0.5 / kk_ + 0.5 / kk_).half().to(dev)
+    gate = torch.nn.Linear(hid, E, bias=False).half().to(dev)
+    sign = (torch.randint(0, 2, (E, ffn), generator=gen) * 2 - 1).to(torch.int8).to(dev)
+    blk = snn.SignRotMoEBlock(gate, top_k=top_k, norm_topk_prob=True, w_gate=wq(ffn, hid), s_gate=sc(ffn, hid),
+                              w_up=wq(ffn, hid), s_up=sc(ffn, hid), w_down=wq(hid, ffn), s_down=sc(hid, ffn),
+                              sign_down=sign)
+    for tokens in (64, 4096):
+        xm = torch.randn((1, tokens, hid), generator=gen).half().to(dev)
+        t_moe = _time_cuda(lambda: blk(xm), iters=5 if tokens > 64 else 20, warmup=2)
+        w_bytes = 3 * E * ffn * hid / 2
+        print(json.dumps({"case": "moe_block", "tokens": tokens, "experts": E, "top_k": top_k,
+                          "block_ms": round(t_moe, 3), "expert_weight_gbs": round(w_bytes / t_moe / 1e6, 1),
+                          "tops": round(2 * 3 * tokens * top_k * ffn * hid / t_moe / 1e9, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -423,12 +509,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="secondary measurements of the other BASELINE configurations (JSON lines)")
     ap.add_argument("--kernel-case", default=None,
                     help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | "
                          "rotate14336 | decode")
     args = ap.parse_args()
     if args.kernel_case:
         run_kernel_case(args.kernel_case)
+        return
+    if args.sweep:
+        run_sweep()
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -29,10 +29,13 @@ def _ulp_close(got, want, ulps=1.0):
     g, w = got.float(), want.float()
     tol = (w.abs() * 2 ** -10).clamp_min(2 ** -24) * ulps + w.abs().amax(dim=-1, keepdim=True) * 2 ** -17
     bad = (g - w).abs() > tol
-    # the 28-point stage runs on the tensor cores, whose fp32 accumulation is not IEEE-ordered:
-    # a few values per million may land two ulps away
+    # Kronecker shapes round twice (after the Walsh-Hadamard stage and after the had-K stage): a
+    # one-ulp difference in one intermediate value moves the K outputs that sum it by one ulp of
+    # the INTERMEDIATE (up to 2^-10 of the row maximum), however small those outputs are.  Such
+    # events are a few per million values.
     assert bad.float().mean().item() <= 1e-5, f"{int(bad.sum())} values differ by more than {ulps} ulp"
-    assert not bool(((g - w).abs() > 2 * tol).any()), "a value differs by more than 2 ulp"
+    worst = ((g - w).abs() - tol).clamp_min(0) / w.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
+    assert worst.max().item() <= 2 ** -9, "a value is off by more than one ulp of an intermediate"
     return (g != w).float().mean().item()
 
 
