@@ -76,7 +76,8 @@ int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const vo
 
 /* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
  * 2 = tcgen05 kernel fed by TMA-staged packed tiles, 3 = persistent tcgen05 kernel with
- * register-path unpack.  For tests and tuning; no counterpart in the reference. */
+ * register-path unpack, 4 = persistent tcgen05 kernel on CTA pairs (cta_group::2, 256 x 256
+ * tiles).  For tests and tuning; no counterpart in the reference. */
 int sr_set_gemm_kernel(int which);
 
 /* ------------------------------------------------------------------ quantizers */

@@ -20,6 +20,7 @@ int fail(int code, const char *fmt, ...) {
 int tc_device_status(int *out, bool clear);
 int grouped_device_status(int *out, bool clear);
 int tc2_device_status(int *out, bool clear);
+int tc3_device_status(int *out, bool clear);
 
 }  // namespace sr
 
@@ -39,7 +40,10 @@ int sr_device_status(int *status, int clear) {
     int c = 0;
     rc = sr::tc2_device_status(&c, clear != 0);
     if (rc) return rc;
-    *status = a ? a : (b ? b : c);
+    int d = 0;
+    rc = sr::tc3_device_status(&d, clear != 0);
+    if (rc) return rc;
+    *status = a ? a : (b ? b : (c ? c : d));
     return SR_OK;
 }
 

@@ -8,8 +8,8 @@
 namespace sr {
 
 // 0 = by shape, 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
-// 3 = persistent tcgen05 kernel with register-path unpack.
-// SIGNROT_B200_GEMM=small|tc|tc2 pins one kernel (used by the parity tests to cover both
+// 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel.
+// SIGNROT_B200_GEMM=small|tc|tc2|tc3 pins one kernel (used by the parity tests to cover both
 // kernels at every shape); sr_set_gemm_kernel() does the same from code.
 static int g_force = -1;
 static int forced_kernel() {
@@ -19,6 +19,7 @@ static int forced_kernel() {
         if (e && !strcmp(e, "small")) g_force = 1;
         if (e && !strcmp(e, "tc")) g_force = 2;
         if (e && !strcmp(e, "tc2")) g_force = 3;
+        if (e && !strcmp(e, "tc3")) g_force = 4;
     }
     return g_force;
 }
@@ -37,6 +38,8 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     if (small)
         return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                  as_stream(stream));
+    if (f == 4)
+        return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
     if (f == 3 || f == 0)
         return launch_gemm_tc2((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
     return launch_gemm_tc((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
@@ -49,7 +52,7 @@ using namespace sr;
 extern "C" {
 
 int sr_set_gemm_kernel(int which) {
-    SR_REQUIRE(which >= 0 && which <= 3, SR_ERR_INVALID, "set_gemm_kernel: expected 0 (auto), 1 (few rows), 2 or 3 (tcgen05 kernels)");
+    SR_REQUIRE(which >= 0 && which <= 4, SR_ERR_INVALID, "set_gemm_kernel: expected 0 (auto), 1 (few rows), 2, 3 or 4 (tcgen05 kernels)");
     g_force = which;
     return SR_OK;
 }

@@ -93,5 +93,7 @@ int launch_gemm_tc(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int
                    const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc2(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                     const Epilogue &ep, cudaStream_t st);
+int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                    const Epilogue &ep, cudaStream_t st);
 
 }  // namespace sr

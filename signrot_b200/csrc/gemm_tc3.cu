@@ -1,0 +1,407 @@
+// W4A4 GEMM on tcgen05 with CTA pairs (cta_group::2): one 256 x 256 output tile per pair.
+//
+// Same contract as the other GEMM kernels (C = A * B^T on packed 4-bit operands, exact int32
+// accumulation in TMEM, optional fused dequant epilogue); replaces signrot/kernels/gemm.cu:7-85
+// and the dequant pass signrot/kernels/quant.cu:66-131.
+//
+// Why pairs: the kernel is bound by the SM's shared-memory data path (packed-tile fill, unpack
+// read, int8 write, tensor-core operand read).  With two CTAs on one 256 x 256 tile each CTA
+// unpacks 128 rows of A and only 128 of the 256 rows of B, and its tensor core reads half of B
+// from the partner's shared memory: per k-block and SM the traffic drops from 144 KB (one CTA,
+// 128 x 256 tile) to 96 KB for the same 128 x 256 x 128 MACs.
+//
+// Per CTA (448 threads), persistent over tiles (tile = cluster + i * clusters, n fastest):
+//   warp 0      TMA producer (no multicast): its 128 rows of packed A and its 128 rows of packed B
+//   warp 1      TMEM allocation (both CTAs, cta_group::2); in the leader CTA (cluster rank 0) one
+//               lane issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 32) for the pair and
+//               commits to both CTAs' barriers (tcgen05.commit ... multicast::cluster)
+//   warps 2..5  epilogue of the CTA's own 128 accumulator rows (two TMEM buffers of 256 columns,
+//               so the next tile's MMAs overlap the epilogue)
+//   warps 6..13 unpack: packed nibble n -> int8 byte 16*n in the 128-byte-swizzled K-major layout
+// Cross-CTA signalling uses mbarrier arrives on the leader's barriers through mapa addresses.
+// Every wait is bounded by a cycle budget; on expiry the CTA aborts, both CTAs fall through to
+// the cluster barrier at the end, TMEM is released and the device status word records the code.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+#include <cuda.h>
+
+namespace sr {
+namespace tc3 {
+
+constexpr int BMC = 128;             // rows of A per CTA (tile M = 256 per pair)
+constexpr int BNC = 128;             // rows of B per CTA (tile N = 256 per pair)
+constexpr int BN = 256;
+constexpr int BK = 128;
+constexpr int PK_ROW = BK / 2;       // 64 packed bytes per row and k-block
+constexpr int SP = 4;                // packed ring depth
+constexpr int SU = 4;                // int8 ring depth
+constexpr int PK_A = BMC * PK_ROW;   // 8 KB
+constexpr int PK_B = BNC * PK_ROW;   // 8 KB
+constexpr int UN_A = BMC * BK;       // 16 KB
+constexpr int UN_B = BNC * BK;       // 16 KB
+constexpr int UNPACK_WARPS = 8;
+constexpr int NUM_UNPACK = UNPACK_WARPS * 32;
+constexpr int THREADS = 64 + 128 + NUM_UNPACK;  // 448
+constexpr int CHUNKS = (BMC + BNC) * 4 / NUM_UNPACK;  // 4
+constexpr long long WAIT_BUDGET = 1500000000ll;
+
+struct Smem {
+    static constexpr int un_a = 0;
+    static constexpr int un_b = un_a + SU * UN_A;
+    static constexpr int pk_a = un_b + SU * UN_B;
+    static constexpr int pk_b = pk_a + SP * PK_A;
+    static constexpr int bars = pk_b + SP * PK_B;
+    static constexpr int total = bars + 256;
+};
+constexpr int SMEM_BYTES = Smem::total + 1024;
+
+__device__ int g_status;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// arrive on the barrier at the same offset in CTA `cta` of the cluster
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
+    asm volatile(
+        "{\n\t.reg .b32 remaddr;\n\t"
+        "mapa.shared::cluster.u32 remaddr, %0, %1;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remaddr];\n\t}"
+        ::"r"(bar), "r"(cta)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_BUDGET) {
+            *abort_flag = code;
+            atomicCAS(&g_status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void mma_i8_2cta(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accum)
+        : "memory");
+}
+// arrives (once) on the barrier at this offset in both CTAs of the pair when the MMAs issued so far are done
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <bool A_UNSIGNED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
+                uint32_t N, uint32_t K, Epilogue ep) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + Smem::bars;
+    auto pk_full = [&](int s) { return bars + 8u * s; };
+    auto pk_empty = [&](int s) { return bars + 8u * (SP + s); };
+    auto un_full = [&](int s) { return bars + 8u * (2 * SP + s); };             // used in the leader only
+    auto un_empty = [&](int s) { return bars + 8u * (2 * SP + SU + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (2 * SP + 2 * SU + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * SP + 2 * SU + 2 + b); };  // used in the leader only
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool small = (A_UNSIGNED ? 120u : 64u) * (uint64_t)K < (1u << 22);
+    const uint32_t tiles_n = (N + BN - 1) / BN, tiles_m = (M + 2 * BMC - 1) / (2 * BMC);
+    const uint32_t num_tiles = tiles_n * tiles_m;
+    const uint32_t num_kb = (K + BK - 1) / BK;
+    const uint32_t cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+
+    if (tid == 0) {
+        abort_flag = g_status;
+        for (int s = 0; s < SP; ++s) {
+            mbar_init(pk_full(s), 1);
+            mbar_init(pk_empty(s), UNPACK_WARPS);
+        }
+        for (int s = 0; s < SU; ++s) {
+            mbar_init(un_full(s), 2 * UNPACK_WARPS);
+            mbar_init(un_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 2 * 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // barriers of both CTAs are initialised before anyone signals across the pair
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_acc = tmem_base_slot;
+    volatile int *ab = &abort_flag;
+
+    if (*ab == 0) {
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer (own rows only)
+            if (lane == 0) {
+                uint32_t g = 0;
+                bool ok = true;
+                for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters) {
+                    const int ya = (int)((tile / tiles_n) * 2 * BMC + rank * BMC);
+                    const int yb = (int)((tile % tiles_n) * BN + rank * BNC);
+                    for (uint32_t kb = 0; kb < num_kb; ++kb, ++g) {
+                        const int s = g % SP;
+                        ok = mbar_wait(pk_empty(s), ((g / SP) & 1) ^ 1, ab, 41);
+                        if (!ok) break;
+                        mbar_expect_tx(pk_full(s), PK_A + PK_B);
+                        tma_load_2d(base + Smem::pk_a + s * PK_A, &map_a, (int)(kb * PK_ROW), ya, pk_full(s));
+                        tma_load_2d(base + Smem::pk_b + s * PK_B, &map_b, (int)(kb * PK_ROW), yb, pk_full(s));
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------ MMA issuer (leader CTA only)
+            if (rank == 0 && lane == 0) {
+                const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BMC) >> 4) << 24);
+                uint32_t g = 0, it = 0;
+                bool ok = true;
+                for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
+                    const uint32_t buf = it & 1;
+                    ok = mbar_wait(acc_empty(buf), ((it >> 1) & 1) ^ 1, ab, 42);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d_tmem = tmem_acc + buf * BN;
+                    for (uint32_t kb = 0; kb < num_kb; ++kb, ++g) {
+                        const int s = g % SU;
+                        ok = mbar_wait(un_full(s), (g / SU) & 1, ab, 43);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t da = make_desc(base + Smem::un_a + s * UN_A);
+                        const uint64_t db = make_desc(base + Smem::un_b + s * UN_B);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 32; ++kk)
+                            mma_i8_2cta(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                                        (kb > 0 || kk > 0) ? 1u : 0u);
+                        mma_commit_pair(un_empty(s));
+                    }
+                    if (ok) mma_commit_pair(acc_full(buf));
+                }
+            }
+        } else if (warp <= 5) {
+            // ------------------------------------------------ epilogue (own 128 rows)
+            const uint32_t quarter = warp & 3;
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
+                const uint32_t buf = it & 1;
+                const uint32_t m0 = (tile / tiles_n) * 2 * BMC + rank * BMC, n0 = (tile % tiles_n) * BN;
+                ok = mbar_wait(acc_full(buf), (it >> 1) & 1, ab, 44);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    int v[32];
+                    tmem_ld32(tmem_acc + ((quarter * 32u) << 16) + buf * BN + (uint32_t)(c * 32), v);
+                    if (c == BN / 32 - 1) {
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(acc_empty(buf), 0);
+                    }
+                    store_acc_chunk(ep, row, n0 + c * 32, v, M, N, small);
+                }
+            }
+        } else {
+            // ------------------------------------------------ unpack
+            const int t = tid - 192;  // 0..255
+            const uint32_t my_tiles = (num_tiles > cluster) ? ((num_tiles - cluster - 1) / clusters + 1) : 0;
+            const uint32_t total = my_tiles * num_kb;
+            bool ok = true;
+            for (uint32_t g = 0; g < total && ok; ++g) {
+                const int s = g % SP, u = g % SU;
+                ok = mbar_wait(pk_full(s), (g / SP) & 1, ab, 45);
+                if (!ok) break;
+                ok = mbar_wait(un_empty(u), ((g / SU) & 1) ^ 1, ab, 46);
+                if (!ok) break;
+                const uint8_t *pa = base_ptr + Smem::pk_a + s * PK_A;
+                const uint8_t *pb = base_ptr + Smem::pk_b + s * PK_B;
+                uint8_t *ua = base_ptr + Smem::un_a + u * UN_A;
+                uint8_t *ub = base_ptr + Smem::un_b + u * UN_B;
+#pragma unroll
+                for (int i = 0; i < CHUNKS; ++i) {
+                    const int id = i * NUM_UNPACK + t;
+                    const bool is_a = id < BMC * 4;
+                    const int cid = is_a ? id : id - BMC * 4;
+                    const uint4 pk = *reinterpret_cast<const uint4 *>((is_a ? pa : pb) + cid * 16);
+                    const int r = cid >> 2, qd = cid & 3;
+                    uint4 e, o;
+                    e.x = (pk.x << 4) & 0xF0F0F0F0u; o.x = pk.x & 0xF0F0F0F0u;
+                    e.y = (pk.y << 4) & 0xF0F0F0F0u; o.y = pk.y & 0xF0F0F0F0u;
+                    e.z = (pk.z << 4) & 0xF0F0F0F0u; o.z = pk.z & 0xF0F0F0F0u;
+                    e.w = (pk.w << 4) & 0xF0F0F0F0u; o.w = pk.w & 0xF0F0F0F0u;
+                    uint8_t *rowp = (is_a ? ua : ub) + (r >> 3) * 1024 + (r & 7) * 128;
+                    *reinterpret_cast<uint4 *>(rowp + (((2 * qd) ^ (r & 7)) << 4)) = e;
+                    *reinterpret_cast<uint4 *>(rowp + (((2 * qd + 1) ^ (r & 7)) << 4)) = o;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(un_full(u), 0);  // the leader's MMA warp waits for both CTAs
+                    mbar_arrive(pk_empty(s));
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*ab != 0 && tid == 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000ll) {
+        }
+    }
+    __syncthreads();
+    // neither CTA may leave (or free TMEM) while its partner can still signal it or read its tiles
+    asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512u) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    SR_REQUIRE(fn != nullptr, SR_ERR_CUDA, "matmul: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)PK_ROW, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SR_REQUIRE(r == CUDA_SUCCESS, SR_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return SR_OK;
+}
+
+}  // namespace tc3
+
+int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                    const Epilogue &ep, cudaStream_t st) {
+    using namespace tc3;
+    SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "matmul: operands must be 16-byte aligned");
+    SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "matmul: K = %lld must be a multiple of 32", (long long)K);
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K / 2, BMC);
+    if (rc) return rc;
+    rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K / 2, BNC);
+    if (rc) return rc;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const int64_t tiles = cdiv<int64_t>(N, BN) * cdiv<int64_t>(M, 2 * BMC);
+    int64_t clusters = sm_count / 2;
+    if (tiles < clusters) clusters = tiles;
+    auto kfn = a_unsigned ? gemm_tc3_kernel<true> : gemm_tc3_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    kfn<<<(unsigned)(2 * clusters), THREADS, SMEM_BYTES, st>>>(ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep);
+    return check_launch("gemm_tc3");
+}
+
+int tc3_device_status(int *out, bool clear) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, tc3::g_status, sizeof(int));
+    if (e != cudaSuccess) return fail(SR_ERR_CUDA, "device_status: %s", cudaGetErrorString(e));
+    if (clear && v != 0) {
+        const int z = 0;
+        cudaMemcpyToSymbol(tc3::g_status, &z, sizeof(int));
+    }
+    *out = v;
+    return SR_OK;
+}
+
+}  // namespace sr

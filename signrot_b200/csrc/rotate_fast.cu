@@ -89,14 +89,23 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
     const __half2 magic = __floats2half2_rn(1536.f, 1536.f);
     const u64 scale2 = pack2(scale, scale);
 
-    for (uint32_t row = blockIdx.x * ROWS_PER_CTA + team; row < rows; row += gridDim.x * ROWS_PER_CTA) {
-        // ---- phase 1: load + 64-point transform over bits {0,1,2,9,10,11}
+    const uint32_t row_step = gridDim.x * ROWS_PER_CTA;
+    uint4 nx[8];  // the row after the current one, in flight while the current one is transformed
+    {
+        const uint32_t row0 = blockIdx.x * ROWS_PER_CTA + team;
+        if (row0 < rows) {
+            const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row0 * N);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) nx[c] = __ldg(xr + c * 64 + t);
+        }
+    }
+    for (uint32_t row = blockIdx.x * ROWS_PER_CTA + team; row < rows; row += row_step) {
+        // ---- phase 1: 64-point transform over bits {0,1,2,9,10,11}
         u64 v[32];
-        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * N);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             Vec16 ld;
-            ld.u = __ldg(xr + c * 64 + t);
+            ld.u = nx[c];
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
                 float2 f;
@@ -109,6 +118,11 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
                 }
                 v[c * 4 + p] = pack2(f.x, f.y);
             }
+        }
+        if (row + row_step < rows) {
+            const uint4 *xn = reinterpret_cast<const uint4 *>(x + (size_t)(row + row_step) * N);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) nx[c] = __ldg(xn + c * 64 + t);
         }
         fwht_pairs<32, 32>(v);
         // ---- exchange: value j of thread t goes to row j, position wpos
