@@ -353,7 +353,7 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": "qlinear-8b-m4096", "M": M, "shapes_KN": SHAPES, "activations": "bf16",
                    "output": "fp16", "parallelism": f"rows x{world} (no collective)",
                    "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB"},
-        "roofline": {"kernel": "gemm_tc2_kernel (persistent tcgen05 kind::i8, register-path unpack, fused dequant)", "bound": "tensor",
+        "roofline": {"kernel": "gemm_tc3_kernel (persistent tcgen05 cta_group::2 kind::i8, 256x256 tile per CTA pair, TMA-staged packed tiles, fused dequant)", "bound": "tensor",
                      "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
                      "frac": round(gemm_ach / int8_peak, 4),
                      "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",

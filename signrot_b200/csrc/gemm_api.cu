@@ -7,7 +7,7 @@
 
 namespace sr {
 
-// 0 = by shape, 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
+// 0 = by shape (M <= 32: few-rows kernel, M <= 128: kernel 3, else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
 // 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel.
 // SIGNROT_B200_GEMM=small|tc|tc2|tc3 pins one kernel (used by the parity tests to cover both
 // kernels at every shape); sr_set_gemm_kernel() does the same from code.
@@ -38,7 +38,7 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     if (small)
         return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                  as_stream(stream));
-    if (f == 4)
+    if (f == 4 || (f == 0 && M > 128))
         return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
     if (f == 3 || f == 0)
         return launch_gemm_tc2((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));

@@ -58,7 +58,9 @@ __device__ __forceinline__ void store_acc_chunk(const Epilogue &ep, uint32_t row
             for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<int4 *>(dst + j) = make_int4(v[j] >> 8, v[j + 1] >> 8, v[j + 2] >> 8, v[j + 3] >> 8);
         } else {
-            for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = v[j] >> 8;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) dst[j] = v[j] >> 8;
         }
         return;
     }
@@ -83,7 +85,9 @@ __device__ __forceinline__ void store_acc_chunk(const Epilogue &ep, uint32_t row
             *reinterpret_cast<uint4 *>(dst + j) = o.u;
         }
     } else {
-        for (int j = 0; j < 32 && col0 + j < N; ++j) dst[j] = ep.dequant(row, col0 + j, v[j] >> 8, N);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) dst[j] = ep.dequant(row, col0 + j, v[j] >> 8, N);
     }
 }
 

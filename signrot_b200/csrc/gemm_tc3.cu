@@ -24,6 +24,8 @@
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 
 namespace sr {
 namespace tc3 {
@@ -33,8 +35,7 @@ constexpr int BNC = 128;             // rows of B per CTA (tile N = 256 per pair
 constexpr int BN = 256;
 constexpr int BK = 128;
 constexpr int PK_ROW = BK / 2;       // 64 packed bytes per row and k-block
-constexpr int SP = 4;                // packed ring depth
-constexpr int SU = 4;                // int8 ring depth
+constexpr int MAX_STAGES = 8;        // ring depths are launch parameters (packed ring sp, int8 ring su)
 constexpr int PK_A = BMC * PK_ROW;   // 8 KB
 constexpr int PK_B = BNC * PK_ROW;   // 8 KB
 constexpr int UN_A = BMC * BK;       // 16 KB
@@ -42,18 +43,25 @@ constexpr int UN_B = BNC * BK;       // 16 KB
 constexpr int UNPACK_WARPS = 8;
 constexpr int NUM_UNPACK = UNPACK_WARPS * 32;
 constexpr int THREADS = 64 + 128 + NUM_UNPACK;  // 448
-constexpr int CHUNKS = (BMC + BNC) * 4 / NUM_UNPACK;  // 4
 constexpr long long WAIT_BUDGET = 1500000000ll;
 
-struct Smem {
-    static constexpr int un_a = 0;
-    static constexpr int un_b = un_a + SU * UN_A;
-    static constexpr int pk_a = un_b + SU * UN_B;
-    static constexpr int pk_b = pk_a + SP * PK_A;
-    static constexpr int bars = pk_b + SP * PK_B;
-    static constexpr int total = bars + 256;
+constexpr int BAR_BYTES = 512;
+constexpr int MAX_SMEM = 226 * 1024;   // dynamic part; the kernel also has a few static words
+__host__ __device__ constexpr int smem_bytes(int sp, int su) {
+    return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + 1024;
+}
+
+// position in a ring of `depth` stages and the parity of the current pass over it
+struct Ring {
+    int s = 0;
+    uint32_t ph = 0;
+    __device__ __forceinline__ void next(int depth) {
+        if (++s == depth) {
+            s = 0;
+            ph ^= 1;
+        }
+    }
 };
-constexpr int SMEM_BYTES = Smem::total + 1024;
 
 __device__ int g_status;
 
@@ -87,11 +95,15 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Bounded wait.  The poll loop touches nothing but the barrier (every other shared-memory access
+// would compete with the operand traffic); the abort flag and the clock are looked at every 64 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_BUDGET) {
             *abort_flag = code;
@@ -144,10 +156,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <bool A_UNSIGNED>
+template <bool A_UNSIGNED, int G>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
-                uint32_t N, uint32_t K, Epilogue ep) {
+                uint32_t N, uint32_t K, int SP, int SU, Epilogue ep) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -155,13 +167,14 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - raw);
-    const uint32_t bars = base + Smem::bars;
+    const int off_un_a = 0, off_un_b = SU * UN_A, off_pk_a = SU * (UN_A + UN_B), off_pk_b = off_pk_a + SP * PK_A;
+    const uint32_t bars = base + off_pk_b + SP * PK_B;
     auto pk_full = [&](int s) { return bars + 8u * s; };
-    auto pk_empty = [&](int s) { return bars + 8u * (SP + s); };
-    auto un_full = [&](int s) { return bars + 8u * (2 * SP + s); };             // used in the leader only
-    auto un_empty = [&](int s) { return bars + 8u * (2 * SP + SU + s); };
-    auto acc_full = [&](int b) { return bars + 8u * (2 * SP + 2 * SU + b); };
-    auto acc_empty = [&](int b) { return bars + 8u * (2 * SP + 2 * SU + 2 + b); };  // used in the leader only
+    auto pk_empty = [&](int s) { return bars + 8u * (MAX_STAGES + s); };
+    auto un_full = [&](int s) { return bars + 8u * (2 * MAX_STAGES + s); };             // used in the leader only
+    auto un_empty = [&](int s) { return bars + 8u * (3 * MAX_STAGES + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (4 * MAX_STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (4 * MAX_STAGES + 2 + b); };       // used in the leader only
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t rank;
@@ -176,10 +189,10 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         abort_flag = g_status;
         for (int s = 0; s < SP; ++s) {
             mbar_init(pk_full(s), 1);
-            mbar_init(pk_empty(s), UNPACK_WARPS);
+            mbar_init(pk_empty(s), UNPACK_WARPS / G);
         }
         for (int s = 0; s < SU; ++s) {
-            mbar_init(un_full(s), 2 * UNPACK_WARPS);
+            mbar_init(un_full(s), 2 * UNPACK_WARPS / G);
             mbar_init(un_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -207,18 +220,18 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (own rows only)
             if (lane == 0) {
-                uint32_t g = 0;
+                Ring pr;
                 bool ok = true;
                 for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters) {
                     const int ya = (int)((tile / tiles_n) * 2 * BMC + rank * BMC);
                     const int yb = (int)((tile % tiles_n) * BN + rank * BNC);
-                    for (uint32_t kb = 0; kb < num_kb; ++kb, ++g) {
-                        const int s = g % SP;
-                        ok = mbar_wait(pk_empty(s), ((g / SP) & 1) ^ 1, ab, 41);
+                    for (uint32_t kb = 0; kb < num_kb; ++kb, pr.next(SP)) {
+                        const int s = pr.s;
+                        ok = mbar_wait(pk_empty(s), pr.ph ^ 1, ab, 41);
                         if (!ok) break;
                         mbar_expect_tx(pk_full(s), PK_A + PK_B);
-                        tma_load_2d(base + Smem::pk_a + s * PK_A, &map_a, (int)(kb * PK_ROW), ya, pk_full(s));
-                        tma_load_2d(base + Smem::pk_b + s * PK_B, &map_b, (int)(kb * PK_ROW), yb, pk_full(s));
+                        tma_load_2d(base + off_pk_a + s * PK_A, &map_a, (int)(kb * PK_ROW), ya, pk_full(s));
+                        tma_load_2d(base + off_pk_b + s * PK_B, &map_b, (int)(kb * PK_ROW), yb, pk_full(s));
                     }
                 }
             }
@@ -227,7 +240,8 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (rank == 0 && lane == 0) {
                 const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
                                        ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BMC) >> 4) << 24);
-                uint32_t g = 0, it = 0;
+                uint32_t it = 0;
+                Ring ur;
                 bool ok = true;
                 for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
                     const uint32_t buf = it & 1;
@@ -235,13 +249,13 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t d_tmem = tmem_acc + buf * BN;
-                    for (uint32_t kb = 0; kb < num_kb; ++kb, ++g) {
-                        const int s = g % SU;
-                        ok = mbar_wait(un_full(s), (g / SU) & 1, ab, 43);
+                    for (uint32_t kb = 0; kb < num_kb; ++kb, ur.next(SU)) {
+                        const int s = ur.s;
+                        ok = mbar_wait(un_full(s), ur.ph, ab, 43);
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint64_t da = make_desc(base + Smem::un_a + s * UN_A);
-                        const uint64_t db = make_desc(base + Smem::un_b + s * UN_B);
+                        const uint64_t da = make_desc(base + off_un_a + s * UN_A);
+                        const uint64_t db = make_desc(base + off_un_b + s * UN_B);
 #pragma unroll
                         for (int kk = 0; kk < BK / 32; ++kk)
                             mma_i8_2cta(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
@@ -277,41 +291,67 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         } else {
             // ------------------------------------------------ unpack
-            const int t = tid - 192;  // 0..255
+            // The warps form G groups; group i converts k-blocks i, i + G, ...  The proxy fence
+            // that publishes a stage to the tensor core takes several hundred cycles, so
+            // consecutive k-blocks are converted by different warps and the fences overlap.
+            constexpr int GT = NUM_UNPACK / G;        // threads per group
+            constexpr int STEPS = 4 * G;              // 16-byte packed chunks per thread and k-block
+            const int t = tid - 192;                  // 0..255
+            const int grp = t / GT, tg = t % GT;
+            // step i handles chunk i * GT + tg: row r0 + i * GT / 4 (r0 = tg / 4), quad tg % 4 of A
+            // (first half of the steps) or B; the row's position inside its 8-row swizzle atom and
+            // the quad never change, so every step is a constant offset from two per-thread bases
+            const int r0 = tg >> 2, qd = tg & 3;
+            const uint32_t ld_off = (uint32_t)tg * 16;
+            const uint32_t st_off = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
+            const uint32_t sw_e = (uint32_t)(((2 * qd) ^ (r0 & 7)) << 4), sw_o = (uint32_t)(((2 * qd + 1) ^ (r0 & 7)) << 4);
             const uint32_t my_tiles = (num_tiles > cluster) ? ((num_tiles - cluster - 1) / clusters + 1) : 0;
             const uint32_t total = my_tiles * num_kb;
             bool ok = true;
-            for (uint32_t g = 0; g < total && ok; ++g) {
-                const int s = g % SP, u = g % SU;
-                ok = mbar_wait(pk_full(s), (g / SP) & 1, ab, 45);
+            Ring pr, ur;
+            for (int i = 0; i < grp; ++i) {
+                pr.next(SP);
+                ur.next(SU);
+            }
+            for (uint32_t g = grp; g < total && ok; g += G) {
+                const int s = pr.s, u = ur.s;
+                ok = mbar_wait(pk_full(s), pr.ph, ab, 45);
                 if (!ok) break;
-                ok = mbar_wait(un_empty(u), ((g / SU) & 1) ^ 1, ab, 46);
+                ok = mbar_wait(un_empty(u), ur.ph ^ 1, ab, 46);
                 if (!ok) break;
-                const uint8_t *pa = base_ptr + Smem::pk_a + s * PK_A;
-                const uint8_t *pb = base_ptr + Smem::pk_b + s * PK_B;
-                uint8_t *ua = base_ptr + Smem::un_a + u * UN_A;
-                uint8_t *ub = base_ptr + Smem::un_b + u * UN_B;
+                const uint8_t *pa = base_ptr + off_pk_a + s * PK_A + ld_off;
+                const uint8_t *pb = base_ptr + off_pk_b + s * PK_B + ld_off;
+                uint8_t *ua = base_ptr + off_un_a + u * UN_A + st_off;
+                uint8_t *ub = base_ptr + off_un_b + u * UN_B + st_off;
 #pragma unroll
-                for (int i = 0; i < CHUNKS; ++i) {
-                    const int id = i * NUM_UNPACK + t;
-                    const bool is_a = id < BMC * 4;
-                    const int cid = is_a ? id : id - BMC * 4;
-                    const uint4 pk = *reinterpret_cast<const uint4 *>((is_a ? pa : pb) + cid * 16);
-                    const int r = cid >> 2, qd = cid & 3;
-                    uint4 e, o;
-                    e.x = (pk.x << 4) & 0xF0F0F0F0u; o.x = pk.x & 0xF0F0F0F0u;
-                    e.y = (pk.y << 4) & 0xF0F0F0F0u; o.y = pk.y & 0xF0F0F0F0u;
-                    e.z = (pk.z << 4) & 0xF0F0F0F0u; o.z = pk.z & 0xF0F0F0F0u;
-                    e.w = (pk.w << 4) & 0xF0F0F0F0u; o.w = pk.w & 0xF0F0F0F0u;
-                    uint8_t *rowp = (is_a ? ua : ub) + (r >> 3) * 1024 + (r & 7) * 128;
-                    *reinterpret_cast<uint4 *>(rowp + (((2 * qd) ^ (r & 7)) << 4)) = e;
-                    *reinterpret_cast<uint4 *>(rowp + (((2 * qd + 1) ^ (r & 7)) << 4)) = o;
+                for (int half = 0; half < 2; ++half) {
+                    const uint8_t *src = half ? pb : pa;
+                    uint8_t *dst = half ? ub : ua;
+                    uint4 pk[STEPS / 2];
+#pragma unroll
+                    for (int i = 0; i < STEPS / 2; ++i) pk[i] = *reinterpret_cast<const uint4 *>(src + i * GT * 16);
+#pragma unroll
+                    for (int i = 0; i < STEPS / 2; ++i) {
+                        uint4 e, od;
+                        // the shift runs as a multiply on the FMA pipe, the masks on the ALU pipe
+                        e.x = (pk[i].x * 16u) & 0xF0F0F0F0u; od.x = pk[i].x & 0xF0F0F0F0u;
+                        e.y = (pk[i].y * 16u) & 0xF0F0F0F0u; od.y = pk[i].y & 0xF0F0F0F0u;
+                        e.z = (pk[i].z * 16u) & 0xF0F0F0F0u; od.z = pk[i].z & 0xF0F0F0F0u;
+                        e.w = (pk[i].w * 16u) & 0xF0F0F0F0u; od.w = pk[i].w & 0xF0F0F0F0u;
+                        uint8_t *rowp = dst + i * (GT / 32) * 1024;
+                        *reinterpret_cast<uint4 *>(rowp + sw_e) = e;
+                        *reinterpret_cast<uint4 *>(rowp + sw_o) = od;
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive_cluster(un_full(u), 0);  // the leader's MMA warp waits for both CTAs
                     mbar_arrive(pk_empty(s));
+                }
+                for (int i = 0; i < G; ++i) {
+                    pr.next(SP);
+                    ur.next(SU);
                 }
             }
         }
@@ -385,10 +425,32 @@ int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, in
     const int64_t tiles = cdiv<int64_t>(N, BN) * cdiv<int64_t>(M, 2 * BMC);
     int64_t clusters = sm_count / 2;
     if (tiles < clusters) clusters = tiles;
-    auto kfn = a_unsigned ? gemm_tc3_kernel<true> : gemm_tc3_kernel<false>;
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    // SIGNROT_B200_TC3_STAGES="<packed ring>,<int8 ring>,<unpack groups>" is a tuning knob
+    static int sp = 0, su = 0, groups = 0;
+    if (sp == 0) {
+        int a = 4, b = 4, c = 4;
+        const char *env = getenv("SIGNROT_B200_TC3_STAGES");
+        if (env) sscanf(env, "%d,%d,%d", &a, &b, &c);
+        const bool groups_ok = c == 1 || c == 2 || c == 4;
+        // a group may run at most one pass ahead of a ring's barriers: groups <= both ring depths
+        if (a < 2 || a > MAX_STAGES || b < 2 || b > MAX_STAGES || !groups_ok || c > a || c > b ||
+            smem_bytes(a, b) > MAX_SMEM) {
+            a = 4;
+            b = 4;
+            c = 4;
+        }
+        sp = a;
+        su = b;
+        groups = c;
+    }
+    void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, Epilogue);
+    if (groups == 1) kfn = a_unsigned ? gemm_tc3_kernel<true, 1> : gemm_tc3_kernel<false, 1>;
+    else if (groups == 2) kfn = a_unsigned ? gemm_tc3_kernel<true, 2> : gemm_tc3_kernel<false, 2>;
+    else kfn = a_unsigned ? gemm_tc3_kernel<true, 4> : gemm_tc3_kernel<false, 4>;
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<(unsigned)(2 * clusters), THREADS, SMEM_BYTES, st>>>(ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep);
+    kfn<<<(unsigned)(2 * clusters), THREADS, smem_bytes(sp, su), st>>>(ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, sp,
+                                                                        su, ep);
     return check_launch("gemm_tc3");
 }
 
