@@ -416,11 +416,29 @@ def run_kernel_case(name: str):
     print(f"kernel case {name}: done")
 
 
-def _time_cuda(fn, iters=30, warmup=5):
+def _time_cuda(fn, iters=30, warmup=5, graph=True):
+    """Mean device time of fn() in ms.  The launches are captured into one CUDA graph and replayed,
+    so the host's per-call cost (tens of microseconds in Python) is not part of a small kernel's figure;
+    callables that cannot be captured are timed launch by launch."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(iters):
+                    fn()
+            gr.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters
+        except Exception:
+            torch.cuda.synchronize()
     e0.record()
     for _ in range(iters):
         fn()
@@ -433,7 +451,7 @@ def run_sweep():
     """Secondary measurements (one JSON line each, not the headline): the fused-op sweep of
     BASELINE config 2 at M in {1, 16, 256, 4096}, decode attention of config 3, one Mixtral-shaped
     MoE block of config 5 at 64 and 4096 tokens.  Each timing is the mean of 30 launches after 5
-    warm-ups; small cases re-use L2-resident buffers, so they measure launch + L2 behaviour."""
+    warm-ups, replayed from a CUDA graph; small cases re-use L2-resident buffers, so they measure L2 behaviour."""
     import signrot_b200  # noqa: F401
     from signrot_b200.functional import kernel
     from signrot_b200.functional.hadamard import get_hadK
@@ -465,7 +483,7 @@ def run_sweep():
     g = torch.Generator().manual_seed(0)
     kk = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
     vv = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
-    t_fill = _time_cuda(lambda: (cache.reset(), cache.update(kk, vv, 0)), iters=5, warmup=1)
+    t_fill = _time_cuda(lambda: (cache.reset(), cache.update(kk, vv, 0)), iters=5, warmup=1, graph=False)
     cache.reset()
     cache.update(kk, vv, 0)
     specs = cache.refresh_specs()

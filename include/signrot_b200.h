@@ -74,6 +74,17 @@ int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const vo
                       const void *ptr_c, const void *lda, const void *ldb, const void *ldc, int signed_a,
                       int64_t max_k, void *stream);
 
+/* Sparse-MoE expert linear in one launch: rows of A are sorted by expert, expert e owns rows
+ * row_offsets[e] .. row_offsets[e+1]-1 (int32 [num_experts + 1], device memory, never read on the
+ * host) and multiplies its own weight W[e] (W packed s4 [num_experts, N, K/2]).  Fuses what the
+ * reference runs as matmul_grouped followed by sym_dequant_moe (signrot/nn/moe.py:114-162,
+ * signrot/kernels/moe.cu:190-233): out[r, n] = rn_h((float(acc) * a_scale[r]) * w_scale[e, n]) with
+ * e = expert_ids[r] (int32 [rows]); asymmetric activations pass a_zero int8 [rows] and w_sum int32
+ * [num_experts, N].  Runs on the tcgen05 CTA-pair kernel; at most 512 experts. */
+int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
+                      const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
+                      int64_t num_experts, int64_t N, int64_t K, void *out, void *stream);
+
 /* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
  * 2 = tcgen05 kernel fed by TMA-staged packed tiles, 3 = persistent tcgen05 kernel with
  * register-path unpack, 4 = persistent tcgen05 kernel on CTA pairs (cta_group::2, 256 x 256

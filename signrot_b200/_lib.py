@@ -31,6 +31,7 @@ _SIGNATURES = {
     "sr_device_status": [ctypes.POINTER(ctypes.c_int), _I],
     "sr_matmul_i4": [_P, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_w4a4_linear": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
+    "sr_grouped_linear": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P],
     "sr_matmul_grouped": [_P, _I64, _P, _P, _P, _P, _P, _P, _I, _I64, _P],
     "sr_set_gemm_kernel": [_I],
     "sr_sym_quant_dynamic": [_P, _I64, _I64, _F, _P, _P, _P],

@@ -83,4 +83,28 @@ int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const
     return run_gemm(A, W, M, N, K, a_zero != nullptr, ep, stream, "w4a4_linear");
 }
 
+int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
+                      const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
+                      int64_t num_experts, int64_t N, int64_t K, void *out, void *stream) {
+    SR_REQUIRE(rows >= 0 && N >= 0 && K >= 0 && num_experts >= 1, SR_ERR_INVALID, "grouped_linear: bad size");
+    if (rows == 0 || N == 0) return SR_OK;
+    SR_REQUIRE(K > 0 && K % 32 == 0, SR_ERR_INVALID, "grouped_linear: K = %lld must be a positive multiple of 32",
+               (long long)K);
+    SR_REQUIRE(A && W && out && a_scale && w_scale && expert_ids && row_offsets, SR_ERR_INVALID,
+               "grouped_linear: null pointer");
+    SR_REQUIRE(a_zero == nullptr || w_sum != nullptr, SR_ERR_INVALID,
+               "grouped_linear: asymmetric activations need the int4 row sums of the weights");
+    SR_REQUIRE(K <= 131072, SR_ERR_UNSUPPORTED, "grouped_linear: size out of range");
+    Epilogue ep = {};
+    ep.mode = 1;
+    ep.out = (__half *)out;
+    ep.a_scale = (const __half *)a_scale;
+    ep.w_scale = (const __half *)w_scale;
+    ep.a_zero = (const int8_t *)a_zero;
+    ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
+    ep.expert_ids = (const int32_t *)expert_ids;
+    return launch_gemm_tc3_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,
+                                   (const int32_t *)row_offsets, (int)num_experts, as_stream(stream));
+}
+
 }  // extern "C"

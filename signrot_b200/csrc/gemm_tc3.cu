@@ -46,9 +46,11 @@ constexpr int THREADS = 64 + 128 + NUM_UNPACK;  // 448
 constexpr long long WAIT_BUDGET = 1500000000ll;
 
 constexpr int BAR_BYTES = 512;
+constexpr int MAX_EXPERTS = 512;                    // grouped launches: first m-tile of every expert, in shared memory
+constexpr int SCHED_BYTES = (MAX_EXPERTS + 4) * 4;
 constexpr int MAX_SMEM = 226 * 1024;   // dynamic part; the kernel also has a few static words
 __host__ __device__ constexpr int smem_bytes(int sp, int su) {
-    return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + 1024;
+    return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + SCHED_BYTES + 1024;
 }
 
 // position in a ring of `depth` stages and the parity of the current pass over it
@@ -156,10 +158,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Tile -> coordinates.  Dense: tile = m_tile * tiles_n + n_tile over one [M, N] problem.
+// Grouped (row_off != null): the rows of A are sorted by expert, expert e owns rows
+// row_off[e] .. row_off[e+1]-1 and multiplies the weight rows e*N .. e*N+N-1 of B; its m-tiles start
+// at its first row, and rows of a tile past the expert's last row are computed but never stored.
+struct TileCoord {
+    uint32_t a_row;     // first row of A of the pair's tile
+    uint32_t b_row;     // first row of B (weight row, expert offset included)
+    uint32_t n0;        // first output column
+    uint32_t row_end;   // rows >= row_end are not stored
+};
+
 template <bool A_UNSIGNED, int G>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
-                uint32_t N, uint32_t K, int SP, int SU, Epilogue ep) {
+                uint32_t N, uint32_t K, int SP, int SU, const int32_t *__restrict__ row_off, int num_experts,
+                Epilogue ep) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -180,12 +194,23 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t rank;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const bool small = (A_UNSIGNED ? 120u : 64u) * (uint64_t)K < (1u << 22);
-    const uint32_t tiles_n = (N + BN - 1) / BN, tiles_m = (M + 2 * BMC - 1) / (2 * BMC);
-    const uint32_t num_tiles = tiles_n * tiles_m;
+    const uint32_t tiles_n = (N + BN - 1) / BN;
     const uint32_t num_kb = (K + BK - 1) / BK;
     const uint32_t cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+    const bool grouped = row_off != nullptr;
+    // mt_start[e] = number of m-tiles of the experts before e (grouped launches only)
+    uint32_t *mt_start = reinterpret_cast<uint32_t *>(base_ptr + off_pk_b + SP * PK_B + BAR_BYTES);
 
     if (tid == 0) {
+        if (grouped) {
+            uint32_t acc = 0;
+            for (int e = 0; e < num_experts; ++e) {
+                mt_start[e] = acc;
+                const int rows_e = row_off[e + 1] - row_off[e];
+                acc += rows_e > 0 ? ((uint32_t)rows_e + 2 * BMC - 1) / (2 * BMC) : 0u;
+            }
+            mt_start[num_experts] = acc;
+        }
         abort_flag = g_status;
         for (int s = 0; s < SP; ++s) {
             mbar_init(pk_full(s), 1);
@@ -215,6 +240,29 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_acc = tmem_base_slot;
     volatile int *ab = &abort_flag;
+    const uint32_t tiles_m = grouped ? mt_start[num_experts] : (M + 2 * BMC - 1) / (2 * BMC);
+    const uint32_t num_tiles = tiles_n * tiles_m;
+    auto coord = [&](uint32_t tile) {
+        TileCoord c;
+        const uint32_t mt = tile / tiles_n, nt = tile % tiles_n;
+        c.n0 = nt * BN;
+        if (!grouped) {
+            c.a_row = mt * 2 * BMC;
+            c.b_row = c.n0;
+            c.row_end = M;
+        } else {
+            int lo = 0, hi = num_experts - 1;   // last expert whose first m-tile is <= mt (empty experts share a start)
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (mt_start[mid] <= mt) lo = mid;
+                else hi = mid - 1;
+            }
+            c.a_row = (uint32_t)row_off[lo] + (mt - mt_start[lo]) * 2 * BMC;
+            c.b_row = (uint32_t)lo * N + c.n0;
+            c.row_end = (uint32_t)row_off[lo + 1];
+        }
+        return c;
+    };
 
     if (*ab == 0) {
         if (warp == 0) {
@@ -223,8 +271,9 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 Ring pr;
                 bool ok = true;
                 for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters) {
-                    const int ya = (int)((tile / tiles_n) * 2 * BMC + rank * BMC);
-                    const int yb = (int)((tile % tiles_n) * BN + rank * BNC);
+                    const TileCoord tc = coord(tile);
+                    const int ya = (int)(tc.a_row + rank * BMC);
+                    const int yb = (int)(tc.b_row + rank * BNC);
                     for (uint32_t kb = 0; kb < num_kb; ++kb, pr.next(SP)) {
                         const int s = pr.s;
                         ok = mbar_wait(pk_empty(s), pr.ph ^ 1, ab, 41);
@@ -272,7 +321,8 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             bool ok = true;
             for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
                 const uint32_t buf = it & 1;
-                const uint32_t m0 = (tile / tiles_n) * 2 * BMC + rank * BMC, n0 = (tile % tiles_n) * BN;
+                const TileCoord tc = coord(tile);
+                const uint32_t m0 = tc.a_row + rank * BMC, n0 = tc.n0;
                 ok = mbar_wait(acc_full(buf), (it >> 1) & 1, ab, 44);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -286,7 +336,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(acc_empty(buf), 0);
                     }
-                    store_acc_chunk(ep, row, n0 + c * 32, v, M, N, small);
+                    store_acc_chunk(ep, row, n0 + c * 32, v, tc.row_end, N, small);
                 }
             }
         } else {
@@ -405,15 +455,20 @@ static int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t r
 
 }  // namespace tc3
 
-int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                    const Epilogue &ep, cudaStream_t st) {
+// Shared launcher.  row_off == null: one dense [M, N] problem.  Otherwise M is the total number
+// of (expert-sorted) rows, B holds num_experts stacked [N, K/2] weights and row_off[num_experts + 1]
+// lives on the device, so the grid is sized for the worst case (every expert adds a partial tile).
+static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                      const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
     using namespace tc3;
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "matmul: operands must be 16-byte aligned");
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "matmul: K = %lld must be a multiple of 32", (long long)K);
+    const int64_t b_rows = row_off ? N * (int64_t)num_experts : N;
+    SR_REQUIRE(M < (1ll << 31) && b_rows < (1ll << 31), SR_ERR_UNSUPPORTED, "matmul: size out of range");
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K / 2, BMC);
     if (rc) return rc;
-    rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K / 2, BNC);
+    rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)K / 2, BNC);
     if (rc) return rc;
     static int sm_count = 0;
     if (sm_count == 0) {
@@ -422,7 +477,8 @@ int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, in
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    const int64_t tiles = cdiv<int64_t>(N, BN) * cdiv<int64_t>(M, 2 * BMC);
+    const int64_t m_tiles = row_off ? cdiv<int64_t>(M, 2 * BMC) + num_experts : cdiv<int64_t>(M, 2 * BMC);
+    const int64_t tiles = cdiv<int64_t>(N, BN) * m_tiles;
     int64_t clusters = sm_count / 2;
     if (tiles < clusters) clusters = tiles;
     // SIGNROT_B200_TC3_STAGES="<packed ring>,<int8 ring>,<unpack groups>" is a tuning knob
@@ -443,15 +499,28 @@ int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, in
         su = b;
         groups = c;
     }
-    void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, Epilogue);
+    void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, const int32_t *, int,
+                Epilogue);
     if (groups == 1) kfn = a_unsigned ? gemm_tc3_kernel<true, 1> : gemm_tc3_kernel<false, 1>;
     else if (groups == 2) kfn = a_unsigned ? gemm_tc3_kernel<true, 2> : gemm_tc3_kernel<false, 2>;
     else kfn = a_unsigned ? gemm_tc3_kernel<true, 4> : gemm_tc3_kernel<false, 4>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     kfn<<<(unsigned)(2 * clusters), THREADS, smem_bytes(sp, su), st>>>(ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, sp,
-                                                                        su, ep);
+                                                                        su, row_off, num_experts, ep);
     return check_launch("gemm_tc3");
+}
+
+int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                    const Epilogue &ep, cudaStream_t st) {
+    return launch_tc3(A, B, M, N, K, a_unsigned, ep, nullptr, 0, st);
+}
+
+int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
+                            const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
+    SR_REQUIRE(num_experts >= 1 && num_experts <= tc3::MAX_EXPERTS, SR_ERR_UNSUPPORTED,
+               "grouped_linear: at most %d experts", tc3::MAX_EXPERTS);
+    return launch_tc3(A, B, rows, N, K, a_unsigned, ep, row_off, num_experts, st);
 }
 
 int tc3_device_status(int *out, bool clear) {

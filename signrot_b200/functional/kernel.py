@@ -26,7 +26,7 @@ __all__ = [
     "sym_quant_dynamic_moe", "asym_quant_dynamic_moe", "sym_dequant_moe",
     "kv_quant_pack", "rope_qk", "swiglu", "rmsnorm", "sym_dequant",
     "asym_quant_f16_si4", "asym_quant_f16_ui4", "sum_i4", "matmul_colrow_i8_i32",
-    "w4a4_linear", "rotate_quant", "hadamard", "hadamard_heads",
+    "w4a4_linear", "grouped_linear", "rotate_quant", "hadamard", "hadamard_heads",
 ]
 
 
@@ -361,6 +361,44 @@ def matmul_colrow_i8_i32(a_col, b_row) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------------------- fused operators
+
+def grouped_linear(packed: PackedQuantizedTensor, expert_ids, row_offsets, weight, weight_scales, weight_sum=None):
+    """fp16 `dequant(packed[r] @ weight[e_r].T)` for expert-sorted rows in ONE launch: the grouped
+    GEMM plus expert-indexed dequant of the sparse MoE block (signrot/nn/moe.py:114-162,
+    functional/kernel.py:83-110 + 146-159).  `packed` rows sorted by expert, `expert_ids` int32
+    [rows], `row_offsets` int32 [E + 1] (first row of every expert, last entry = rows), `weight`
+    uint8 [E, N, K/2], `weight_scales` fp16 [E, N], `weight_sum` int32 [E, N] when `packed.zeros_x` is set."""
+    qx, sx, zx = packed.quantized_x, packed.scales_x, packed.zeros_x
+    assert qx.dim() == 2 and weight.dim() == 3
+    assert qx.shape[-1] % 16 == 0, "A.shape[-1]: {} must be multiplication of 32".format(qx.shape[-1] * 2)
+    sx = sx.reshape(-1)
+    E, N = weight.shape[0], weight.shape[1]
+    rows, K = qx.shape[0], qx.shape[1] * 2
+    if zx is not None:
+        zx = zx.reshape(-1)
+        if weight_sum is None:
+            raise RuntimeError("grouped_linear: asymmetric activations need weight_sum")
+    dev = require_cuda("grouped_linear", qx, sx, zx, expert_ids, row_offsets, weight, weight_scales,
+                       weight_sum if zx is not None else None)
+    _check_dtype("grouped_linear", qx, torch.uint8)
+    _check_dtype("grouped_linear", weight, torch.uint8)
+    _check_dtype("grouped_linear", sx, torch.float16)
+    _check_dtype("grouped_linear", weight_scales, torch.float16)
+    _check_dtype("grouped_linear", expert_ids, torch.int32)
+    _check_dtype("grouped_linear", row_offsets, torch.int32)
+    if weight.shape[2] != qx.shape[1] or weight_scales.numel() != E * N or sx.numel() != rows \
+            or expert_ids.numel() != rows or row_offsets.numel() != E + 1:
+        raise RuntimeError("grouped_linear: shapes of activations, weights, scales and offsets do not match")
+    if not (qx.is_contiguous() and weight.is_contiguous() and weight_scales.is_contiguous()):
+        raise RuntimeError("grouped_linear: operands must be contiguous")
+    if zx is not None:
+        _check_dtype("grouped_linear", zx, torch.int8)
+        _check_dtype("grouped_linear", weight_sum, torch.int32)
+    out = torch.empty((rows, N), dtype=torch.float16, device=dev)
+    run(dev, "sr_grouped_linear", ptr(qx), ptr(sx), ptr(zx), ptr(expert_ids), ptr(row_offsets), ptr(weight),
+        ptr(weight_scales), ptr(weight_sum) if zx is not None else None, rows, E, N, K, ptr(out))
+    return out
+
 
 def w4a4_linear(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum=None, bias=None):
     """fp16 `dequant(packed @ weight.T) (+ bias)`: the GEMM, the asymmetric zero correction

@@ -87,3 +87,38 @@ def test_cuda_graph_replay():
         torch.cuda.synchronize()
         eager, _ = blk(x)
         assert torch.equal(static_y, eager)
+
+
+@pytest.mark.parametrize("counts,N,K", [
+    ([5, 0, 300, 1, 0, 257, 64, 0], 320, 256),      # empty experts, several m-tiles, ragged N
+    ([0, 0, 700], 256, 4096),                       # leading empty experts
+    ([130] * 16, 768, 512),
+    ([1, 2, 3, 4], 40, 64),
+])
+@pytest.mark.parametrize("asym", [False, True])
+def test_grouped_linear_bit_exact(counts, N, K, asym):
+    """One tensor-core launch for all experts == per-expert integer GEMM + expert-indexed dequant."""
+    E, rows = len(counts), sum(counts)
+    g = torch.Generator().manual_seed(rows + N)
+    lo, hi = (0, 16) if asym else (-8, 8)
+    a = torch.randint(lo, hi, (rows, K), generator=g, dtype=torch.int32)
+    w = torch.randint(-8, 8, (E, N, K), generator=g, dtype=torch.int32)
+    A = oracle.pack_codes(a) if asym else oracle.pack_i4(a)
+    W = oracle.pack_i4(w.view(E * N, K)).view(E, N, K // 2)
+    sa = (torch.rand((rows,), generator=g) * 0.1 + 0.01).half()
+    sw = (torch.rand((E, N), generator=g) * 0.1 + 0.01).half()
+    eid = torch.repeat_interleave(torch.arange(E, dtype=torch.int32), torch.tensor(counts))
+    off = torch.zeros(E + 1, dtype=torch.int32)
+    off[1:] = torch.cumsum(torch.tensor(counts), 0)
+    zero = torch.randint(0, 16, (rows,), generator=g, dtype=torch.int32).to(torch.int8) if asym else None
+    wsum = w.sum(-1).to(torch.int32) if asym else None
+    acc = torch.empty((rows, N), dtype=torch.int32)
+    for e in range(E):
+        sl = slice(int(off[e]), int(off[e + 1]))
+        acc[sl] = a[sl] @ w[e].T
+    want = oracle.sym_dequant_moe(acc, sa.view(-1, 1), sw, eid, zero, wsum)
+    pk = kernel.PackedQuantizedTensor(A.to(DEV), sa.to(DEV), zero.to(DEV) if asym else None)
+    got = kernel.grouped_linear(pk, eid.to(DEV), off.to(DEV), W.to(DEV), sw.to(DEV), wsum.to(DEV) if asym else None)
+    from signrot_b200 import _lib
+    assert _lib.device_status() == 0
+    assert torch.equal(got.cpu(), want)
