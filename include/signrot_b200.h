@@ -88,7 +88,8 @@ int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, co
 /* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
  * 2 = tcgen05 kernel fed by TMA-staged packed tiles, 3 = persistent tcgen05 kernel with
  * register-path unpack, 4 = persistent tcgen05 kernel on CTA pairs (cta_group::2, 256 x 256
- * tiles).  For tests and tuning; no counterpart in the reference. */
+ * tiles), 5 = weight-streaming mma.sync kernel for at most 64 rows (larger M falls through to the
+ * shape rule).  For tests and tuning; no counterpart in the reference. */
 int sr_set_gemm_kernel(int which);
 
 /* ------------------------------------------------------------------ quantizers */

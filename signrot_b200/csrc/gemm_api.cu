@@ -7,9 +7,10 @@
 
 namespace sr {
 
-// 0 = by shape (M <= 32: few-rows kernel, M <= 128: kernel 3, else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
-// 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel.
-// SIGNROT_B200_GEMM=small|tc|tc2|tc3 pins one kernel (used by the parity tests to cover both
+// 0 = by shape (M <= 64: kernel 5, M <= 128: kernel 3, else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
+// 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel,
+// 5 = weight-streaming mma.sync kernel of the decode regime (M <= 64).
+// SIGNROT_B200_GEMM=small|tc|tc2|tc3|skinny pins one kernel (used by the parity tests to cover both
 // kernels at every shape); sr_set_gemm_kernel() does the same from code.
 static int g_force = -1;
 static int forced_kernel() {
@@ -20,6 +21,7 @@ static int forced_kernel() {
         if (e && !strcmp(e, "tc")) g_force = 2;
         if (e && !strcmp(e, "tc2")) g_force = 3;
         if (e && !strcmp(e, "tc3")) g_force = 4;
+        if (e && !strcmp(e, "skinny")) g_force = 5;
     }
     return g_force;
 }
@@ -34,7 +36,10 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     SR_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K <= 131072, SR_ERR_UNSUPPORTED, "%s: size out of range", who);
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "%s: operands must be 16-byte aligned", who);
     const int f = forced_kernel();
-    const bool small = f == 1 || (f == 0 && M <= 32);
+    if ((f == 5 || f == 0) && M <= 64)
+        return launch_gemm_skinny((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
+                                  as_stream(stream));
+    const bool small = f == 1;
     if (small)
         return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                  as_stream(stream));
@@ -52,7 +57,8 @@ using namespace sr;
 extern "C" {
 
 int sr_set_gemm_kernel(int which) {
-    SR_REQUIRE(which >= 0 && which <= 4, SR_ERR_INVALID, "set_gemm_kernel: expected 0 (auto), 1 (few rows), 2, 3 or 4 (tcgen05 kernels)");
+    SR_REQUIRE(which >= 0 && which <= 5, SR_ERR_INVALID,
+               "set_gemm_kernel: expected 0 (auto), 1 (few rows, dp4a), 2, 3, 4 (tcgen05 kernels) or 5 (few rows, mma)");
     g_force = which;
     return SR_OK;
 }

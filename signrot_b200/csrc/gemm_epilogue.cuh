@@ -93,6 +93,8 @@ __device__ __forceinline__ void store_acc_chunk(const Epilogue &ep, uint32_t row
 
 int launch_gemm_small(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                       const Epilogue &ep, cudaStream_t st);
+int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                       const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                    const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc2(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,

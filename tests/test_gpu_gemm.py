@@ -28,7 +28,7 @@ SHAPES = [(1, 4096, 4096), (16, 4096, 4096), (3, 64, 40), (33, 256, 96), (128, 4
           (200, 1024, 300), (129, 14336, 264), (512, 2048, 14336), (64, 14336, 256), (16, 14336, 4096)]
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta"])
+@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
 @pytest.mark.parametrize("M,K,N", SHAPES)
 def test_matmul_si4_bit_exact(which, M, K, N):
     if which == 1 and M * N * K > 16 * 14336 * 4096 * 4:
@@ -41,7 +41,7 @@ def test_matmul_si4_bit_exact(which, M, K, N):
     assert torch.equal(C, oracle.matmul_i4(A, B))
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta"])
+@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
 def test_matmul_ui4_and_extremes(which):
     _lib.call_nostream("sr_set_gemm_kernel", which)
     M, K, N = 130, 1024, 257 + 7
@@ -69,7 +69,7 @@ def test_matmul_leading_dims_and_empty():
     assert E.shape == (0, 10)
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta"])
+@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
 @pytest.mark.parametrize("M,K,N,asym,bias", [(16, 4096, 4096, False, False), (200, 1024, 264, False, True),
                                              (130, 2048, 512, True, False), (7, 256, 40, True, True)])
 def test_w4a4_linear_fused_epilogue(which, M, K, N, asym, bias):
