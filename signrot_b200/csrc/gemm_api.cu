@@ -7,7 +7,7 @@
 
 namespace sr {
 
-// 0 = by shape (M <= 64: kernel 5, M <= 128: kernel 3, else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
+// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; M <= 128: kernel 3; else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
 // 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel,
 // 5 = weight-streaming mma.sync kernel of the decode regime (M <= 64).
 // SIGNROT_B200_GEMM=small|tc|tc2|tc3|skinny pins one kernel (used by the parity tests to cover both
@@ -36,7 +36,8 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     SR_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K <= 131072, SR_ERR_UNSUPPORTED, "%s: size out of range", who);
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "%s: operands must be 16-byte aligned", who);
     const int f = forced_kernel();
-    if ((f == 5 || f == 0) && M <= 64)
+    // auto: the mma.sync rate bounds that kernel at about 32 rows; wide outputs go to the tcgen05 kernels earlier
+    if ((f == 5 && M <= 64) || (f == 0 && (M <= 32 || (M <= 64 && N <= 8192))))
         return launch_gemm_skinny((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                   as_stream(stream));
     const bool small = f == 1;
