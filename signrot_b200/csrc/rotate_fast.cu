@@ -30,6 +30,8 @@
 // CTAs are persistent over rows; a thread's sign masks live in its own shared-memory row.
 #include "rotate.cuh"
 #include <cfloat>
+#include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 namespace sr {
@@ -262,6 +264,16 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
 }  // namespace
 
 int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
+    // SIGNROT_B200_ROTATE=butterfly keeps the butterfly kernels (A/B runs); default: tensor-core transform first
+    static int use_tc = -1;
+    if (use_tc < 0) {
+        const char *e = getenv("SIGNROT_B200_ROTATE");
+        use_tc = (e && !strcmp(e, "butterfly")) ? 0 : 1;
+    }
+    if (use_tc) {
+        const int rc = launch_rotate_tc4096(a, st);
+        if (rc != SR_ERR_UNSUPPORTED) return rc;
+    }
     const bool shape_ok = a.n == 4096 && a.K == 1 && a.stride == 1 && a.S == 4096 && a.q != nullptr &&
                           !a.fp32_mode && (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) &&
                           aligned16(a.x) && aligned4(a.q) && (a.out == nullptr || a.out_dtype == SR_F16);

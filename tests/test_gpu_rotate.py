@@ -147,3 +147,36 @@ def test_rotation_is_orthogonal_at_full_size():
         assert torch.allclose(y.norm(dim=-1), x.float().norm(dim=-1), rtol=1e-4)
         z = kernel.hadamard(y, hadK, K)
         assert torch.allclose(z, x.float(), atol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("clip", [1.0, 0.9])
+def test_rotate_quant_4096_asym_full_width(dtype, clip):
+    """Full-width rotation with asymmetric codes (the tensor-core kernel's second code path)."""
+    x = _x(37, 4096, 11, dtype)
+    sign = (torch.randint(0, 2, (4096,), generator=torch.Generator().manual_seed(5)) * 2 - 1).to(torch.int8)
+    pk, rot = kernel.rotate_quant(x.to(DEV), None, 1, sign=sign.to(DEV), asym=True, clip_ratio=clip,
+                                  return_rotated=True)
+    want_rot = oracle.rotate(x, None, 1, sign, cast_in_to_f16=True, out_dtype=torch.float16)
+    _ulp_close(rot.cpu(), want_rot)
+    q2, s2, z2 = kernel.asym_quant_dynamic(rot, clip)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    assert torch.equal(z2.to(torch.int8), pk.zeros_x)
+
+
+@pytest.mark.parametrize("rows", [300, 4096])
+def test_rotate_quant_4096_many_rows_self_consistent(rows):
+    """Every row of a launch that keeps all SMs busy for several rounds: the packed codes are
+    exactly the stand-alone quantizer applied to the rotated rows the same launch wrote, and
+    those rows equal the stand-alone rotation."""
+    x = _x(rows, 4096, 13, torch.bfloat16).to(DEV)
+    sign = (torch.randint(0, 2, (4096,), generator=torch.Generator().manual_seed(6)) * 2 - 1).to(torch.int8).to(DEV)
+    pk, rot = kernel.rotate_quant(x, None, 1, sign=sign, return_rotated=True)
+    q2, s2 = kernel.sym_quant_dynamic(rot)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    pk2 = kernel.rotate_quant(x, None, 1, sign=sign)
+    assert torch.equal(pk2.quantized_x, pk.quantized_x) and torch.equal(pk2.scales_x, pk.scales_x)
+    ref = kernel.hadamard(x.half(), None, 1) * sign.to(torch.float16)
+    diff = (rot.float() - ref.float()).abs()
+    tol = rot.float().abs() * 2.0 ** -10 + rot.float().abs().amax(dim=-1, keepdim=True) * 2.0 ** -17
+    assert (diff > tol).float().mean().item() <= 1e-5
