@@ -209,8 +209,9 @@ rotate_quant_4096_tc_kernel(const InT *__restrict__ x, const int8_t *__restrict_
                     float r[4];
                     unpack2(sub2(u2[hl][0], pack2(__uint_as_float(hi[0]), __uint_as_float(hi[1]))), r[0], r[1]);
                     unpack2(sub2(u2[hl][1], pack2(__uint_as_float(hi[2]), __uint_as_float(hi[3]))), r[2], r[3]);
+                    // the tensor core reads the upper 19 bits of a tf32 operand: the remainder needs no mask
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) lo[i] = __float_as_uint(r[i]) & 0xFFFFE000u;
+                    for (int i = 0; i < 4; ++i) lo[i] = __float_as_uint(r[i]);
                     // A slots: a0 = (line g, k qd) = l 2 qd; a1 = (line g + 8, k qd); a2 = (line g, k qd + 4) = l 2 qd + 1; a3
                     mma_1688_tf32<false>(c2[hl][nt], hi[0], hi[2], hi[1], hi[3], b2_0, b2_1);
                     mma_1688_tf32<true>(c2[hl][nt], lo[0], lo[2], lo[1], lo[3], b2_0, b2_1);
@@ -338,11 +339,15 @@ rotate_quant_4096_tc_kernel(const InT *__restrict__ x, const int8_t *__restrict_
                         if (CLAMP) qh = __hmin2(__hmax2(qh, lo_c), hi_c);
                         bits[i] = h2_bits(__hadd2(qh, mg));
                         if (ASYM) bits[i] += zero_u;
-                        bits[i] &= 0x000F000Fu;
                     }
-                    // bits[i] = (code of l + 1) << 16 | code of l: byte i of the word = lo | hi << 4
-                    const uint32_t p01 = bits[0] + (bits[1] << 8), p23 = bits[2] + (bits[3] << 8);
-                    const uint32_t ev = __byte_perm(p01, p23, 0x5410), od = __byte_perm(p01, p23, 0x7632);
+                    // the sum lies in [1536, 1552): the low BYTE of each half is the code (+ zero point), the
+                    // rest is constant.  Gather the bytes: x = [l0, l1, h0, h1] of two pairs, then evens and odds.
+                    const uint32_t x01 = __byte_perm(bits[0], bits[1], 0x6240), x23 = __byte_perm(bits[2], bits[3], 0x6240);
+                    uint32_t ev = __byte_perm(x01, x23, 0x5410), od = __byte_perm(x01, x23, 0x7632);
+                    if (ASYM) {
+                        ev &= 0x0F0F0F0Fu;
+                        od &= 0x0F0F0F0Fu;
+                    }
                     w[part] = ev + (od << 4);
                 }
                 if (!ASYM) {
