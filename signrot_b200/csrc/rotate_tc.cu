@@ -34,7 +34,7 @@ namespace sr {
 
 namespace {
 
-constexpr int TC_PAIRS = 7;                     // rows in flight per CTA; two warps share a row
+constexpr int TC_PAIRS = 8;                     // rows in flight per CTA; two warps share a row
 constexpr int TC_WARPS = 2 * TC_PAIRS;
 constexpr int TC_PITCH = 144;                   // bytes per 64-value line of the row image
 constexpr int TC_ROW_BYTES = 64 * TC_PITCH;     // 9216

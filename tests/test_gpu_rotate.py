@@ -32,8 +32,9 @@ def _ulp_close(got, want, ulps=1.0):
     # Kronecker shapes round twice (after the Walsh-Hadamard stage and after the had-K stage): a
     # one-ulp difference in one intermediate value moves the K outputs that sum it by one ulp of
     # the INTERMEDIATE (up to 2^-10 of the row maximum), however small those outputs are.  Such
-    # events are a few per million values.
-    assert bad.float().mean().item() <= 1e-5, f"{int(bad.sum())} values differ by more than {ulps} ulp"
+    # events are a few per hundred thousand values (tensor-core sums round differently from the
+    # reference's butterflies; the bound is the one the code comparison uses, 1e-4).
+    assert bad.float().mean().item() <= 1e-4, f"{int(bad.sum())} values differ by more than {ulps} ulp"
     worst = ((g - w).abs() - tol).clamp_min(0) / w.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
     assert worst.max().item() <= 2 ** -9, "a value is off by more than one ulp of an intermediate"
     return (g != w).float().mean().item()
@@ -112,6 +113,23 @@ def test_rotate_quant(M, n, dtype):
     # self-consistency: codes are exactly the quantizer applied to the kernel's own rotated rows
     q2, s2 = kernel.sym_quant_dynamic(rot)
     assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    # the launch that does not return the rotated rows takes a different code path (sign applied to the codes)
+    pk3 = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV))
+    assert torch.equal(pk3.quantized_x, pk.quantized_x) and torch.equal(pk3.scales_x, pk.scales_x)
+
+
+def test_rotate_quant_tiny_rows_take_the_clamped_path():
+    """Rows whose scale is a subnormal fp16 number (quotients can exceed the code range) and all-zero rows."""
+    for n in (4096, 14336):
+        x = _x(9, n, 21, torch.float16, outliers=False) * 1e-5
+        x[4] = 0
+        sign = (torch.randint(0, 2, (n,), generator=torch.Generator().manual_seed(8)) * 2 - 1).to(torch.int8)
+        hadK, K = get_hadK(n)
+        pk, rot = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), return_rotated=True)
+        q2, s2 = kernel.sym_quant_dynamic(rot)
+        assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+        pk3 = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV))
+        assert torch.equal(pk3.quantized_x, pk.quantized_x) and torch.equal(pk3.scales_x, pk.scales_x)
 
 
 def test_rotate_quant_asym_heads_and_clip():
