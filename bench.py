@@ -357,7 +357,7 @@ def run_ours(args, rank, world, local_rank):
                      "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
                      "frac": round(gemm_ach / int8_peak, 4),
                      "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",
-                     "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "traffic": None,
+                     "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "traffic": 106.75e6, "traffic_note": "dram read+write of one M=4096 K=4096 N=14336 launch under ncu (profiles/gemm_tc3_kernel_m4096_k4096_n14336.md); algorithmic 155 MB, the rest of the fp16 output is still in L2 when the kernel ends",
                      "per_shape_ms": [round(v, 4) for v in gemm_ms],
                      "per_shape_tops": [round(o / (t * 1e-3) / 1e12, 1) for o, t in zip(gemm_ops, gemm_ms)]},
         "rotate_quant": {"kernel": "fused rotate+sign+quant", "bound": "hbm", "achieved": round(rot_ach, 1),
