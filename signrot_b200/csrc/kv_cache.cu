@@ -17,25 +17,12 @@
 //  * quantisation of new K/V (with the Hadamard on K) happens in the kernel that
 //    writes the page slot.
 #include "common.cuh"
+#include "kv_cache.cuh"
 #include <cfloat>
+#include <cstdlib>
+#include <cstring>
 
 namespace sr {
-
-struct PagedKV {
-    uint8_t *data;
-    __half2 *param;
-    const int32_t *indptr, *indices, *last_page_offset;
-    uint32_t num_layers, layer, heads, page_size;  // head_dim fixed to 128
-
-    __device__ __forceinline__ size_t vec_index(uint32_t page, uint32_t kv, uint32_t head, uint32_t entry) const {
-        return ((((size_t)page * num_layers + layer) * 2 + kv) * heads + head) * page_size + entry;
-    }
-    __device__ __forceinline__ uint32_t seq_len(uint32_t b) const {
-        return (uint32_t)(indptr[b + 1] - indptr[b] - 1) * page_size + (uint32_t)last_page_offset[b];
-    }
-};
-
-constexpr int HD = 128;
 
 // ------------------------------------------------------------------ scatter of pre-quantised vectors
 
@@ -147,12 +134,6 @@ kv_append_quant_kernel(PagedKV kv, const __half *__restrict__ k, const __half *_
 }
 
 // ------------------------------------------------------------------ decode attention
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 // 4-bit code -> fp32 without the conversion pipe (2^23 + n has n in its low mantissa bits).
 __device__ __forceinline__ float nib2f(uint32_t w) { return __uint_as_float(0x4B000000u | (w & 15u)) - 8388608.f; }
@@ -466,7 +447,14 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
     __half *op = (__half *)o;
     float *tp = (float *)tmp;
     const uint32_t nc = (uint32_t)num_chunks;
-    switch (G) {
+    // SIGNROT_B200_DECODE=scalar keeps the CUDA-core kernel (A/B runs); default: tensor-core kernel when it applies
+    static int use_tc = -1;
+    if (use_tc < 0) {
+        const char *e = getenv("SIGNROT_B200_DECODE");
+        use_tc = (e && !strcmp(e, "scalar")) ? 0 : 1;
+    }
+    const bool took = use_tc && launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st);
+    if (!took) switch (G) {
         case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 4: decode_kernel<4><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;

@@ -1,0 +1,297 @@
+// Split-KV GQA decode attention over the int4 paged cache, with both products on the tensor cores.
+//
+// Replaces kernels/flashinfer.cu:11-106 + include/flashinfer/decode.cuh:481-751 (one query token per
+// request against a quantized paged cache) with the same workspace format as the CUDA-core kernel in
+// kv_cache.cu: per (request, q head, chunk) 128 unnormalised outputs, the running maximum and the sum.
+//
+// grid (batch, kv heads, chunks), 4 warps; a warp takes blocks of 16 cached tokens (block index
+// = warp, warp + 4, ... inside the chunk's pages) and keeps the flash-decoding state of all q heads
+// of the group (rows of an m16 tile; rows >= G stay zero).
+//
+// The 4-bit codes never become numbers on the CUDA cores.  A code n masked into the low bits of an
+// fp16 lane IS the subnormal n * 2^-24, which mma.sync.m16n8k16 multiplies exactly; the affine
+// dequantisation is applied around the products:
+//   scores  x_t = (s_t 2^24) (q' . c_t 2^-24) - z_t sum(q')            (q' = q * log2(e) / sqrt(d))
+//   output  O_d = 2^24 sum_t (p_t vs_t) (c_td 2^-24) - sum_t p_t vz_t
+// K operand: lane (g, qd) loads bytes 16 qd .. 16 qd + 15 of token g's row, (w >> 4i) & 0x000F000F
+// are the fp16 pairs (dims i, i + 4 of a word); the permutation of the head dimension is baked into
+// the q fragments.  V operand: pairs run over tokens, so the rows of tokens 2 qd and 2 qd + 1 are
+// merged byte-wise, (A & 0x0F..) | ((B << 4) & 0xF0..), and a byte broadcast + mask 0x00F0000F gives
+// the pair (n_A 2^-24, n_B 2^-20); the factor 16 is taken off p for the odd token.
+#include "kv_cache.cuh"
+#include <cfloat>
+
+namespace sr {
+
+namespace {
+
+constexpr int DT_WARPS = 4;
+constexpr int DT_BLOCK = 16;   // cached tokens per warp iteration
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// logical head dimension of physical operand slot (k-step ks, quad lane qd, register reg, half h) of the K product
+__device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
+    const int w = ks >> 1, i = 2 * (ks & 1) + reg;
+    return 32 * qd + 8 * w + i + 4 * h;
+}
+
+template <int G>
+__global__ void __launch_bounds__(DT_WARPS * 32)
+decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
+                 uint32_t num_chunks, int had_q, float had_scale) {
+    const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
+    const uint32_t hq_total = gridDim.y * G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, qd = lane & 3;
+
+    __shared__ float sh_q[G][HD];
+    __shared__ float sh_o[DT_WARPS][G][HD];
+    __shared__ float sh_md[DT_WARPS][G][2];
+
+    // ---- q (optionally Hadamard-rotated, kv_cache.py:157-158), one warp per q head
+    const float sm_scale = 1.44269504088896340736f * 0.08838834764831845f;  // log2(e) / sqrt(128)
+    for (int gg = warp; gg < G; gg += DT_WARPS) {
+        const uint32_t hq = hk * G + gg;
+        const __half *qp = q + ((size_t)b * hq_total + hq) * HD + lane * 4;
+        const uint2 raw = *reinterpret_cast<const uint2 *>(qp);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+        float a[4] = {__half2float(h01.x), __half2float(h01.y), __half2float(h23.x), __half2float(h23.y)};
+        if (had_q) {
+            float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
+            a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float ot = __shfl_xor_sync(0xffffffffu, a[j], m);
+                    a[j] = (lane & m) ? (ot - a[j]) : (a[j] + ot);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
+        }
+        // the products take q' as fp16: round once here so that sum(q') below is the sum of what is multiplied
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sh_q[gg][lane * 4 + j] = __half2float(__float2half_rn(a[j] * sm_scale));
+    }
+    __syncthreads();
+
+    // A fragments of q' (rows g < G; rows g + 8 are zero) in the K product's dimension order, and sum(q') per head
+    uint32_t qa[8][2];
+    float qsum = 0.f;
+    {
+        const int gq = g < G ? g : 0;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int reg = 0; reg < 2; ++reg) {
+                const float lo = sh_q[gq][k_dim(ks, qd, reg, 0)], hi = sh_q[gq][k_dim(ks, qd, reg, 1)];
+                qa[ks][reg] = g < G ? pack_h2(lo, hi) : 0u;
+            }
+        float s = 0.f;
+        for (int j = 0; j < 32; ++j) s += sh_q[gq][qd * 32 + j];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        qsum = s;
+    }
+
+    // ---- this chunk's token range (whole pages, as the CUDA-core kernel splits them)
+    const uint32_t page_begin = (uint32_t)kv.indptr[b], page_end = (uint32_t)kv.indptr[b + 1];
+    const uint32_t pages_total = page_end - page_begin;
+    const uint32_t per_chunk = (pages_total + num_chunks - 1) / num_chunks;
+    const uint32_t cp_begin = min(chunk * per_chunk, pages_total), cp_end = min(cp_begin + per_chunk, pages_total);
+    const uint32_t last_valid = (uint32_t)kv.last_page_offset[b];
+    const uint32_t blocks_per_page = kv.page_size / DT_BLOCK;
+    const uint32_t num_blocks = (cp_end - cp_begin) * blocks_per_page;
+
+    float m_run = -5e4f, d_run = 0.f, z_run = 0.f;   // head g: running max (quad-uniform), this lane's part of sum p and sum p vz
+    float acc[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+
+    struct Stage {
+        uint4 k[2];      // K rows of tokens g and 8 + g, bytes 16 qd ..
+        uint2 v[4];      // V rows of tokens 2 qd, 2 qd + 1, 8 + 2 qd, 9 + 2 qd, bytes 8 g ..
+        __half2 kp[4];   // (scale, zero) of K for tokens 2 qd, 2 qd + 1, 8 + 2 qd, 9 + 2 qd
+        __half2 vp[4];
+        uint32_t valid;  // tokens of the block that exist
+    };
+    auto load = [&](uint32_t blk, Stage &s) {
+        const uint32_t pi = cp_begin + blk / blocks_per_page, e0 = (blk % blocks_per_page) * DT_BLOCK;
+        const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
+        const uint32_t valid_page = (pi == pages_total - 1) ? last_valid : kv.page_size;
+        s.valid = valid_page > e0 ? min(valid_page - e0, (uint32_t)DT_BLOCK) : 0u;
+        const size_t kbase = kv.vec_index(page, 0, hk, e0), vbase = kv.vec_index(page, 1, hk, e0);
+        // rows past the end of a partially filled page belong to the same allocation: they are read and masked
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+            s.k[t] = __ldg(reinterpret_cast<const uint4 *>(kv.data + (kbase + 8 * t + g) * 64) + qd);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t tok = 8 * (t >> 1) + 2 * qd + (t & 1);
+            s.v[t] = __ldg(reinterpret_cast<const uint2 *>(kv.data + (vbase + tok) * 64) + g);
+            s.kp[t] = kv.param[kbase + tok];
+            s.vp[t] = kv.param[vbase + tok];
+        }
+    };
+
+    Stage cur, nxt;
+    if ((uint32_t)warp < num_blocks) load(warp, cur);
+    for (uint32_t blk = warp; blk < num_blocks; blk += DT_WARPS) {
+        if (blk + DT_WARPS < num_blocks) load(blk + DT_WARPS, nxt);
+
+        // ---- scores of 16 tokens: two n-tiles of 8 tokens, 8 k-steps over the head dimension
+        float sc[2][4];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+            const uint32_t w[4] = {cur.k[t].x, cur.k[t].y, cur.k[t].z, cur.k[t].w};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t word = w[ks >> 1];
+                const int i = 2 * (ks & 1);
+                const uint32_t b0 = (word >> (4 * i)) & 0x000F000Fu, b1 = (word >> (4 * i + 4)) & 0x000F000Fu;
+                mma_f16(sc[t], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            }
+        }
+        // lane holds head g, tokens 2 qd, 2 qd + 1 (tile 0) and 8 + 2 qd, 9 + 2 qd (tile 1)
+        float x[4], p[4];
+        float bmax = -5e4f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float2 kp = __half22float2(cur.kp[t]);
+            const uint32_t tok = 8 * (t >> 1) + 2 * qd + (t & 1);
+            x[t] = sc[t >> 1][t & 1] * (kp.x * 16777216.f) - kp.y * qsum;
+            if (tok >= cur.valid) x[t] = -5e4f;
+            bmax = fmaxf(bmax, x[t]);
+        }
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+        bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+        const float m_new = fmaxf(m_run, bmax);
+        // the running maximum moves in few blocks: the rescale of the 64 accumulators is skipped when no lane needs it
+        if (__any_sync(0xffffffffu, m_new > m_run)) {
+            const float alpha = ex2(m_run - m_new);
+            d_run *= alpha;
+            z_run *= alpha;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                acc[j][0] *= alpha;
+                acc[j][1] *= alpha;
+            }
+            m_run = m_new;
+        }
+        uint32_t pa[2];
+        {
+            float pv[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                // slots past the end of a page hold whatever was there before: their parameters are not numbers to trust
+                const bool live = (uint32_t)(8 * (t >> 1) + 2 * qd + (t & 1)) < cur.valid;
+                const float2 vp = live ? __half22float2(cur.vp[t]) : make_float2(0.f, 0.f);
+                p[t] = live ? ex2(x[t] - m_run) : 0.f;
+                d_run += p[t];
+                z_run = fmaf(p[t], vp.y, z_run);
+                // odd tokens carry their codes 16 times too large (see the V operand below)
+                pv[t] = p[t] * vp.x * ((t & 1) ? 0.0625f : 1.f);
+            }
+            pa[0] = pack_h2(pv[0], pv[1]);
+            pa[1] = pack_h2(pv[2], pv[3]);
+        }
+        // ---- output: 16 n-tiles of 8 dims; lane's bytes 8 g .. 8 g + 7 of four token rows
+        uint32_t even[2][2], odd[2][2];   // [token pair][word]: bytes = (code of the even token, code of the odd token << 4)
+#pragma unroll
+        for (int tp = 0; tp < 2; ++tp) {
+            const uint32_t ax = cur.v[2 * tp].x, ay = cur.v[2 * tp].y, bx = cur.v[2 * tp + 1].x, by = cur.v[2 * tp + 1].y;
+            even[tp][0] = (ax & 0x0F0F0F0Fu) | ((bx << 4) & 0xF0F0F0F0u);
+            even[tp][1] = (ay & 0x0F0F0F0Fu) | ((by << 4) & 0xF0F0F0F0u);
+            odd[tp][0] = ((ax >> 4) & 0x0F0F0F0Fu) | (bx & 0xF0F0F0F0u);
+            odd[tp][1] = ((ay >> 4) & 0x0F0F0F0Fu) | (by & 0xF0F0F0F0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            // n-tile j <-> nibble j of the lane's 16: byte j / 2 (word j / 8), low (even j) or high (odd j) nibble
+            const int byte = (j >> 1) & 3, word = j >> 3;
+            const uint32_t sel = (uint32_t)(byte | (byte << 8));
+            const uint32_t s0 = (j & 1) ? odd[0][word] : even[0][word];
+            const uint32_t s1 = (j & 1) ? odd[1][word] : even[1][word];
+            const uint32_t b0 = __byte_perm(s0, s0, sel) & 0x00F0000Fu;
+            const uint32_t b1 = __byte_perm(s1, s1, sel) & 0x00F0000Fu;
+            mma_f16(acc[j], pa[0], 0u, pa[1], 0u, b0, b1);
+        }
+        cur = nxt;
+    }
+
+    // ---- fold the warp's state: sums across the quad, the 2^24 of the subnormal codes, the zero points
+    d_run += __shfl_xor_sync(0xffffffffu, d_run, 1);
+    d_run += __shfl_xor_sync(0xffffffffu, d_run, 2);
+    z_run += __shfl_xor_sync(0xffffffffu, z_run, 1);
+    z_run += __shfl_xor_sync(0xffffffffu, z_run, 2);
+    if (g < G) {
+        float *so = &sh_o[warp][g][0];
+        // n-tile j, column 2 qd + h of the accumulator <-> dim 16 (2 qd + h) + j
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            so[16 * (2 * qd) + j] = acc[j][0] * 16777216.f - z_run;
+            so[16 * (2 * qd + 1) + j] = acc[j][1] * 16777216.f - z_run;
+        }
+        if (qd == 0) {
+            sh_md[warp][g][0] = m_run;
+            sh_md[warp][g][1] = d_run;
+        }
+    }
+    __syncthreads();
+    // thread t finalises dim t (HD == blockDim) for every head of the group
+    for (int gg = 0; gg < G; ++gg) {
+        float mm = sh_md[0][gg][0];
+#pragma unroll
+        for (int w = 1; w < DT_WARPS; ++w) mm = fmaxf(mm, sh_md[w][gg][0]);
+        float dd = 0.f, oo = 0.f;
+#pragma unroll
+        for (int w = 0; w < DT_WARPS; ++w) {
+            const float scl = ex2(sh_md[w][gg][0] - mm);
+            dd += sh_md[w][gg][1] * scl;
+            oo += sh_o[w][gg][tid] * scl;
+        }
+        const uint32_t hq = hk * G + gg;
+        if (num_chunks == 1) {
+            o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+        } else {
+            float *dst = tmp + (((size_t)b * hq_total + hq) * num_chunks + chunk) * (HD + 4);
+            dst[tid] = oo;
+            if (tid == 0) {
+                dst[HD] = mm;
+                dst[HD + 1] = dd;
+            }
+        }
+    }
+}
+
+}  // namespace
+
+bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
+                      int had_q, float had_scale, cudaStream_t st) {
+    if (kv.page_size % DT_BLOCK != 0) return false;
+    switch (G) {
+        case 1: decode_tc_kernel<1><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
+        case 2: decode_tc_kernel<2><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
+        case 4: decode_tc_kernel<4><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
+        case 8: decode_tc_kernel<8><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
+        default: return false;
+    }
+    return true;
+}
+
+}  // namespace sr
