@@ -27,6 +27,9 @@ namespace {
 
 constexpr int DT_WARPS = 4;
 constexpr int DT_BLOCK = 16;   // cached tokens per warp iteration
+#ifndef DT_MIN_CTAS
+#define DT_MIN_CTAS 3
+#endif
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {
@@ -47,7 +50,7 @@ __device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
 }
 
 template <int G>
-__global__ void __launch_bounds__(DT_WARPS * 32)
+__global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
                  uint32_t num_chunks, int had_q, float had_scale) {
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
@@ -157,6 +160,8 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         float sc[2][4];
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
+            // two accumulators per tile (even and odd k-steps) halve the chain of dependent MMAs
+            float s2[4] = {0.f, 0.f, 0.f, 0.f};
             sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
             const uint32_t w[4] = {cur.k[t].x, cur.k[t].y, cur.k[t].z, cur.k[t].w};
 #pragma unroll
@@ -164,8 +169,11 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
                 const uint32_t word = w[ks >> 1];
                 const int i = 2 * (ks & 1);
                 const uint32_t b0 = (word >> (4 * i)) & 0x000F000Fu, b1 = (word >> (4 * i + 4)) & 0x000F000Fu;
-                mma_f16(sc[t], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                if (ks & 1) mma_f16(s2, qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                else mma_f16(sc[t], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
             }
+            sc[t][0] += s2[0];
+            sc[t][1] += s2[1];
         }
         // lane holds head g, tokens 2 qd, 2 qd + 1 (tile 0) and 8 + 2 qd, 9 + 2 qd (tile 1)
         float x[4], p[4];
