@@ -410,10 +410,64 @@ def run_kernel_case(name: str):
         for _ in range(5):
             attend = cache.update(kk[:, :1].contiguous(), kk[:, :1].contiguous(), 0)
             attend(q)
+    elif name == "decode_layer":
+        from signrot_b200.transformers import kv_cache as kvc
+        B, Hq, Hkv, T, page = 16, 32, 8, 4096, 256
+        cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 64, dev, 1, Hkv, 128, group_size=Hq // Hkv)
+        g = torch.Generator().manual_seed(0)
+        kk = torch.randn((B, T, Hkv, 128), generator=g).half().to(dev)
+        cache.update(kk, kk, 0)
+        cache.refresh_specs()
+        layer = build_decode_layer(cache, B, Hq, Hkv, dev)
+        for _ in range(3):
+            layer()
     else:
         raise SystemExit(f"unknown kernel case {name}")
     torch.cuda.synchronize()
     print(f"kernel case {name}: done")
+
+
+def build_decode_layer(cache, B, Hq, Hkv, dev):
+    """Closure running one decode step of a Llama-3-8B-shaped decoder layer (hidden 4096, FFN 14336,
+    head_dim 128) on `cache` (already holding the context): RMSNorm, quantizer, q/k/v, RoPE, fused
+    KV append, int4 decode attention, head-wise rotation + o_proj, RMSNorm, quantizer, gate/up,
+    SwiGLU, had28 rotation + down_proj, residuals."""
+    from signrot_b200 import nn as snn
+    from signrot_b200.functional import kernel
+    from signrot_b200.functional.hadamard import get_hadK
+    hid, ffn, D = 4096, 14336, 128
+    gen = torch.Generator().manual_seed(2)
+
+    def qlin(k_, n_):
+        m_ = snn.Linear4bit(k_, n_).to(dev)
+        m_.weight.copy_(torch.randint(0, 256, (n_, k_ // 2), generator=gen, dtype=torch.uint8))
+        m_.weight_scales = (torch.rand((n_, 1), generator=gen) * 0.5 / k_ + 0.5 / k_).half().to(dev)
+        return m_
+    lq, lk, lv, lo = qlin(hid, Hq * D), qlin(hid, Hkv * D), qlin(hid, Hkv * D), qlin(Hq * D, hid)
+    lg, lu, ld = qlin(hid, ffn), qlin(hid, ffn), qlin(ffn, hid)
+    norm, quant = snn.RMSNorm(hid, eps=1e-5).to(dev), snn.Quantizer()
+    had28, K28 = get_hadK(ffn)
+    had28 = had28.to(dev, torch.float16)
+    sg_down = (torch.randint(0, 2, (ffn,), generator=gen) * 2 - 1).to(torch.int8).to(dev)
+    ang = torch.rand((1, 1, D), generator=gen)
+    cos, sin = torch.cos(ang).half().to(dev), torch.sin(ang).half().to(dev)   # [1, T = 1, D]
+    xdec = torch.randn((B, 1, hid), generator=gen).half().to(dev)
+    cache.freeze_specs(True)
+
+    def decode_layer():
+        h = norm(xdec)
+        pkd = quant(h)
+        qd_ = lq(pkd).view(B, 1, Hq, D)
+        kd_ = lk(pkd).view(B, 1, Hkv, D)
+        vd_ = lv(pkd).view(B, 1, Hkv, D)
+        kernel.rope_qk(qd_, kd_, cos, sin)
+        attend = cache.update(kd_, vd_, 0)
+        a_ = attend(qd_).reshape(B, 1, Hq * D)
+        x1 = xdec + lo(kernel.rotate_quant(a_, heads=Hq))
+        pk2 = quant(norm(x1))
+        mid = kernel.swiglu(lg(pk2), lu(pk2))
+        return x1 + ld(kernel.rotate_quant(mid, had28, K28, sign=sg_down))
+    return decode_layer
 
 
 def _time_cuda(fn, iters=30, warmup=5, graph=True):
@@ -497,9 +551,21 @@ def run_sweep():
                       "chunks": chunks, "decode_us": round(t_dec * 1e3, 2),
                       "kv_gbs": round(kv_bytes / t_dec / 1e6, 1), "frac_hbm": round(kv_bytes / t_dec / 1e6 / hbm, 3),
                       "prefill_append_quant_us": round(t_fill * 1e3, 1)}))
+    # config 4 (one layer of it): decode step of a Llama-3-8B-shaped decoder layer, batch 16 at context 4096,
+    # int4 weights + int4 paged KV cache, every operator from this package, replayed from one CUDA graph
+    decode_layer = build_decode_layer(cache, B, Hq, Hkv, dev)
+    hid, ffn, D = 4096, 14336, 128
+    try:
+        t_layer = _time_cuda(decode_layer, iters=20, warmup=3)
+        w_bytes = (2 * hid * Hq * D + 2 * hid * Hkv * D + 3 * hid * ffn) / 2
+        print(json.dumps({"case": "decode_step_llama3_8b_layer", "batch": B, "ctx": T, "layer_us": round(t_layer * 1e3, 1),
+                          "weight_plus_kv_gbs": round((w_bytes + kv_bytes) / t_layer / 1e6, 1),
+                          "tokens_per_s_32_layers": round(B / (32 * t_layer * 1e-3), 1),
+                          "note": "one layer timed, 32 identical layers assumed; embeddings and lm_head not included"}))
+    except Exception as e:  # the sweep is secondary: report and go on
+        print(json.dumps({"case": "decode_step_llama3_8b_layer", "error": str(e)[:200]}))
+    cache.freeze_specs(False)
     # config 5: one Mixtral-8x7B-shaped MoE block (8 experts, top-2, hidden 4096, ffn 14336)
-    from signrot_b200 import nn as snn
-    from signrot_b200.functional import pack_i4
     E, hid, ffn, top_k = 8, 4096, 14336, 2
     gen = torch.Generator().manual_seed(1)
     def wq(nn_, kk_):
@@ -530,7 +596,7 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="secondary measurements of the other BASELINE configurations (JSON lines)")
     ap.add_argument("--kernel-case", default=None,
-                    help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | "
+                    help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | decode_layer | "
                          "rotate14336 | decode")
     args = ap.parse_args()
     if args.kernel_case:
