@@ -1,5 +1,5 @@
-// C ABI of the dense W4A4 GEMM: regime selection between the weight-streaming
-// kernel (few rows) and the tcgen05 kernel, argument validation.
+// C ABI of the W4A4 GEMMs: argument validation and the choice of kernel by shape (weight-streaming
+// mma.sync kernel for the decode regime, tcgen05 kernels above it, CTA pairs for large M and MoE).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cstdlib>
@@ -7,7 +7,8 @@
 
 namespace sr {
 
-// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; M <= 128: kernel 3; else kernel 4), 1 = always the few-rows kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
+// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; M <= 128: kernel 3; else kernel 4),
+// 1 = dp4a weight-streaming kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
 // 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel,
 // 5 = weight-streaming mma.sync kernel of the decode regime (M <= 64).
 // SIGNROT_B200_GEMM=small|tc|tc2|tc3|skinny pins one kernel (used by the parity tests to cover both

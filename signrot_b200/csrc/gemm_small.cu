@@ -1,4 +1,5 @@
-// W4A4 GEMM for few rows (decode): C[M,N] = A[M,K] * B[N,K]^T with packed 4-bit
+// W4A4 GEMM for few rows on dp4a (selectable as kernel 1; the mma.sync kernel in gemm_skinny.cu is the
+// default of the decode regime): C[M,N] = A[M,K] * B[N,K]^T with packed 4-bit
 // operands, exact int32 accumulation, optional fused dequant epilogue.
 //
 // Replaces signrot/kernels/gemm.cu:7-85 (CUTLASS Sm80 s4 tensor-op GEMM, one
