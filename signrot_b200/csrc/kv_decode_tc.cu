@@ -17,7 +17,9 @@
 // are the fp16 pairs (dims i, i + 4 of a word); the permutation of the head dimension is baked into
 // the q fragments.  V operand: pairs run over tokens, so the rows of tokens 2 qd and 2 qd + 1 are
 // merged byte-wise, (A & 0x0F..) | ((B << 4) & 0xF0..), and a byte broadcast + mask 0x00F0000F gives
-// the pair (n_A 2^-24, n_B 2^-20); the factor 16 is taken off p for the odd token.
+// the pair (n_A 2^-24, n_B 2^-20); the factor 16 is taken off p for the odd token.  That product
+// runs transposed (dims x heads, 8 MMAs per 16 tokens): the probabilities of the score tile are
+// already in the layout of its second operand, and the accumulator has no padded rows.
 #include "kv_cache.cuh"
 #include <cfloat>
 
@@ -119,17 +121,19 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     const uint32_t num_blocks = (cp_end - cp_begin) * blocks_per_page;
 
     float m_run = -5e4f, d_run = 0.f, z_run = 0.f;   // head g: running max (quad-uniform), this lane's part of sum p and sum p vz
-    float acc[16][4];
+    // O^T accumulators: m-tile j = byte j of the lane's eight V bytes; slot 0,1: dim 16 g + 2 j, heads 2 qd, 2 qd + 1;
+    // slot 2,3: dim 16 g + 2 j + 1
+    float acc[8][4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
 
     struct Stage {
         uint4 k[2];      // K rows of tokens g and 8 + g, bytes 16 qd ..
         uint2 v[4];      // V rows of tokens 2 qd, 2 qd + 1, 8 + 2 qd, 9 + 2 qd, bytes 8 g ..
-        __half2 kp[4];   // (scale, zero) of K for tokens 2 qd, 2 qd + 1, 8 + 2 qd, 9 + 2 qd
-        __half2 vp[4];
+        uint2 kp[2];     // (scale, zero) fp16 pairs of K for tokens (2 qd, 2 qd + 1) and (8 + 2 qd, 9 + 2 qd)
+        uint2 vp[2];
         uint32_t valid;  // tokens of the block that exist
     };
     auto load = [&](uint32_t blk, Stage &s) {
@@ -139,23 +143,20 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         s.valid = valid_page > e0 ? min(valid_page - e0, (uint32_t)DT_BLOCK) : 0u;
         const size_t kbase = kv.vec_index(page, 0, hk, e0), vbase = kv.vec_index(page, 1, hk, e0);
         // rows past the end of a partially filled page belong to the same allocation: they are read and masked
+        const uint8_t *krow = kv.data + (kbase + g) * 64 + qd * 16;
+        const uint8_t *vrow = kv.data + (vbase + 2 * qd) * 64 + g * 8;
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
-            s.k[t] = __ldg(reinterpret_cast<const uint4 *>(kv.data + (kbase + 8 * t + g) * 64) + qd);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const uint32_t tok = 8 * (t >> 1) + 2 * qd + (t & 1);
-            s.v[t] = __ldg(reinterpret_cast<const uint2 *>(kv.data + (vbase + tok) * 64) + g);
-            s.kp[t] = kv.param[kbase + tok];
-            s.vp[t] = kv.param[vbase + tok];
+        for (int t = 0; t < 2; ++t) {
+            s.k[t] = __ldg(reinterpret_cast<const uint4 *>(krow + t * 512));
+            s.v[2 * t] = __ldg(reinterpret_cast<const uint2 *>(vrow + t * 512));
+            s.v[2 * t + 1] = __ldg(reinterpret_cast<const uint2 *>(vrow + t * 512 + 64));
+            // block bases are multiples of 16 vectors: the pair of 4-byte parameters is 8-byte aligned
+            s.kp[t] = __ldg(reinterpret_cast<const uint2 *>(kv.param + kbase + 8 * t + 2 * qd));
+            s.vp[t] = __ldg(reinterpret_cast<const uint2 *>(kv.param + vbase + 8 * t + 2 * qd));
         }
     };
 
-    Stage cur, nxt;
-    if ((uint32_t)warp < num_blocks) load(warp, cur);
-    for (uint32_t blk = warp; blk < num_blocks; blk += DT_WARPS) {
-        if (blk + DT_WARPS < num_blocks) load(blk + DT_WARPS, nxt);
-
+    auto process = [&](const Stage &cur) {
         // ---- scores of 16 tokens: two n-tiles of 8 tokens, 8 k-steps over the head dimension
         float sc[2][4];
 #pragma unroll
@@ -176,50 +177,67 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
             sc[t][1] += s2[1];
         }
         // lane holds head g, tokens 2 qd, 2 qd + 1 (tile 0) and 8 + 2 qd, 9 + 2 qd (tile 1)
-        float x[4], p[4];
+        float x[4], kz[4], vs[4], vz[4];
         float bmax = -5e4f;
 #pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&cur.kp[t].x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2 *>(&cur.kp[t].y));
+            const float2 v0 = __half22float2(*reinterpret_cast<const __half2 *>(&cur.vp[t].x));
+            const float2 v1 = __half22float2(*reinterpret_cast<const __half2 *>(&cur.vp[t].y));
+            x[2 * t] = sc[t][0] * (k0.x * 16777216.f);
+            x[2 * t + 1] = sc[t][1] * (k1.x * 16777216.f);
+            kz[2 * t] = k0.y;
+            kz[2 * t + 1] = k1.y;
+            vs[2 * t] = v0.x;
+            vs[2 * t + 1] = v1.x * 0.0625f;   // odd tokens carry their codes 16 times too large (see the V operand)
+            vz[2 * t] = v0.y;
+            vz[2 * t + 1] = v1.y;
+        }
+        bool live[4];
+#pragma unroll
         for (int t = 0; t < 4; ++t) {
-            const float2 kp = __half22float2(cur.kp[t]);
-            const uint32_t tok = 8 * (t >> 1) + 2 * qd + (t & 1);
-            x[t] = sc[t >> 1][t & 1] * (kp.x * 16777216.f) - kp.y * qsum;
-            if (tok >= cur.valid) x[t] = -5e4f;
+            live[t] = (uint32_t)(8 * (t >> 1) + 2 * qd + (t & 1)) < cur.valid;
+            x[t] = live[t] ? x[t] - kz[t] * qsum : -5e4f;
             bmax = fmaxf(bmax, x[t]);
         }
         bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
         bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
         const float m_new = fmaxf(m_run, bmax);
-        // the running maximum moves in few blocks: the rescale of the 64 accumulators is skipped when no lane needs it
+        // the running maximum moves in few blocks: the rescale of the accumulators is skipped when no lane needs it
         if (__any_sync(0xffffffffu, m_new > m_run)) {
             const float alpha = ex2(m_run - m_new);
             d_run *= alpha;
             z_run *= alpha;
+            // the accumulator columns of this lane are heads 2 qd and 2 qd + 1: their factors live in lanes g = head
+            const float a_lo = __shfl_sync(0xffffffffu, alpha, (2 * qd) << 2);
+            const float a_hi = __shfl_sync(0xffffffffu, alpha, (2 * qd + 1) << 2);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                acc[j][0] *= alpha;
-                acc[j][1] *= alpha;
+            for (int j = 0; j < 8; ++j) {
+                acc[j][0] *= a_lo;
+                acc[j][1] *= a_hi;
+                acc[j][2] *= a_lo;
+                acc[j][3] *= a_hi;
             }
             m_run = m_new;
         }
-        uint32_t pa[2];
+        uint32_t pb[2];
         {
             float pv[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 // slots past the end of a page hold whatever was there before: their parameters are not numbers to trust
-                const bool live = (uint32_t)(8 * (t >> 1) + 2 * qd + (t & 1)) < cur.valid;
-                const float2 vp = live ? __half22float2(cur.vp[t]) : make_float2(0.f, 0.f);
-                p[t] = live ? ex2(x[t] - m_run) : 0.f;
-                d_run += p[t];
-                z_run = fmaf(p[t], vp.y, z_run);
-                // odd tokens carry their codes 16 times too large (see the V operand below)
-                pv[t] = p[t] * vp.x * ((t & 1) ? 0.0625f : 1.f);
+                const float p = live[t] ? ex2(x[t] - m_run) : 0.f;
+                d_run += p;
+                z_run = fmaf(p, live[t] ? vz[t] : 0.f, z_run);
+                pv[t] = live[t] ? p * vs[t] : 0.f;
             }
-            pa[0] = pack_h2(pv[0], pv[1]);
-            pa[1] = pack_h2(pv[2], pv[3]);
+            pb[0] = pack_h2(pv[0], pv[1]);
+            pb[1] = pack_h2(pv[2], pv[3]);
         }
-        // ---- output: 16 n-tiles of 8 dims; lane's bytes 8 g .. 8 g + 7 of four token rows
-        uint32_t even[2][2], odd[2][2];   // [token pair][word]: bytes = (code of the even token, code of the odd token << 4)
+        // ---- output, transposed: O^T[dims x heads] += V^T[dims x tokens] P^T[tokens x heads]; 8 m-tiles of 16 dims.
+        // bytes of the merged words = (code of the even token, code of the odd token << 4)
+        uint32_t even[2][2], odd[2][2];   // [token pair][word]
 #pragma unroll
         for (int tp = 0; tp < 2; ++tp) {
             const uint32_t ax = cur.v[2 * tp].x, ay = cur.v[2 * tp].y, bx = cur.v[2 * tp + 1].x, by = cur.v[2 * tp + 1].y;
@@ -229,17 +247,27 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
             odd[tp][1] = ((ay >> 4) & 0x0F0F0F0Fu) | (by & 0xF0F0F0F0u);
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            // n-tile j <-> nibble j of the lane's 16: byte j / 2 (word j / 8), low (even j) or high (odd j) nibble
-            const int byte = (j >> 1) & 3, word = j >> 3;
+        for (int j = 0; j < 8; ++j) {
+            const int byte = j & 3, word = j >> 2;
             const uint32_t sel = (uint32_t)(byte | (byte << 8));
-            const uint32_t s0 = (j & 1) ? odd[0][word] : even[0][word];
-            const uint32_t s1 = (j & 1) ? odd[1][word] : even[1][word];
-            const uint32_t b0 = __byte_perm(s0, s0, sel) & 0x00F0000Fu;
-            const uint32_t b1 = __byte_perm(s1, s1, sel) & 0x00F0000Fu;
-            mma_f16(acc[j], pa[0], 0u, pa[1], 0u, b0, b1);
+            const uint32_t a0 = __byte_perm(even[0][word], even[0][word], sel) & 0x00F0000Fu;   // dim 16 g + 2 j,     tokens 2 qd, 2 qd + 1
+            const uint32_t a1 = __byte_perm(odd[0][word], odd[0][word], sel) & 0x00F0000Fu;     // dim 16 g + 2 j + 1
+            const uint32_t a2 = __byte_perm(even[1][word], even[1][word], sel) & 0x00F0000Fu;   // tokens 8 + 2 qd, 9 + 2 qd
+            const uint32_t a3 = __byte_perm(odd[1][word], odd[1][word], sel) & 0x00F0000Fu;
+            mma_f16(acc[j], a0, a1, a2, a3, pb[0], pb[1]);
         }
-        cur = nxt;
+    };
+
+    // two stages in registers, alternating: the loads of one block are in flight while the other is processed
+    Stage sa, sb;
+    if ((uint32_t)warp < num_blocks) load(warp, sa);
+    for (uint32_t blk = warp; blk < num_blocks; blk += 2 * DT_WARPS) {
+        const bool has_b = blk + DT_WARPS < num_blocks;
+        if (has_b) load(blk + DT_WARPS, sb);
+        process(sa);
+        if (!has_b) break;
+        if (blk + 2 * DT_WARPS < num_blocks) load(blk + 2 * DT_WARPS, sa);
+        process(sb);
     }
 
     // ---- fold the warp's state: sums across the quad, the 2^24 of the subnormal codes, the zero points
@@ -247,15 +275,22 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     d_run += __shfl_xor_sync(0xffffffffu, d_run, 2);
     z_run += __shfl_xor_sync(0xffffffffu, z_run, 1);
     z_run += __shfl_xor_sync(0xffffffffu, z_run, 2);
-    if (g < G) {
-        float *so = &sh_o[warp][g][0];
-        // n-tile j, column 2 qd + h of the accumulator <-> dim 16 (2 qd + h) + j
+    {
+        const float z_lo = __shfl_sync(0xffffffffu, z_run, (2 * qd) << 2);
+        const float z_hi = __shfl_sync(0xffffffffu, z_run, (2 * qd + 1) << 2);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            so[16 * (2 * qd) + j] = acc[j][0] * 16777216.f - z_run;
-            so[16 * (2 * qd + 1) + j] = acc[j][1] * 16777216.f - z_run;
+        for (int j = 0; j < 8; ++j) {
+            const int dim = 16 * g + 2 * j;
+            if (2 * qd < G) {
+                sh_o[warp][2 * qd][dim] = acc[j][0] * 16777216.f - z_lo;
+                sh_o[warp][2 * qd][dim + 1] = acc[j][2] * 16777216.f - z_lo;
+            }
+            if (2 * qd + 1 < G) {
+                sh_o[warp][2 * qd + 1][dim] = acc[j][1] * 16777216.f - z_hi;
+                sh_o[warp][2 * qd + 1][dim + 1] = acc[j][3] * 16777216.f - z_hi;
+            }
         }
-        if (qd == 0) {
+        if (g < G && qd == 0) {
             sh_md[warp][g][0] = m_run;
             sh_md[warp][g][1] = d_run;
         }
