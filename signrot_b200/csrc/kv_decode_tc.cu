@@ -29,8 +29,11 @@ namespace {
 
 constexpr int DT_WARPS = 4;
 constexpr int DT_BLOCK = 16;   // cached tokens per warp iteration
+constexpr int DT_DEPTH = 4;    // blocks in flight per warp
+constexpr int DT_STAGE_BYTES = 3072;   // per warp and block: 2 KB of codes + 1 KB of parameter pairs (tokens repeat across lanes)
+constexpr int DT_RING_BYTES = DT_WARPS * DT_DEPTH * DT_STAGE_BYTES;
 #ifndef DT_MIN_CTAS
-#define DT_MIN_CTAS 3
+#define DT_MIN_CTAS 4
 #endif
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -60,6 +63,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, qd = lane & 3;
 
+    extern __shared__ __align__(16) uint8_t dt_smem[];
     __shared__ float sh_q[G][HD];
     __shared__ float sh_o[DT_WARPS][G][HD];
     __shared__ float sh_md[DT_WARPS][G][2];
@@ -136,23 +140,44 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         uint2 vp[2];
         uint32_t valid;  // tokens of the block that exist
     };
-    auto load = [&](uint32_t blk, Stage &s) {
+    // The rows travel through a cp.async ring in shared memory, DT_DEPTH blocks ahead of the math.  Every lane
+    // copies exactly the bytes its own fragments need into slots nobody else touches: no barrier guards the ring.
+    // ring[warp][stage]: 64 x 16 B (K), then 128 x 8 B (V), then 128 x 8 B (parameters), lane-interleaved.
+    uint8_t *ring = dt_smem + (size_t)warp * DT_DEPTH * DT_STAGE_BYTES;
+    const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
+    auto issue = [&](uint32_t blk, int slot) {
+        if (blk < num_blocks) {
+            const uint32_t pi = cp_begin + blk / blocks_per_page, e0 = (blk % blocks_per_page) * DT_BLOCK;
+            const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
+            const size_t kbase = kv.vec_index(page, 0, hk, e0), vbase = kv.vec_index(page, 1, hk, e0);
+            // rows past the end of a partially filled page belong to the same allocation: they are read and masked
+            const uint8_t *krow = kv.data + (kbase + g) * 64 + qd * 16;
+            const uint8_t *vrow = kv.data + (vbase + 2 * qd) * 64 + g * 8;
+            const uint32_t dst = ring_u32 + (uint32_t)slot * DT_STAGE_BYTES;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (t * 32 + lane) * 16), "l"(krow + t * 512) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 1024 + (2 * t * 32 + lane) * 8), "l"(vrow + t * 512) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 1024 + ((2 * t + 1) * 32 + lane) * 8), "l"(vrow + t * 512 + 64) : "memory");
+                // block bases are multiples of 16 vectors: the pair of 4-byte parameters is 8-byte aligned
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 2048 + (t * 32 + lane) * 8), "l"(kv.param + kbase + 8 * t + 2 * qd) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 2048 + ((2 + t) * 32 + lane) * 8), "l"(kv.param + vbase + 8 * t + 2 * qd) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto fetch = [&](uint32_t blk, int slot, Stage &s) {
         const uint32_t pi = cp_begin + blk / blocks_per_page, e0 = (blk % blocks_per_page) * DT_BLOCK;
-        const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
         const uint32_t valid_page = (pi == pages_total - 1) ? last_valid : kv.page_size;
         s.valid = valid_page > e0 ? min(valid_page - e0, (uint32_t)DT_BLOCK) : 0u;
-        const size_t kbase = kv.vec_index(page, 0, hk, e0), vbase = kv.vec_index(page, 1, hk, e0);
-        // rows past the end of a partially filled page belong to the same allocation: they are read and masked
-        const uint8_t *krow = kv.data + (kbase + g) * 64 + qd * 16;
-        const uint8_t *vrow = kv.data + (vbase + 2 * qd) * 64 + g * 8;
+        const uint8_t *src = ring + (size_t)slot * DT_STAGE_BYTES;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-            s.k[t] = __ldg(reinterpret_cast<const uint4 *>(krow + t * 512));
-            s.v[2 * t] = __ldg(reinterpret_cast<const uint2 *>(vrow + t * 512));
-            s.v[2 * t + 1] = __ldg(reinterpret_cast<const uint2 *>(vrow + t * 512 + 64));
-            // block bases are multiples of 16 vectors: the pair of 4-byte parameters is 8-byte aligned
-            s.kp[t] = __ldg(reinterpret_cast<const uint2 *>(kv.param + kbase + 8 * t + 2 * qd));
-            s.vp[t] = __ldg(reinterpret_cast<const uint2 *>(kv.param + vbase + 8 * t + 2 * qd));
+            s.k[t] = *reinterpret_cast<const uint4 *>(src + (t * 32 + lane) * 16);
+            s.v[2 * t] = *reinterpret_cast<const uint2 *>(src + 1024 + (2 * t * 32 + lane) * 8);
+            s.v[2 * t + 1] = *reinterpret_cast<const uint2 *>(src + 1024 + ((2 * t + 1) * 32 + lane) * 8);
+            s.kp[t] = *reinterpret_cast<const uint2 *>(src + 2048 + (t * 32 + lane) * 8);
+            s.vp[t] = *reinterpret_cast<const uint2 *>(src + 2048 + ((2 + t) * 32 + lane) * 8);
         }
     };
 
@@ -258,17 +283,19 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         }
     };
 
-    // two stages in registers, alternating: the loads of one block are in flight while the other is processed
-    Stage sa, sb;
-    if ((uint32_t)warp < num_blocks) load(warp, sa);
-    for (uint32_t blk = warp; blk < num_blocks; blk += 2 * DT_WARPS) {
-        const bool has_b = blk + DT_WARPS < num_blocks;
-        if (has_b) load(blk + DT_WARPS, sb);
-        process(sa);
-        if (!has_b) break;
-        if (blk + 2 * DT_WARPS < num_blocks) load(blk + 2 * DT_WARPS, sa);
-        process(sb);
+#pragma unroll 1
+    for (int d = 0; d < DT_DEPTH; ++d) issue(warp + d * DT_WARPS, d);
+    int slot = 0;
+#pragma unroll 1
+    for (uint32_t blk = warp; blk < num_blocks; blk += DT_WARPS) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(DT_DEPTH - 1) : "memory");
+        Stage st;
+        fetch(blk, slot, st);
+        process(st);
+        issue(blk + DT_DEPTH * DT_WARPS, slot);   // after the math that consumed the slot
+        slot = slot + 1 == DT_DEPTH ? 0 : slot + 1;
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 
     // ---- fold the warp's state: sums across the quad, the 2^24 of the subnormal codes, the zero points
     d_run += __shfl_xor_sync(0xffffffffu, d_run, 1);
@@ -327,13 +354,21 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
 bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
                       int had_q, float had_scale, cudaStream_t st) {
     if (kv.page_size % DT_BLOCK != 0) return false;
+#define SR_DT(GG)                                                                                              \
+    do {                                                                                                       \
+        auto kfn = decode_tc_kernel<GG>;                                                                       \
+        if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
+            return false;                                                                                      \
+        kfn<<<grid, DT_WARPS * 32, DT_RING_BYTES, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale);          \
+    } while (0)
     switch (G) {
-        case 1: decode_tc_kernel<1><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
-        case 2: decode_tc_kernel<2><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
-        case 4: decode_tc_kernel<4><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
-        case 8: decode_tc_kernel<8><<<grid, DT_WARPS * 32, 0, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale); break;
+        case 1: SR_DT(1); break;
+        case 2: SR_DT(2); break;
+        case 4: SR_DT(4); break;
+        case 8: SR_DT(8); break;
         default: return false;
     }
+#undef SR_DT
     return true;
 }
 
