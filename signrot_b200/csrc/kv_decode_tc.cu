@@ -64,8 +64,10 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     const int g = lane >> 2, qd = lane & 3;
 
     extern __shared__ __align__(16) uint8_t dt_smem[];
-    __shared__ float sh_q[G][HD];
-    __shared__ float sh_o[DT_WARPS][G][HD];
+    // padded so that the gathers below are bank-conflict free: q row pitch 132 with one extra word per 32 dims
+    // (lane (g, qd) reads row g, dims 32 qd + c); output rows hold dim d at d + 2 (d / 16), pitch 148
+    __shared__ float sh_q[G][132];
+    __shared__ float sh_o[DT_WARPS][G][148];
     __shared__ float sh_md[DT_WARPS][G][2];
 
     // ---- q (optionally Hadamard-rotated, kv_cache.py:157-158), one warp per q head
@@ -92,7 +94,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         }
         // the products take q' as fp16: round once here so that sum(q') below is the sum of what is multiplied
 #pragma unroll
-        for (int j = 0; j < 4; ++j) sh_q[gg][lane * 4 + j] = __half2float(__float2half_rn(a[j] * sm_scale));
+        for (int j = 0; j < 4; ++j) sh_q[gg][lane * 4 + j + (lane >> 3)] = __half2float(__float2half_rn(a[j] * sm_scale));
     }
     __syncthreads();
 
@@ -105,11 +107,11 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
             for (int reg = 0; reg < 2; ++reg) {
-                const float lo = sh_q[gq][k_dim(ks, qd, reg, 0)], hi = sh_q[gq][k_dim(ks, qd, reg, 1)];
+                const float lo = sh_q[gq][k_dim(ks, qd, reg, 0) + qd], hi = sh_q[gq][k_dim(ks, qd, reg, 1) + qd];
                 qa[ks][reg] = g < G ? pack_h2(lo, hi) : 0u;
             }
         float s = 0.f;
-        for (int j = 0; j < 32; ++j) s += sh_q[gq][qd * 32 + j];
+        for (int j = 0; j < 32; ++j) s += sh_q[gq][qd * 33 + j];
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         qsum = s;
@@ -307,15 +309,13 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         const float z_hi = __shfl_sync(0xffffffffu, z_run, (2 * qd + 1) << 2);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int dim = 16 * g + 2 * j;
-            if (2 * qd < G) {
-                sh_o[warp][2 * qd][dim] = acc[j][0] * 16777216.f - z_lo;
-                sh_o[warp][2 * qd][dim + 1] = acc[j][2] * 16777216.f - z_lo;
-            }
-            if (2 * qd + 1 < G) {
-                sh_o[warp][2 * qd + 1][dim] = acc[j][1] * 16777216.f - z_hi;
-                sh_o[warp][2 * qd + 1][dim + 1] = acc[j][3] * 16777216.f - z_hi;
-            }
+            const int at = 18 * g + 2 * j;   // dims 16 g + 2 j and + 1, skewed
+            if (2 * qd < G)
+                *reinterpret_cast<float2 *>(&sh_o[warp][2 * qd][at]) =
+                    make_float2(acc[j][0] * 16777216.f - z_lo, acc[j][2] * 16777216.f - z_lo);
+            if (2 * qd + 1 < G)
+                *reinterpret_cast<float2 *>(&sh_o[warp][2 * qd + 1][at]) =
+                    make_float2(acc[j][1] * 16777216.f - z_hi, acc[j][3] * 16777216.f - z_hi);
         }
         if (g < G && qd == 0) {
             sh_md[warp][g][0] = m_run;
@@ -333,7 +333,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         for (int w = 0; w < DT_WARPS; ++w) {
             const float scl = ex2(sh_md[w][gg][0] - mm);
             dd += sh_md[w][gg][1] * scl;
-            oo += sh_o[w][gg][tid] * scl;
+            oo += sh_o[w][gg][tid + 2 * (tid >> 4)] * scl;
         }
         const uint32_t hq = hk * G + gg;
         if (num_chunks == 1) {
