@@ -11,7 +11,7 @@
 // the activation rows are its 8-wide operand, one MMA column block per 8 tokens.
 //
 // The weight stream is what must never stall: every lane copies the 16 bytes of its own MMA
-// fragments with cp.async into a private shared-memory slot, SK_DEPTH steps ahead of the math, and
+// fragments with cp.async into a private shared-memory slot, 8 KB per warp ahead of the math, and
 // the queue runs on across row blocks, so the loads of the next block are in flight while this one
 // is reduced and stored.  Slots are private to a lane: no barrier guards the ring.
 // Nibble n becomes the byte 16*n ((w << 4) & 0xF0F0F0F0 for the even nibbles of a word, w &
@@ -28,7 +28,6 @@ namespace {
 constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = 16;      // weight rows per CTA
 constexpr int SK_STEP = 64;      // packed bytes of K per row and step (128 values)
-constexpr int SK_DEPTH = 8;      // steps in flight per warp
 
 template <bool A_UNSIGNED>
 __device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -49,71 +48,84 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
-constexpr size_t skinny_smem(int nt) {
-    return (size_t)SK_WARPS * SK_DEPTH * 2 * 32 * 16 + (size_t)2 * SK_WARPS * nt * 4 * 32 * 4;
+// ring: SK_RING_BYTES per warp (steps of 1 KB per m-tile); red: one or two buffers of [warp][MT][NT][4][32] ints
+constexpr int SK_RING_BYTES = 8192;
+constexpr size_t skinny_smem(int nt, int mt) {
+    return (size_t)SK_WARPS * SK_RING_BYTES + (size_t)(nt <= 2 ? 2 : 1) * SK_WARPS * mt * nt * 4 * 32 * 4;
 }
 
-// NT = token blocks of 8 (M <= 8 * NT).  A = activations [M, K/2], B = weights [N, K/2].
-template <int NT, bool A_UNSIGNED>
+// NT = token blocks of 8 (M <= 8 * NT), MT = blocks of 16 weight rows a warp multiplies per step (the
+// activation fragments of a step are unpacked once for all of them).  A = activations [M, K/2], B = weights [N, K/2].
+template <int NT, int MT, bool A_UNSIGNED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
                    Epilogue ep) {
+    constexpr int ROWS = SK_ROWS * MT;                  // weight rows per block
+    constexpr int STAGE = 1024 * MT;                    // bytes per warp and step
+    constexpr int DEPTH = SK_RING_BYTES / STAGE;        // steps in flight per warp
+    constexpr int RED_BUFS = NT <= 2 ? 2 : 1;
     extern __shared__ __align__(16) uint8_t sk_smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
-    // ring[warp][stage][row half][lane] (16 bytes each), then red[2][warp][NT][4][32]
-    uint4 *ring = reinterpret_cast<uint4 *>(sk_smem) + (size_t)warp * SK_DEPTH * 64 + lane;
+    // ring[warp][stage][row slot 0 .. 2 MT - 1][lane] (16 bytes each)
+    const uint4 *ring = reinterpret_cast<const uint4 *>(sk_smem + (size_t)warp * SK_RING_BYTES) + lane;
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
-    int *red = reinterpret_cast<int *>(sk_smem + (size_t)SK_WARPS * SK_DEPTH * 2 * 32 * 16);
+    int *red = reinterpret_cast<int *>(sk_smem + (size_t)SK_WARPS * SK_RING_BYTES);
 
     const uint32_t kp = K >> 1;                         // packed bytes per row
     const uint32_t steps = (kp + SK_STEP - 1) / SK_STEP;
-    const uint32_t blocks = (N + SK_ROWS - 1) / SK_ROWS;
+    const uint32_t blocks = (N + ROWS - 1) / ROWS;
     const bool has_steps = (uint32_t)warp < steps;
     const uint8_t *x_row = A + (size_t)g * kp + 16 * q;
 
     // queue of (row block, step) items of this warp, in the order they are consumed
     uint32_t iss_blk = blockIdx.x, iss_step = warp;
+    const uint8_t *iss_ptr = B + ((size_t)iss_blk * ROWS + g) * kp + (size_t)iss_step * SK_STEP + 16 * q;
     auto issue = [&](int slot) {
         if (has_steps && iss_blk < blocks) {
-            const uint32_t row = iss_blk * SK_ROWS + g;
             const bool k_ok = iss_step * SK_STEP + 16 * q + 16 <= kp;
-            const uint8_t *src = B + (size_t)row * kp + (size_t)iss_step * SK_STEP + 16 * q;
-            const uint32_t dst = ring_u32 + (uint32_t)slot * 1024;
-            const bool lo = k_ok && row < N, hi = k_ok && row + 8 < N;
-            cp_async16(dst, lo ? src : B, lo ? 16u : 0u);
-            cp_async16(dst + 512, hi ? src + (size_t)8 * kp : B, hi ? 16u : 0u);
+            const uint32_t row = iss_blk * ROWS + g;
+            const uint32_t dst = ring_u32 + (uint32_t)slot * STAGE;
+#pragma unroll
+            for (int r = 0; r < 2 * MT; ++r) {
+                const bool ok = k_ok && row + 8 * r < N;
+                cp_async16(dst + r * 512, ok ? iss_ptr + (size_t)(8 * r) * kp : B, ok ? 16u : 0u);
+            }
             iss_step += SK_WARPS;
+            iss_ptr += SK_WARPS * SK_STEP;
             if (iss_step >= steps) {
                 iss_step = warp;
                 iss_blk += gridDim.x;
+                iss_ptr = B + ((size_t)iss_blk * ROWS + g) * kp + (size_t)warp * SK_STEP + 16 * q;
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 #pragma unroll 1
-    for (int d = 0; d < SK_DEPTH; ++d) issue(d);
+    for (int d = 0; d < DEPTH; ++d) issue(d);
 
     // activation fragments of the step after the current one (they come from L1/L2, one step ahead is enough)
     auto load_x = [&](uint32_t step, uint4 (&x)[NT]) {
         const bool k_ok = step * SK_STEP + 16 * q + 16 <= kp;
+        const uint8_t *xs = x_row + (size_t)step * SK_STEP;
 #pragma unroll
         for (int t = 0; t < NT; ++t)
-            x[t] = k_ok && (uint32_t)(g + 8 * t) < M
-                       ? __ldg(reinterpret_cast<const uint4 *>(x_row + (size_t)(8 * t) * kp + (size_t)step * SK_STEP))
-                       : make_uint4(0, 0, 0, 0);
+            x[t] = k_ok && (uint32_t)(g + 8 * t) < M ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * kp))
+                                                     : make_uint4(0, 0, 0, 0);
     };
     uint4 xn[NT];
     if (has_steps) load_x(warp, xn);
 
     int slot = 0;
     uint32_t parity = 0;
-    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x, parity ^= 1) {
-        int acc[NT][4];
+    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x, parity ^= (RED_BUFS - 1)) {
+        int acc[MT][NT][4];
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
+        for (int m = 0; m < MT; ++m)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[m][t][i] = 0;
         if (has_steps) {
 #pragma unroll 1
             for (uint32_t s = warp; s < steps; s += SK_WARPS) {
@@ -121,43 +133,55 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
 #pragma unroll
                 for (int t = 0; t < NT; ++t) x[t] = xn[t];
                 load_x(s + SK_WARPS < steps ? s + SK_WARPS : (uint32_t)warp, xn);
-                asm volatile("cp.async.wait_group %0;" ::"n"(SK_DEPTH - 1) : "memory");
-                const uint4 cl = ring[slot * 64], ch = ring[slot * 64 + 32];
+                asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+                uint4 w[2 * MT];
+#pragma unroll
+                for (int r = 0; r < 2 * MT; ++r) w[r] = ring[slot * (STAGE / 16) + r * 32];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t pl = word(cl, j), ph = word(ch, j);
-                    uint32_t a[4];
-                    a[0] = (pl << 4) & 0xF0F0F0F0u;   // row g,     even nibbles
-                    a[1] = (ph << 4) & 0xF0F0F0F0u;   // row g + 8, even nibbles
-                    a[2] = pl & 0xF0F0F0F0u;          // row g,     odd nibbles
-                    a[3] = ph & 0xF0F0F0F0u;          // row g + 8, odd nibbles
+                    uint32_t be[NT], bo[NT];
 #pragma unroll
                     for (int t = 0; t < NT; ++t) {
                         const uint32_t px = word(x[t], j);
-                        mma_s8<A_UNSIGNED>(acc[t], a, (px << 4) & 0xF0F0F0F0u, px & 0xF0F0F0F0u);
+                        be[t] = (px << 4) & 0xF0F0F0F0u;
+                        bo[t] = px & 0xF0F0F0F0u;
+                    }
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint32_t pl = word(w[2 * m], j), ph = word(w[2 * m + 1], j);
+                        uint32_t a[4];
+                        a[0] = (pl << 4) & 0xF0F0F0F0u;   // row g,     even nibbles
+                        a[1] = (ph << 4) & 0xF0F0F0F0u;   // row g + 8, even nibbles
+                        a[2] = pl & 0xF0F0F0F0u;          // row g,     odd nibbles
+                        a[3] = ph & 0xF0F0F0F0u;          // row g + 8, odd nibbles
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) mma_s8<A_UNSIGNED>(acc[m][t], a, be[t], bo[t]);
                     }
                 }
                 issue(slot);   // after the math that consumed the slot
-                slot = slot + 1 == SK_DEPTH ? 0 : slot + 1;
+                slot = slot + 1 == DEPTH ? 0 : slot + 1;
             }
         }
-        int *rb = red + (size_t)parity * SK_WARPS * NT * 128;
+        if (RED_BUFS == 1) __syncthreads();   // the previous block's sums have been read
+        int *rb = red + (size_t)parity * SK_WARPS * MT * NT * 128;
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
+        for (int m = 0; m < MT; ++m)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) rb[((warp * NT + t) * 4 + i) * 32 + lane] = acc[t][i];
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rb[(((warp * MT + m) * NT + t) * 4 + i) * 32 + lane] = acc[m][t][i];
         __syncthreads();
-        // fragment slot i of lane (g, q): weight row g + 8 * (i >> 1), token 2 * q + (i & 1) of its block.
-        // The buffer written two blocks later is this one: the barrier of the block in between orders it.
-        const uint32_t n0 = blk * SK_ROWS;
-        for (int idx = tid; idx < NT * 128; idx += SK_WARPS * 32) {
-            const int l = idx & 31, i = (idx >> 5) & 3, t = idx >> 7;
+        // fragment slot i of lane (g, q) in m-tile m: weight row 16 m + g + 8 * (i >> 1), token 2 * q + (i & 1) of its
+        // block.  With two buffers the one written two blocks later is this one: the barrier in between orders it.
+        const uint32_t n0 = blk * ROWS;
+        for (int idx = tid; idx < MT * NT * 128; idx += SK_WARPS * 32) {
+            const int l = idx & 31, i = (idx >> 5) & 3, t = (idx >> 7) % NT, m = idx / (NT * 128);
             int sum = 0;
 #pragma unroll
-            for (int w = 0; w < SK_WARPS; ++w) sum += rb[((w * NT + t) * 4 + i) * 32 + l];
-            const uint32_t n = n0 + (l >> 2) + 8 * (i >> 1);
-            const uint32_t m = 8 * t + 2 * (l & 3) + (i & 1);
-            if (n < N && m < M) ep.store(m, n, sum >> 8, N);
+            for (int w = 0; w < SK_WARPS; ++w) sum += rb[(((w * MT + m) * NT + t) * 4 + i) * 32 + l];
+            const uint32_t n = n0 + 16 * m + (l >> 2) + 8 * (i >> 1);
+            const uint32_t mm = 8 * t + 2 * (l & 3) + (i & 1);
+            if (n < N && mm < M) ep.store(mm, n, sum >> 8, N);
         }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -178,24 +202,32 @@ int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N,
         if (sm_count <= 0) sm_count = 148;
     }
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
-    const int64_t blocks = cdiv<int64_t>(N, SK_ROWS);
+    // two m-tiles per warp step when there are enough row blocks to keep every SM busy and the sums fit
+    const int mt = (nt <= 4 && (N >= 8192 || (N >= 4096 && nt >= 2))) ? 2 : 1;   // measured crossover
+    const int64_t blocks = cdiv<int64_t>(N, SK_ROWS * mt);
     // two CTAs per SM; the row blocks are dealt round-robin, so shrink the grid to even the deal out
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas) ctas = blocks;
     else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas));
     const unsigned grid = (unsigned)ctas;
-#define SR_SK(NT)                                                                                              \
+#define SR_SK(NT, MT)                                                                                          \
     do {                                                                                                       \
-        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, true> : gemm_skinny_kernel<NT, false>;                  \
+        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, MT, true> : gemm_skinny_kernel<NT, MT, false>;          \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
-                                             (int)skinny_smem(NT));                                            \
+                                             (int)skinny_smem(NT, MT));                                        \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep);    \
+        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, MT), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep); \
     } while (0)
-    if (nt == 1) SR_SK(1);
-    else if (nt == 2) SR_SK(2);
-    else if (nt == 4) SR_SK(4);
-    else SR_SK(8);
+    if (mt == 2) {
+        if (nt == 1) SR_SK(1, 2);
+        else if (nt == 2) SR_SK(2, 2);
+        else SR_SK(4, 2);
+    } else {
+        if (nt == 1) SR_SK(1, 1);
+        else if (nt == 2) SR_SK(2, 1);
+        else if (nt == 4) SR_SK(4, 1);
+        else SR_SK(8, 1);
+    }
 #undef SR_SK
     return check_launch("gemm_skinny");
 }
