@@ -167,6 +167,7 @@ struct TileCoord {
     uint32_t b_row;     // first row of B (weight row, expert offset included)
     uint32_t n0;        // first output column
     uint32_t row_end;   // rows >= row_end are not stored
+    uint32_t bn;        // output columns of this item: 256, or 128 for the halves of the last wave's tiles
 };
 
 template <bool A_UNSIGNED, int G>
@@ -242,10 +243,22 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int *ab = &abort_flag;
     const uint32_t tiles_m = grouped ? mt_start[num_experts] : (M + 2 * BMC - 1) / (2 * BMC);
     const uint32_t num_tiles = tiles_n * tiles_m;
-    auto coord = [&](uint32_t tile) {
+    // Work items.  Tiles are dealt round-robin to the clusters; when the last round would leave at least half of
+    // the clusters idle, its tiles are split into two 256 x 128 halves so that the round costs half a tile.
+    const uint32_t rem = num_tiles % clusters;
+    const uint32_t split = (rem != 0 && 2 * rem <= clusters) ? rem : 0u;
+    const uint32_t full_items = num_tiles - split, num_items = num_tiles + split;
+    auto coord = [&](uint32_t item) {
         TileCoord c;
+        uint32_t tile = item, half = 0;
+        c.bn = BN;
+        if (item >= full_items) {
+            tile = full_items + ((item - full_items) >> 1);
+            half = (item - full_items) & 1;
+            c.bn = BN / 2;
+        }
         const uint32_t mt = tile / tiles_n, nt = tile % tiles_n;
-        c.n0 = nt * BN;
+        c.n0 = nt * BN + half * (BN / 2);
         if (!grouped) {
             c.a_row = mt * 2 * BMC;
             c.b_row = c.n0;
@@ -270,10 +283,10 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (lane == 0) {
                 Ring pr;
                 bool ok = true;
-                for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters) {
-                    const TileCoord tc = coord(tile);
+                for (uint32_t item = cluster; item < num_items && ok; item += clusters) {
+                    const TileCoord tc = coord(item);
                     const int ya = (int)(tc.a_row + rank * BMC);
-                    const int yb = (int)(tc.b_row + rank * BNC);
+                    const int yb = (int)(tc.b_row + rank * (tc.bn / 2));   // a half tile uses the first 64 rows of the box
                     for (uint32_t kb = 0; kb < num_kb; ++kb, pr.next(SP)) {
                         const int s = pr.s;
                         ok = mbar_wait(pk_empty(s), pr.ph ^ 1, ab, 41);
@@ -287,13 +300,14 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         } else if (warp == 1) {
             // ------------------------------------------------ MMA issuer (leader CTA only)
             if (rank == 0 && lane == 0) {
-                const uint32_t idesc = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
-                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BMC) >> 4) << 24);
+                const uint32_t idesc_base = (2u << 4) | ((A_UNSIGNED ? 0u : 1u) << 7) | (1u << 10) |
+                                            ((uint32_t)((2 * BMC) >> 4) << 24);
                 uint32_t it = 0;
                 Ring ur;
                 bool ok = true;
-                for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
+                for (uint32_t item = cluster; item < num_items && ok; item += clusters, ++it) {
                     const uint32_t buf = it & 1;
+                    const uint32_t idesc = idesc_base | (((item >= full_items ? BN / 2 : BN) >> 3) << 17);
                     ok = mbar_wait(acc_empty(buf), ((it >> 1) & 1) ^ 1, ab, 42);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -319,19 +333,20 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t quarter = warp & 3;
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t tile = cluster; tile < num_tiles && ok; tile += clusters, ++it) {
+            for (uint32_t item = cluster; item < num_items && ok; item += clusters, ++it) {
                 const uint32_t buf = it & 1;
-                const TileCoord tc = coord(tile);
+                const TileCoord tc = coord(item);
                 const uint32_t m0 = tc.a_row + rank * BMC, n0 = tc.n0;
+                const int chunks = (int)(tc.bn / 32);
                 ok = mbar_wait(acc_full(buf), (it >> 1) & 1, ab, 44);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < chunks; ++c) {
                     int v[32];
                     tmem_ld32(tmem_acc + ((quarter * 32u) << 16) + buf * BN + (uint32_t)(c * 32), v);
-                    if (c == BN / 32 - 1) {
+                    if (c == chunks - 1) {
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(acc_empty(buf), 0);
@@ -355,15 +370,22 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t ld_off = (uint32_t)tg * 16;
             const uint32_t st_off = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
             const uint32_t sw_e = (uint32_t)(((2 * qd) ^ (r0 & 7)) << 4), sw_o = (uint32_t)(((2 * qd + 1) ^ (r0 & 7)) << 4);
-            const uint32_t my_tiles = (num_tiles > cluster) ? ((num_tiles - cluster - 1) / clusters + 1) : 0;
-            const uint32_t total = my_tiles * num_kb;
+            const uint32_t my_items = (num_items > cluster) ? ((num_items - cluster - 1) / clusters + 1) : 0;
+            const uint32_t total = my_items * num_kb;
             bool ok = true;
             Ring pr, ur;
             for (int i = 0; i < grp; ++i) {
                 pr.next(SP);
                 ur.next(SU);
             }
-            for (uint32_t g = grp; g < total && ok; g += G) {
+            // position of k-block g in the item sequence: a half tile needs only the first 64 rows of B
+            uint32_t cur_item = cluster, kb_pos = (uint32_t)grp;
+            for (uint32_t g = grp; g < total && ok; g += G, kb_pos += G) {
+                while (kb_pos >= num_kb) {
+                    kb_pos -= num_kb;
+                    cur_item += clusters;
+                }
+                const int b_steps = cur_item >= full_items ? STEPS / 4 : STEPS / 2;
                 const int s = pr.s, u = ur.s;
                 ok = mbar_wait(pk_full(s), pr.ph, ab, 45);
                 if (!ok) break;
@@ -377,11 +399,14 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int half = 0; half < 2; ++half) {
                     const uint8_t *src = half ? pb : pa;
                     uint8_t *dst = half ? ub : ua;
+                    const int n_steps = half ? b_steps : STEPS / 2;
                     uint4 pk[STEPS / 2];
 #pragma unroll
-                    for (int i = 0; i < STEPS / 2; ++i) pk[i] = *reinterpret_cast<const uint4 *>(src + i * GT * 16);
+                    for (int i = 0; i < STEPS / 2; ++i)
+                        if (i < n_steps) pk[i] = *reinterpret_cast<const uint4 *>(src + i * GT * 16);
 #pragma unroll
                     for (int i = 0; i < STEPS / 2; ++i) {
+                        if (i >= n_steps) break;
                         uint4 e, od;
                         // the shift runs as a multiply on the FMA pipe, the masks on the ALU pipe
                         e.x = (pk[i].x * 16u) & 0xF0F0F0F0u; od.x = pk[i].x & 0xF0F0F0F0u;
