@@ -314,13 +314,36 @@ def run_ours(args, rank, world, local_rank):
     rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in range(args.steps)) / args.steps for j in range(3)]
     gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in range(args.steps)) / args.steps for j in range(3)]
 
-    # ---- end to end through the public API from pinned host memory
+    # ---- end to end through the public API from pinned host memory.  Every step copies its inputs host -> device
+    # and its outputs device -> host; the two directions of the link run at the same time (three streams: copy-in,
+    # compute, copy-out, ordered by events, one device buffer per linear), as a serving loop would drive it.
+    s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    x_dev = [torch.empty_like(w["x_host"], device=dev) for w in weights]
+    ev_x_ready = [torch.cuda.Event() for _ in weights]
+    ev_x_free = [torch.cuda.Event() for _ in weights]
+    ev_y_ready = [torch.cuda.Event() for _ in weights]
+    ev_y_done = [torch.cuda.Event() for _ in weights]
+    y_keep = [None] * len(weights)
+
     def e2e_step():
-        for w, oh in zip(weights, out_host):
-            x = w["x_host"].to(dev, non_blocking=True)
-            pk = kernel.rotate_quant(x, w["hadK"], w["K"], sign=w["sign"])
-            y = kernel.w4a4_linear(pk, w["w"], w["ws"])
-            oh.copy_(y, non_blocking=True)
+        for j, (w, oh) in enumerate(zip(weights, out_host)):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_x_free[j])
+                x_dev[j].copy_(w["x_host"], non_blocking=True)
+                ev_x_ready[j].record(s_in)
+            with torch.cuda.stream(s_comp):
+                s_comp.wait_event(ev_x_ready[j])
+                pk = kernel.rotate_quant(x_dev[j], w["hadK"], w["K"], sign=w["sign"])
+                ev_x_free[j].record(s_comp)
+                s_comp.wait_event(ev_y_done[j])      # the previous result of this linear has left the device
+                y = kernel.w4a4_linear(pk, w["w"], w["ws"])
+                ev_y_ready[j].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_y_ready[j])
+                oh.copy_(y, non_blocking=True)
+                ev_y_done[j].record(s_out)
+                y.record_stream(s_out)
+            y_keep[j] = y
     e2e_steps = max(2, min(args.steps, 10))
     e2e_step()
     torch.cuda.synchronize()
