@@ -111,6 +111,12 @@ int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, co
     ep.a_zero = (const int8_t *)a_zero;
     ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
     ep.expert_ids = (const int32_t *)expert_ids;
+    // few rows per expert (decode): the weight-streaming kernel; otherwise the CTA-pair tensor-core kernel.
+    // sr_set_gemm_kernel(4 / 5) pins one of them.
+    const int f = forced_kernel();
+    if (f == 5 || (f != 4 && rows <= 16 * num_experts))
+        return launch_gemm_skinny_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,
+                                          (const int32_t *)row_offsets, (int)num_experts, as_stream(stream));
     return launch_gemm_tc3_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,
                                    (const int32_t *)row_offsets, (int)num_experts, as_stream(stream));
 }

@@ -50,21 +50,34 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32
 
 // ring: SK_RING_BYTES per warp (steps of 1 KB per m-tile); red: one or two buffers of [warp][MT][NT][4][32] ints
 constexpr int SK_RING_BYTES = 8192;
+constexpr int SK_MAX_EXPERTS = 512;
 constexpr size_t skinny_smem(int nt, int mt) {
     return (size_t)SK_WARPS * SK_RING_BYTES + (size_t)(nt <= 2 ? 2 : 1) * SK_WARPS * mt * nt * 4 * 32 * 4;
 }
 
-// NT = token blocks of 8 (M <= 8 * NT), MT = blocks of 16 weight rows a warp multiplies per step (the
-// activation fragments of a step are unpacked once for all of them).  A = activations [M, K/2], B = weights [N, K/2].
-template <int NT, int MT, bool A_UNSIGNED>
+// One unit of work: a block of ROWS weight rows of one problem against up to 8 * NT activation rows.
+// Dense launches have one problem; grouped (MoE) launches one per expert and, for an expert with more
+// than 8 * NT rows, one pass per 8 * NT rows (its weights are then streamed once per pass).
+struct SkItem {
+    uint32_t w_row;     // first weight row (expert offset included)
+    uint32_t n0;        // first output column
+    uint32_t x_row0;    // first activation row of the pass
+    uint32_t x_end;     // activation rows >= x_end do not exist
+};
+
+// NT = token blocks of 8 (at most 8 * NT activation rows per pass), MT = blocks of 16 weight rows a warp
+// multiplies per step (the activation fragments of a step are unpacked once for all of them).
+// A = activations [M, K/2], B = weights [N, K/2] (grouped: [E * N, K/2], row_off[E + 1] on the device).
+template <int NT, int MT, bool A_UNSIGNED, bool GROUPED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
-                   Epilogue ep) {
+                   const int32_t *__restrict__ row_off, int num_experts, Epilogue ep) {
     constexpr int ROWS = SK_ROWS * MT;                  // weight rows per block
     constexpr int STAGE = 1024 * MT;                    // bytes per warp and step
     constexpr int DEPTH = SK_RING_BYTES / STAGE;        // steps in flight per warp
     constexpr int RED_BUFS = NT <= 2 ? 2 : 1;
     extern __shared__ __align__(16) uint8_t sk_smem[];
+    __shared__ uint32_t item_start[GROUPED ? SK_MAX_EXPERTS + 1 : 1];   // first item of every expert
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     // ring[warp][stage][row slot 0 .. 2 MT - 1][lane] (16 bytes each)
@@ -76,27 +89,71 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     const uint32_t steps = (kp + SK_STEP - 1) / SK_STEP;
     const uint32_t blocks = (N + ROWS - 1) / ROWS;
     const bool has_steps = (uint32_t)warp < steps;
-    const uint8_t *x_row = A + (size_t)g * kp + 16 * q;
 
-    // queue of (row block, step) items of this warp, in the order they are consumed
-    uint32_t iss_blk = blockIdx.x, iss_step = warp;
-    const uint8_t *iss_ptr = B + ((size_t)iss_blk * ROWS + g) * kp + (size_t)iss_step * SK_STEP + 16 * q;
+    uint32_t total_items = blocks;
+    if (GROUPED) {
+        if (tid == 0) {
+            uint32_t acc = 0;
+            for (int e = 0; e < num_experts; ++e) {
+                item_start[e] = acc;
+                const int rows_e = row_off[e + 1] - row_off[e];
+                acc += rows_e > 0 ? (((uint32_t)rows_e + 8 * NT - 1) / (8 * NT)) * blocks : 0u;
+            }
+            item_start[num_experts] = acc;
+        }
+        __syncthreads();
+        total_items = item_start[num_experts];
+    }
+    auto decode = [&](uint32_t item) {
+        SkItem it;
+        if (!GROUPED) {
+            it.w_row = item * ROWS;
+            it.n0 = it.w_row;
+            it.x_row0 = 0;
+            it.x_end = M;
+        } else {
+            int lo = 0, hi = num_experts - 1;   // last expert whose first item is <= item (empty experts share a start)
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (item_start[mid] <= item) lo = mid;
+                else hi = mid - 1;
+            }
+            const uint32_t local = item - item_start[lo];
+            it.n0 = (local % blocks) * ROWS;
+            it.w_row = (uint32_t)lo * N + it.n0;
+            it.x_row0 = (uint32_t)row_off[lo] + (local / blocks) * 8 * NT;
+            it.x_end = (uint32_t)row_off[lo + 1];
+        }
+        return it;
+    };
+
+    // queue of (item, step) of this warp, in the order they are consumed
+    uint32_t iss_item = blockIdx.x, iss_step = warp;
+    uint32_t iss_n0 = 0;
+    const uint8_t *iss_ptr = B;
+    auto iss_open = [&]() {
+        if (iss_item < total_items) {
+            const SkItem it = decode(iss_item);
+            iss_n0 = it.n0;
+            iss_ptr = B + ((size_t)it.w_row + g) * kp + (size_t)warp * SK_STEP + 16 * q;
+        }
+    };
+    iss_open();
     auto issue = [&](int slot) {
-        if (has_steps && iss_blk < blocks) {
+        if (has_steps && iss_item < total_items) {
             const bool k_ok = iss_step * SK_STEP + 16 * q + 16 <= kp;
-            const uint32_t row = iss_blk * ROWS + g;
             const uint32_t dst = ring_u32 + (uint32_t)slot * STAGE;
 #pragma unroll
             for (int r = 0; r < 2 * MT; ++r) {
-                const bool ok = k_ok && row + 8 * r < N;
+                const bool ok = k_ok && iss_n0 + g + 8 * r < N;
                 cp_async16(dst + r * 512, ok ? iss_ptr + (size_t)(8 * r) * kp : B, ok ? 16u : 0u);
             }
             iss_step += SK_WARPS;
             iss_ptr += SK_WARPS * SK_STEP;
             if (iss_step >= steps) {
                 iss_step = warp;
-                iss_blk += gridDim.x;
-                iss_ptr = B + ((size_t)iss_blk * ROWS + g) * kp + (size_t)warp * SK_STEP + 16 * q;
+                iss_item += gridDim.x;
+                iss_open();
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -105,20 +162,24 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     for (int d = 0; d < DEPTH; ++d) issue(d);
 
     // activation fragments of the step after the current one (they come from L1/L2, one step ahead is enough)
-    auto load_x = [&](uint32_t step, uint4 (&x)[NT]) {
+    auto load_x = [&](const SkItem &it, uint32_t step, uint4 (&x)[NT]) {
         const bool k_ok = step * SK_STEP + 16 * q + 16 <= kp;
-        const uint8_t *xs = x_row + (size_t)step * SK_STEP;
+        const uint8_t *xs = A + ((size_t)it.x_row0 + g) * kp + 16 * q + (size_t)step * SK_STEP;
 #pragma unroll
         for (int t = 0; t < NT; ++t)
-            x[t] = k_ok && (uint32_t)(g + 8 * t) < M ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * kp))
-                                                     : make_uint4(0, 0, 0, 0);
+            x[t] = k_ok && it.x_row0 + g + 8 * t < it.x_end ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * kp))
+                                                           : make_uint4(0, 0, 0, 0);
     };
+    uint32_t item = blockIdx.x;
+    SkItem cur = decode(item < total_items ? item : 0u);
     uint4 xn[NT];
-    if (has_steps) load_x(warp, xn);
+    if (has_steps && item < total_items) load_x(cur, warp, xn);
 
     int slot = 0;
     uint32_t parity = 0;
-    for (uint32_t blk = blockIdx.x; blk < blocks; blk += gridDim.x, parity ^= (RED_BUFS - 1)) {
+    for (; item < total_items; item += gridDim.x, parity ^= (RED_BUFS - 1)) {
+        const bool more = item + gridDim.x < total_items;
+        const SkItem nxt = decode(more ? item + gridDim.x : item);
         int acc[MT][NT][4];
 #pragma unroll
         for (int m = 0; m < MT; ++m)
@@ -132,7 +193,8 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 uint4 x[NT];
 #pragma unroll
                 for (int t = 0; t < NT; ++t) x[t] = xn[t];
-                load_x(s + SK_WARPS < steps ? s + SK_WARPS : (uint32_t)warp, xn);
+                if (s + SK_WARPS < steps) load_x(cur, s + SK_WARPS, xn);
+                else if (more) load_x(nxt, warp, xn);
                 asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
                 uint4 w[2 * MT];
 #pragma unroll
@@ -173,25 +235,24 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
         __syncthreads();
         // fragment slot i of lane (g, q) in m-tile m: weight row 16 m + g + 8 * (i >> 1), token 2 * q + (i & 1) of its
         // block.  With two buffers the one written two blocks later is this one: the barrier in between orders it.
-        const uint32_t n0 = blk * ROWS;
         for (int idx = tid; idx < MT * NT * 128; idx += SK_WARPS * 32) {
             const int l = idx & 31, i = (idx >> 5) & 3, t = (idx >> 7) % NT, m = idx / (NT * 128);
             int sum = 0;
 #pragma unroll
             for (int w = 0; w < SK_WARPS; ++w) sum += rb[(((w * MT + m) * NT + t) * 4 + i) * 32 + l];
-            const uint32_t n = n0 + 16 * m + (l >> 2) + 8 * (i >> 1);
-            const uint32_t mm = 8 * t + 2 * (l & 3) + (i & 1);
-            if (n < N && mm < M) ep.store(mm, n, sum >> 8, N);
+            const uint32_t n = cur.n0 + 16 * m + (l >> 2) + 8 * (i >> 1);
+            const uint32_t mm = cur.x_row0 + 8 * t + 2 * (l & 3) + (i & 1);
+            if (n < N && mm < cur.x_end) ep.store(mm, n, sum >> 8, N);
         }
+        cur = nxt;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 }  // namespace
 
-int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                       const Epilogue &ep, cudaStream_t st) {
-    SR_REQUIRE(M >= 1 && M <= 64, SR_ERR_UNSUPPORTED, "matmul: the decode kernel takes at most 64 rows");
+static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                         const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "matmul: operands must be 16-byte aligned");
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "matmul: K = %lld must be a multiple of 32", (long long)K);
     static int sm_count = 0;
@@ -201,35 +262,56 @@ int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N,
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
+    const bool grouped = row_off != nullptr;
+    // grouped launches: 32 rows per pass (an expert with more rows streams its weights again for the rest)
+    const int nt = grouped ? 4 : (M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)));
     // two m-tiles per warp step when there are enough row blocks to keep every SM busy and the sums fit
     const int mt = (nt <= 4 && (N >= 8192 || (N >= 4096 && nt >= 2))) ? 2 : 1;   // measured crossover
-    const int64_t blocks = cdiv<int64_t>(N, SK_ROWS * mt);
+    const int64_t blocks = cdiv<int64_t>(N, SK_ROWS * mt) * (grouped ? num_experts : 1);
     // two CTAs per SM; the row blocks are dealt round-robin, so shrink the grid to even the deal out
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas) ctas = blocks;
     else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas));
     const unsigned grid = (unsigned)ctas;
-#define SR_SK(NT, MT)                                                                                          \
+#define SR_SK(NT, MT, GR)                                                                                      \
     do {                                                                                                       \
-        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, MT, true> : gemm_skinny_kernel<NT, MT, false>;          \
+        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, MT, true, GR> : gemm_skinny_kernel<NT, MT, false, GR>;  \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                              (int)skinny_smem(NT, MT));                                        \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, MT), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, ep); \
+        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, MT), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, row_off, \
+                                                               num_experts, ep);                               \
     } while (0)
-    if (mt == 2) {
-        if (nt == 1) SR_SK(1, 2);
-        else if (nt == 2) SR_SK(2, 2);
-        else SR_SK(4, 2);
+    if (grouped) {
+        if (mt == 2) SR_SK(4, 2, true);
+        else SR_SK(4, 1, true);
+    } else if (mt == 2) {
+        if (nt == 1) SR_SK(1, 2, false);
+        else if (nt == 2) SR_SK(2, 2, false);
+        else SR_SK(4, 2, false);
     } else {
-        if (nt == 1) SR_SK(1, 1);
-        else if (nt == 2) SR_SK(2, 1);
-        else if (nt == 4) SR_SK(4, 1);
-        else SR_SK(8, 1);
+        if (nt == 1) SR_SK(1, 1, false);
+        else if (nt == 2) SR_SK(2, 1, false);
+        else if (nt == 4) SR_SK(4, 1, false);
+        else SR_SK(8, 1, false);
     }
 #undef SR_SK
     return check_launch("gemm_skinny");
+}
+
+int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                       const Epilogue &ep, cudaStream_t st) {
+    SR_REQUIRE(M >= 1 && M <= 64, SR_ERR_UNSUPPORTED, "matmul: the decode kernel takes at most 64 rows");
+    return launch_skinny(A, B, M, N, K, a_unsigned, ep, nullptr, 0, st);
+}
+
+int launch_gemm_skinny_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
+                               const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
+    SR_REQUIRE(num_experts >= 1 && num_experts <= SK_MAX_EXPERTS, SR_ERR_UNSUPPORTED,
+               "grouped_linear: at most %d experts", SK_MAX_EXPERTS);
+    SR_REQUIRE((int64_t)num_experts * N < (1ll << 31) && rows < (1ll << 31), SR_ERR_UNSUPPORTED,
+               "grouped_linear: size out of range");
+    return launch_skinny(A, B, rows, N, K, a_unsigned, ep, row_off, num_experts, st);
 }
 
 }  // namespace sr

@@ -12,10 +12,11 @@ captured in a CUDA graph):
 `use_grouped=False` runs the per-expert loop over the dense kernels (host-synchronising);
 it is the equivalence check for the grouped path, bit-identical by construction.
 
-The grouped GEMM + dequant pair runs as ONE tensor-core launch (`kernel.grouped_linear`) when
-the routed rows number at least `TENSOR_CORE_MIN_ROWS`; below that the weight-streaming grouped
-kernel followed by `sym_dequant_moe` (the reference's two calls) is the faster choice.  Both
-produce the same bits: the int32 accumulators are exact either way and the dequant arithmetic is shared.
+The grouped GEMM + dequant pair runs as ONE launch (`kernel.grouped_linear`): the library takes the
+weight-streaming mma.sync kernel when the routed rows average at most 16 per expert (decode) and
+the CTA-pair tcgen05 kernel otherwise.  The reference's two calls (`matmul_grouped` followed by
+`sym_dequant_moe`) remain for more than 512 experts.  All of them produce the same bits: the int32
+accumulators are exact either way and the dequant arithmetic is shared.
 """
 from __future__ import annotations
 
@@ -26,8 +27,6 @@ from ..functional.hadamard import get_hadK
 
 
 class SignRotMoEBlock(torch.nn.Module):
-    TENSOR_CORE_MIN_ROWS = 64
-
     def __init__(self, gate, *, top_k, norm_topk_prob,
                  w_gate, s_gate, w_up, s_up, w_down, s_down,
                  sign_down=None, wsum_gate=None, wsum_up=None, wsum_down=None,
@@ -104,7 +103,7 @@ class SignRotMoEBlock(torch.nn.Module):
 
     def _gemm_dequant_grouped(self, q, s, z, eid, row_off, w, s_w, wsum, gc):
         m, n = q.shape[0], w.shape[1]
-        if m >= self.TENSOR_CORE_MIN_ROWS and self.num_experts <= 512:
+        if self.num_experts <= 512:
             return kernel.grouped_linear(kernel.PackedQuantizedTensor(q, s, z), eid, self._row_off32, w, s_w, wsum)
         c = torch.empty((m, n), dtype=torch.int32, device=q.device)
         ptr_a = q.data_ptr() + row_off * q.shape[1]

@@ -94,10 +94,14 @@ def test_cuda_graph_replay():
     ([0, 0, 700], 256, 4096),                       # leading empty experts
     ([130] * 16, 768, 512),
     ([1, 2, 3, 4], 40, 64),
+    ([40, 0, 3, 1, 0, 0, 20, 0], 4096, 512),        # an expert with more rows than one pass of the decode kernel
 ])
 @pytest.mark.parametrize("asym", [False, True])
-def test_grouped_linear_bit_exact(counts, N, K, asym):
-    """One tensor-core launch for all experts == per-expert integer GEMM + expert-indexed dequant."""
+@pytest.mark.parametrize("which", [0, 4, 5], ids=["auto", "tcgen05_2cta", "few_rows_mma"])
+def test_grouped_linear_bit_exact(counts, N, K, asym, which):
+    """One launch for all experts == per-expert integer GEMM + expert-indexed dequant, for both grouped kernels."""
+    from signrot_b200 import _lib
+    _lib.call_nostream("sr_set_gemm_kernel", which)
     E, rows = len(counts), sum(counts)
     g = torch.Generator().manual_seed(rows + N)
     lo, hi = (0, 16) if asym else (-8, 8)
@@ -119,6 +123,6 @@ def test_grouped_linear_bit_exact(counts, N, K, asym):
     want = oracle.sym_dequant_moe(acc, sa.view(-1, 1), sw, eid, zero, wsum)
     pk = kernel.PackedQuantizedTensor(A.to(DEV), sa.to(DEV), zero.to(DEV) if asym else None)
     got = kernel.grouped_linear(pk, eid.to(DEV), off.to(DEV), W.to(DEV), sw.to(DEV), wsum.to(DEV) if asym else None)
-    from signrot_b200 import _lib
+    _lib.call_nostream("sr_set_gemm_kernel", 0)
     assert _lib.device_status() == 0
     assert torch.equal(got.cpu(), want)
