@@ -589,6 +589,7 @@ def run_sweep():
         print(json.dumps({"case": "decode_step_llama3_8b_layer", "error": str(e)[:200]}))
     cache.freeze_specs(False)
     # config 5: one Mixtral-8x7B-shaped MoE block (8 experts, top-2, hidden 4096, ffn 14336)
+    from signrot_b200 import nn as snn
     E, hid, ffn, top_k = 8, 4096, 14336, 2
     gen = torch.Generator().manual_seed(1)
     def wq(nn_, kk_):
