@@ -1,7 +1,7 @@
 """Imports the reference's own Python on the CPU (test infrastructure only).
 
-Works only where a SignRot checkout is present (default /root/reference, or
-$SIGNROT_REFERENCE); used by tests/golden/make_golden.py to produce the committed golden
+Works only where a SignRot checkout is present (its path in $SIGNROT_REFERENCE, else the
+directory `reference` beside this repository's parent); used by tests/golden/make_golden.py to produce the committed golden
 vectors and by CPU tests that compare the oracle with the reference directly (skipped when
 the checkout is absent, e.g. on the GPU box).
 
@@ -22,7 +22,7 @@ from pathlib import Path
 
 import torch
 
-REF = Path(os.environ.get("SIGNROT_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("SIGNROT_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
 
 
 def available() -> bool:

@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own Python on the CPU.
 
-    python tests/golden/make_golden.py            # needs a SignRot checkout (/root/reference)
+    SIGNROT_REFERENCE=<SignRot checkout> python tests/golden/make_golden.py
 
 The reference has no stored golden vectors for this path; these files pin the oracle (and,
 through it, the CUDA kernels) to what the reference's code computes on fixed seeded inputs.
