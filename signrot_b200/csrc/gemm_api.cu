@@ -7,7 +7,7 @@
 
 namespace sr {
 
-// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; M <= 128: kernel 3; else kernel 4),
+// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; else kernel 4),
 // 1 = dp4a weight-streaming kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
 // 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel,
 // 5 = weight-streaming mma.sync kernel of the decode regime (M <= 64).
@@ -45,9 +45,9 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     if (small)
         return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
                                  as_stream(stream));
-    if (f == 4 || (f == 0 && M > 128))
+    if (f == 4 || f == 0)
         return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
-    if (f == 3 || f == 0)
+    if (f == 3)
         return launch_gemm_tc2((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
     return launch_gemm_tc((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
 }

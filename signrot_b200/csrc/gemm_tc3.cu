@@ -245,8 +245,9 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t num_tiles = tiles_n * tiles_m;
     // Work items.  Tiles are dealt round-robin to the clusters; when the last round would leave at least half of
     // the clusters idle, its tiles are split into two 256 x 128 halves so that the round costs half a tile.
+    // (A problem with so few tiles that even the halves leave clusters idle is split entirely.)
     const uint32_t rem = num_tiles % clusters;
-    const uint32_t split = (rem != 0 && 2 * rem <= clusters) ? rem : 0u;
+    const uint32_t split = (2 * num_tiles <= clusters) ? num_tiles : ((rem != 0 && 2 * rem <= clusters) ? rem : 0u);
     const uint32_t full_items = num_tiles - split, num_items = num_tiles + split;
     auto coord = [&](uint32_t item) {
         TileCoord c;
@@ -505,7 +506,8 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     const int64_t m_tiles = row_off ? cdiv<int64_t>(M, 2 * BMC) + num_experts : cdiv<int64_t>(M, 2 * BMC);
     const int64_t tiles = cdiv<int64_t>(N, BN) * m_tiles;
     int64_t clusters = sm_count / 2;
-    if (tiles < clusters) clusters = tiles;
+    if (2 * tiles <= clusters) clusters = 2 * tiles;   // every tile is split into two halves (see the kernel)
+    else if (tiles < clusters) clusters = tiles;
     // SIGNROT_B200_TC3_STAGES="<packed ring>,<int8 ring>,<unpack groups>" is a tuning knob
     static int sp = 0, su = 0, groups = 0;
     if (sp == 0) {
