@@ -74,12 +74,15 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// arrive on the barrier at the same offset in CTA `cta` of the cluster
+// Arrive on the barrier at the same offset in CTA `cta` of the cluster.  CTA-scope release (the default) is
+// what is needed: the data this signal publishes (an unpacked stage, a drained accumulator) is consumed by this
+// SM's own tensor core and TMEM, only the signal crosses to the partner.  A cluster-scope release stalls the
+// arriving warp for several hundred cycles per k-block.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
     asm volatile(
         "{\n\t.reg .b32 remaddr;\n\t"
         "mapa.shared::cluster.u32 remaddr, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remaddr];\n\t}"
+        "mbarrier.arrive.shared::cluster.b64 _, [remaddr];\n\t}"
         ::"r"(bar), "r"(cta)
         : "memory");
 }
@@ -405,6 +408,18 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < STEPS / 2; ++i)
                         if (i < n_steps) pk[i] = *reinterpret_cast<const uint4 *>(src + i * GT * 16);
+                    if (half == 1) {
+                        // every packed byte of the stage is in registers (the masks below depend on the loads of this
+                        // half, the first half was consumed before): the TMA producer may refill it while the rest of
+                        // the conversion, the stores and the fence run
+                        uint32_t seen = 0;
+#pragma unroll
+                        for (int i = 0; i < STEPS / 2; ++i)
+                            if (i < n_steps) seen |= pk[i].x | pk[i].y | pk[i].z | pk[i].w;
+                        asm volatile("" ::"r"(seen) : "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(pk_empty(s));
+                    }
 #pragma unroll
                     for (int i = 0; i < STEPS / 2; ++i) {
                         if (i >= n_steps) break;
@@ -421,10 +436,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive_cluster(un_full(u), 0);  // the leader's MMA warp waits for both CTAs
-                    mbar_arrive(pk_empty(s));
-                }
+                if (lane == 0) mbar_arrive_cluster(un_full(u), 0);  // the leader's MMA warp waits for both CTAs
                 for (int i = 0; i < G; ++i) {
                     pr.next(SP);
                     ur.next(SU);
@@ -511,14 +523,14 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     // SIGNROT_B200_TC3_STAGES="<packed ring>,<int8 ring>,<unpack groups>" is a tuning knob
     static int sp = 0, su = 0, groups = 0;
     if (sp == 0) {
-        int a = 4, b = 4, c = 4;
+        int a = 5, b = 4, c = 4;
         const char *env = getenv("SIGNROT_B200_TC3_STAGES");
         if (env) sscanf(env, "%d,%d,%d", &a, &b, &c);
         const bool groups_ok = c == 1 || c == 2 || c == 4;
         // a group may run at most one pass ahead of a ring's barriers: groups <= both ring depths
         if (a < 2 || a > MAX_STAGES || b < 2 || b > MAX_STAGES || !groups_ok || c > a || c > b ||
             smem_bytes(a, b) > MAX_SMEM) {
-            a = 4;
+            a = 5;
             b = 4;
             c = 4;
         }
