@@ -91,6 +91,52 @@ __device__ __forceinline__ void store_acc_chunk(const Epilogue &ep, uint32_t row
     }
 }
 
+// Warp-collective variant of the dequant path for the tcgen05 epilogues: lane l holds 32 consecutive columns
+// of row row0 + l.  When the plain symmetric case applies to the whole chunk (uniform across the warp), the 64
+// output bytes of every row go through a 32 x 80-byte staging area in shared memory and leave as 64-byte runs,
+// four lanes per row: whole 32-byte sectors instead of the half sectors a lane-per-row store writes.
+// `stage` = 2560 bytes private to the warp.  Falls back to store_acc_chunk otherwise.
+__device__ __forceinline__ void store_acc_chunk_warp(const Epilogue &ep, uint32_t row0, int lane, uint32_t col0,
+                                                     const int (&v)[32], uint32_t row_end, uint32_t N, bool small,
+                                                     uint8_t *stage) {
+    if (row0 >= row_end) return;   // warp-uniform: none of the 32 rows exists
+    const uint32_t row = row0 + lane;
+    bool vec = false;
+    if (ep.mode == 1 && col0 + 32 <= N && !ep.a_zero && !ep.bias) {
+        const size_t e = ep.expert_ids ? (size_t)ep.expert_ids[row < row_end ? row : row0] * N : 0;
+        const __half *ws = ep.w_scale + e + col0;
+        vec = ((reinterpret_cast<uintptr_t>(ep.out + (size_t)row0 * N + col0) | reinterpret_cast<uintptr_t>(ws) |
+                (uintptr_t)(N * 2)) & 15u) == 0;
+        vec = __all_sync(0xffffffffu, vec);
+        if (vec) {
+            const float sr_ = row < row_end ? __half2float(ep.a_scale[row]) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                Vec16 s, o;
+                s.u = __ldg(reinterpret_cast<const uint4 *>(ws + j));
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float2 sc = __half22float2(s.h2[t]);
+                    const float a = (int_to_float_fast(v[j + 2 * t] >> 8, small) * sr_) * sc.x;
+                    const float b = (int_to_float_fast(v[j + 2 * t + 1] >> 8, small) * sr_) * sc.y;
+                    o.h2[t] = __floats2half2_rn(a, b);
+                }
+                *reinterpret_cast<uint4 *>(stage + lane * 80 + j * 2) = o.u;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                const int r = it * 8 + (lane >> 2), piece = lane & 3;
+                const uint4 val = *reinterpret_cast<const uint4 *>(stage + r * 80 + piece * 16);
+                if (row0 + r < row_end)
+                    *reinterpret_cast<uint4 *>(ep.out + (size_t)(row0 + r) * N + col0 + piece * 8) = val;
+            }
+            __syncwarp();
+        }
+    }
+    if (!vec) store_acc_chunk(ep, row, col0, v, row_end, N, small);
+}
+
 int launch_gemm_small(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                       const Epilogue &ep, cudaStream_t st);
 int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,

@@ -48,9 +48,10 @@ constexpr long long WAIT_BUDGET = 1500000000ll;
 constexpr int BAR_BYTES = 512;
 constexpr int MAX_EXPERTS = 512;                    // grouped launches: first m-tile of every expert, in shared memory
 constexpr int SCHED_BYTES = (MAX_EXPERTS + 4) * 4;
+constexpr int EPI_STAGE_BYTES = 4 * 2560;           // one 32 x 80-byte output staging area per epilogue warp
 constexpr int MAX_SMEM = 226 * 1024;   // dynamic part; the kernel also has a few static words
 __host__ __device__ constexpr int smem_bytes(int sp, int su) {
-    return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + SCHED_BYTES + 1024;
+    return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + SCHED_BYTES + EPI_STAGE_BYTES + 1024;
 }
 
 // position in a ring of `depth` stages and the parity of the current pass over it
@@ -204,6 +205,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool grouped = row_off != nullptr;
     // mt_start[e] = number of m-tiles of the experts before e (grouped launches only)
     uint32_t *mt_start = reinterpret_cast<uint32_t *>(base_ptr + off_pk_b + SP * PK_B + BAR_BYTES);
+    uint8_t *epi_stage = base_ptr + off_pk_b + SP * PK_B + BAR_BYTES + SCHED_BYTES;
 
     if (tid == 0) {
         if (grouped) {
@@ -345,7 +347,8 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 ok = mbar_wait(acc_full(buf), (it >> 1) & 1, ab, 44);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t row = m0 + quarter * 32 + lane;
+                const uint32_t row0 = m0 + quarter * 32;
+                uint8_t *stage = epi_stage + quarter * 2560;
 #pragma unroll 1
                 for (int c = 0; c < chunks; ++c) {
                     int v[32];
@@ -355,7 +358,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(acc_empty(buf), 0);
                     }
-                    store_acc_chunk(ep, row, n0 + c * 32, v, tc.row_end, N, small);
+                    store_acc_chunk_warp(ep, row0, lane, n0 + c * 32, v, tc.row_end, N, small, stage);
                 }
             }
         } else {
