@@ -35,6 +35,8 @@ act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict_
 
     Vec16 v[NV];
     float vmax = ASYM ? -FLT_MAX : 0.f, vmin = FLT_MAX;
+    __half2 hmax2 = __floats2half2_rn(ASYM ? -65504.f : 0.f, ASYM ? -65504.f : 0.f);
+    __half2 hmin2 = __floats2half2_rn(65504.f, 65504.f);
     if (live) {
         const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
         const int8_t *sr_ = sign ? sign + (size_t)(expert_ids ? expert_ids[row] : 0) * cols : nullptr;
@@ -55,18 +57,21 @@ act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict_
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float f = __half2float(v[i].h[j]);
+                for (int j = 0; j < 4; ++j) {
                     if (ASYM) {
-                        vmax = fmaxf(vmax, f);
-                        vmin = fminf(vmin, f);
+                        hmax2 = __hmax2(hmax2, v[i].h2[j]);
+                        hmin2 = __hmin2(hmin2, v[i].h2[j]);
                     } else {
-                        vmax = fmaxf(vmax, fabsf(f));
+                        hmax2 = __hmax2(hmax2, __habs2(v[i].h2[j]));
                     }
                 }
             }
         }
     }
+    // packed fp16 maxima are exact (comparisons only); widen once
+    vmax = fmaxf(__low2float(hmax2), __high2float(hmax2));
+    if (ASYM) vmin = fminf(__low2float(hmin2), __high2float(hmin2));
+    if (!ASYM && vmax < 0.f) vmax = 0.f;
     // team reduction
     if (TPR <= 32) {
 #pragma unroll
@@ -118,17 +123,41 @@ act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict_
         rcp = rcp_approx_ftz(__half2float(scale));
     }
 
+    // Codes on packed fp16 pairs, the arithmetic of sym_code / asym_code without the conversion unit:
+    // quotient rn_h(x * rcp), clamp, round half to even by the fp16 addition of 1536 (the low byte of the sum is
+    // then the integer; + 8 makes signed codes non-negative until the last xor), bytes gathered with permutes.
+    // A zero scale gives rcp = inf and 0 * inf = NaN (code 0 in the scalar path): a huge finite factor gives the
+    // same codes without the NaN.
+    const float rcp_f = fminf(rcp, 3.0e38f);
+    const float zf = (float)zero_i;
+    const __half2 lo_c = __floats2half2_rn(ASYM ? -zf : -8.f, ASYM ? -zf : -8.f);
+    const __half2 hi_c = __floats2half2_rn(ASYM ? 15.f - zf : 7.f, ASYM ? 15.f - zf : 7.f);
+    const __half2 magic = __floats2half2_rn(ASYM ? 1536.f : 1544.f, ASYM ? 1536.f : 1544.f);
+    const uint32_t zero_u = (uint32_t)(zero_i & 15) * 0x00010001u;
     uint32_t *qr = reinterpret_cast<uint32_t *>(q + (size_t)row * (cols >> 1));
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const uint32_t vi = sub + i * TPR;
         if (vi < nvec) {
-            uint32_t packed = 0;
+            uint32_t bits[4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = ASYM ? asym_code(v[i].h[j], rcp, zero_i, 0, 15) : sym_code(v[i].h[j], rcp);
-                packed |= (uint32_t)(c & 15) << (4 * j);
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(v[i].h2[j]);
+                __half2 qh = __floats2half2_rn(f.x * rcp_f, f.y * rcp_f);
+                qh = __hmin2(__hmax2(qh, lo_c), hi_c);
+                qh = __hadd2(qh, magic);
+                bits[j] = *reinterpret_cast<uint32_t *>(&qh);
+                if (ASYM) bits[j] += zero_u;
             }
+            // bits[j] = halves (code of element 2j, code of element 2j + 1) in their low bytes
+            const uint32_t x01 = __byte_perm(bits[0], bits[1], 0x6240), x23 = __byte_perm(bits[2], bits[3], 0x6240);
+            uint32_t ev = __byte_perm(x01, x23, 0x5410), od = __byte_perm(x01, x23, 0x7632);
+            if (ASYM) {
+                ev &= 0x0F0F0F0Fu;
+                od &= 0x0F0F0F0Fu;
+            }
+            uint32_t packed = ev + (od << 4);
+            if (!ASYM) packed ^= 0x88888888u;
             qr[vi] = packed;
         }
     }
