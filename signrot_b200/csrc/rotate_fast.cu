@@ -271,7 +271,9 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
         use_tc = (e && !strcmp(e, "butterfly")) ? 0 : 1;
     }
     if (use_tc) {
-        const int rc = launch_rotate_tc4096(a, st);
+        int rc = launch_rotate_tc4096(a, st);
+        if (rc != SR_ERR_UNSUPPORTED) return rc;
+        rc = launch_rotate_heads32(a, st);
         if (rc != SR_ERR_UNSUPPORTED) return rc;
     }
     const bool shape_ok = a.n == 4096 && a.K == 1 && a.stride == 1 && a.S == 4096 && a.q != nullptr &&

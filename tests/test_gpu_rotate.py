@@ -198,3 +198,21 @@ def test_rotate_quant_4096_many_rows_self_consistent(rows):
     diff = (rot.float() - ref.float()).abs()
     tol = rot.float().abs() * 2.0 ** -10 + rot.float().abs().amax(dim=-1, keepdim=True) * 2.0 ** -17
     assert (diff > tol).float().mean().item() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [1, 37, 600])
+def test_rotate_quant_heads32_symmetric(dtype, rows):
+    """Head-wise rotation of a 32-head, head_dim-128 row (the o_proj input) with symmetric codes:
+    the tensor-core kernel against the oracle and against the stand-alone quantizer."""
+    x = _x(rows, 4096, 17 + rows, dtype)
+    pk, rot = kernel.rotate_quant(x.to(DEV), heads=32, return_rotated=True)
+    want_rot = oracle.rotate_heads(x, 32, cast_in_to_f16=True)
+    _ulp_close(rot.cpu(), want_rot)
+    q2, s2 = kernel.sym_quant_dynamic(rot)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    pk3 = kernel.rotate_quant(x.to(DEV), heads=32)
+    assert torch.equal(pk3.quantized_x, pk.quantized_x) and torch.equal(pk3.scales_x, pk.scales_x)
+    codes, scale = oracle.sym_quant_dynamic(want_rot)
+    same = (pk.scales_x.cpu() == scale).view(-1)
+    assert_codes_close(oracle.unpack_i4(pk.quantized_x.cpu())[same], codes[same])
