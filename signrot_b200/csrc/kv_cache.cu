@@ -73,63 +73,92 @@ __device__ __forceinline__ void kv_params_dev(float vmin, float vmax, __half &sc
     zero = __hneg(hmin);
 }
 
-// One warp per (token, head, k|v) vector of 128: lane holds 4 consecutive values.
-// k, v: [B, T, heads, 128] fp16.  K goes through H_128 / sqrt(128) (fp32 butterflies,
-// rounded to fp16: kv_cache.py:70-73,308-309) when had_k is set, then both are
-// quantised (fused.cu:214-265) straight into their page slots.
+// A warp takes KV_VPW consecutive (token, head, k|v) vectors of 128 at a time (lane holds 4 consecutive values
+// of each; the loads and the shuffle butterflies of the KV_VPW vectors are independent, which is what hides
+// their latency).  k, v: [B, T, heads, 128] fp16.  K goes through H_128 / sqrt(128) (fp32 butterflies,
+// rounded to fp16: kv_cache.py:70-73,308-309) when had_k is set, then both are quantised (fused.cu:214-265)
+// straight into their page slots.
+constexpr int KV_VPW = 4;
+
 __global__ void __launch_bounds__(256)
 kv_append_quant_kernel(PagedKV kv, const __half *__restrict__ k, const __half *__restrict__ v, uint32_t batch,
                        uint32_t T, int had_k, float had_scale) {
-    const uint32_t w = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const uint32_t total = batch * T * kv.heads * 2;
-    if (w >= total) return;
-    const uint32_t which = w & 1;
-    const uint32_t vec = w >> 1;  // (b, t, head)
-    const uint32_t head = vec % kv.heads;
-    const uint32_t t = (vec / kv.heads) % T, b = vec / (kv.heads * T);
-    const __half *src = (which ? v : k) + (size_t)vec * HD + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2 *>(src);
-    const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
-    float a[4] = {__half2float(h01.x), __half2float(h01.y), __half2float(h23.x), __half2float(h23.y)};
-    if (which == 0 && had_k) {
-        float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
-        a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
+    const uint32_t warps = gridDim.x * 8;
+    for (uint32_t w0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * KV_VPW; w0 < total; w0 += warps * KV_VPW) {
+        float a[KV_VPW][4];
+        bool live[KV_VPW];
 #pragma unroll
-        for (int m = 1; m < 32; m <<= 1) {
+        for (int u = 0; u < KV_VPW; ++u) {
+            const uint32_t w = w0 + u;
+            live[u] = w < total;
+            uint2 raw = make_uint2(0, 0);
+            if (live[u]) raw = __ldg(reinterpret_cast<const uint2 *>(((w & 1) ? v : k) + (size_t)(w >> 1) * HD + lane * 4));
+            const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+            a[u][0] = __half2float(h01.x); a[u][1] = __half2float(h01.y);
+            a[u][2] = __half2float(h23.x); a[u][3] = __half2float(h23.y);
+        }
+        if (had_k) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float o = __shfl_xor_sync(0xffffffffu, a[j], m);
-                a[j] = (lane & m) ? (o - a[j]) : (a[j] + o);
+            for (int u = 0; u < KV_VPW; ++u) {
+                if (((w0 + u) & 1) == 0) {   // K vectors only (uniform across the warp)
+                    const float t0 = a[u][0] + a[u][1], t1 = a[u][0] - a[u][1], t2 = a[u][2] + a[u][3], t3 = a[u][2] - a[u][3];
+                    a[u][0] = t0 + t2; a[u][1] = t1 + t3; a[u][2] = t0 - t2; a[u][3] = t1 - t3;
+                }
             }
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int u = 0; u < KV_VPW; ++u) {
+                    if (((w0 + u) & 1) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float o = __shfl_xor_sync(0xffffffffu, a[u][j], m);
+                            a[u][j] = (lane & m) ? (o - a[u][j]) : (a[u][j] + o);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < KV_VPW; ++u)
+                if (((w0 + u) & 1) == 0)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a[u][j] = __half2float(__float2half_rn(a[u][j] * had_scale));
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
-    }
-    float vmax = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
-    float vmin = fminf(fminf(a[0], a[1]), fminf(a[2], a[3]));
-    vmax = warp_max(vmax);
-    vmin = warp_min(vmin);
-    __half scale, zero;
-    kv_params_dev(vmin, vmax, scale, zero);
-    const float fs = __half2float(scale), fz = __half2float(zero);
-    uint32_t code = 0;
+        for (int u = 0; u < KV_VPW; ++u) {
+            float vmax = fmaxf(fmaxf(a[u][0], a[u][1]), fmaxf(a[u][2], a[u][3]));
+            float vmin = fminf(fminf(a[u][0], a[u][1]), fminf(a[u][2], a[u][3]));
+            vmax = warp_max(vmax);
+            vmin = warp_min(vmin);
+            __half scale, zero;
+            kv_params_dev(vmin, vmax, scale, zero);
+            const float fs = __half2float(scale), fz = __half2float(zero);
+            uint32_t code = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const __half shifted = __float2half(a[j] + fz);
-        const __half scaled = __float2half(__half2float(shifted) / fs);
-        code |= (uint32_t)clampi((int)nearbyintf(__half2float(scaled)), 0, 15) << (4 * j);
-    }
-    const uint32_t pos = kv.seq_len(b) - T + t;
-    const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
-    const uint32_t entry = pos % kv.page_size;
-    const size_t vi = kv.vec_index(page, which, head, entry);
-    reinterpret_cast<uint16_t *>(kv.data + vi * 64)[lane] = (uint16_t)code;
-    if (lane == 0) {
-        __half2 p;
-        p.x = scale;
-        p.y = zero;
-        kv.param[vi] = p;
+            for (int j = 0; j < 4; ++j) {
+                const __half shifted = __float2half(a[u][j] + fz);
+                const __half scaled = __float2half(__half2float(shifted) / fs);
+                code |= (uint32_t)clampi((int)nearbyintf(__half2float(scaled)), 0, 15) << (4 * j);
+            }
+            if (live[u]) {
+                const uint32_t w = w0 + u, which = w & 1, vec = w >> 1;
+                const uint32_t head = vec % kv.heads;
+                const uint32_t t = (vec / kv.heads) % T, b = vec / (kv.heads * T);
+                const uint32_t pos = kv.seq_len(b) - T + t;
+                const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
+                const uint32_t entry = pos % kv.page_size;
+                const size_t vi = kv.vec_index(page, which, head, entry);
+                reinterpret_cast<uint16_t *>(kv.data + vi * 64)[lane] = (uint16_t)code;
+                if (lane == 0) {
+                    __half2 p;
+                    p.x = scale;
+                    p.y = zero;
+                    kv.param[vi] = p;
+                }
+            }
+        }
     }
 }
 
@@ -417,7 +446,10 @@ int sr_kv_append_quant(void *kv_data, void *kv_param, const void *kv_indptr, con
     const int64_t warps = batch_size * new_tokens * num_heads * 2;
     SR_REQUIRE(warps < (1ll << 31), SR_ERR_UNSUPPORTED, "kv_append_quant: too many tokens");
     const float had_scale = (float)(1.0 / sqrt(128.0));
-    kv_append_quant_kernel<<<(unsigned)cdiv<int64_t>(warps, 8), 256, 0, as_stream(stream)>>>(
+    // persistent over groups of KV_VPW vectors per warp; small launches keep one group per warp
+    int64_t ctas = cdiv<int64_t>(cdiv<int64_t>(warps, KV_VPW), 8);
+    if (ctas > 148 * 8) ctas = 148 * 8;
+    kv_append_quant_kernel<<<(unsigned)ctas, 256, 0, as_stream(stream)>>>(
         kv, (const __half *)k, (const __half *)v, (uint32_t)batch_size, (uint32_t)new_tokens, hadamard_k, had_scale);
     return check_launch("kv_append_quant");
 }
