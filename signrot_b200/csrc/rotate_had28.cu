@@ -50,18 +50,20 @@ __device__ __forceinline__ float had_pm(int r, int c) { return (__popc(r & c) & 
 // code(-v) = -code(v) as long as nothing saturates, which holds for clip = 1 and a normal fp16 scale
 // (|v / scale| < 7.5); such launches (no per-row sign table, no rotated output) skip the per-value
 // sign work, and a row whose scale is subnormal falls back to the value path.
-template <typename InT, bool LATE>
+// ASYM (never together with LATE): unsigned codes with a per-row zero point (asym_quant_dynamic).
+template <typename InT, bool LATE, bool ASYM>
 __global__ void __launch_bounds__(THREADS, 2)
 rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ hadk,
                           const int8_t *__restrict__ sign, const int32_t *__restrict__ expert_ids, uint32_t rows,
                           float scale, float clip, uint8_t *__restrict__ q, __half *__restrict__ q_scale,
-                          __half *__restrict__ rotated) {
+                          __half *__restrict__ q_zero, __half *__restrict__ rotated) {
+    static_assert(!(LATE && ASYM), "the sign can only move onto symmetric codes");
     constexpr bool BF16 = std::is_same<InT, __nv_bfloat16>::value;
     extern __shared__ __align__(16) uint8_t smem[];
     __half *zbuf = reinterpret_cast<__half *>(smem + IMG_BYTES);
     uint8_t *obuf = smem + IMG_BYTES + Z_BYTES;
     const uint32_t img_u32 = (uint32_t)__cvta_generic_to_shared(smem);
-    __shared__ float red[14];
+    __shared__ float red[2][14];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, qd = lane & 3;  // mma fragment coordinates
@@ -228,7 +230,8 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
             y[ti][mt][0] = *reinterpret_cast<__half2 *>(&lw);
             y[ti][mt][1] = *reinterpret_cast<__half2 *>(&hw_);
         };
-        __half2 amax2 = __floats2half2_rn(0.f, 0.f);
+        __half2 amax2 = __floats2half2_rn(ASYM ? -65504.f : 0.f, ASYM ? -65504.f : 0.f);
+        __half2 amin2 = __floats2half2_rn(65504.f, 65504.f);
 #pragma unroll
         for (int ti = 0; ti < 5; ++ti) {
             if (ti < n_tiles) {
@@ -256,25 +259,69 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                     y[ti][mt][0] = __floats2half2_rn(c0, c1);
                     y[ti][mt][1] = __floats2half2_rn(c2, c3);
                     if (!LATE) flip(ti, mt);
-                    amax2 = __hmax2(amax2, __hmax2(__habs2(y[ti][mt][0]), __habs2(y[ti][mt][1])));
+                    if (ASYM) {
+                        // rows 28..31 are padding: their zeros must not enter the range
+                        amax2 = __hmax2(amax2, y[ti][mt][0]);
+                        amin2 = __hmin2(amin2, y[ti][mt][0]);
+                        if (mt == 0 || g < 4) {
+                            amax2 = __hmax2(amax2, y[ti][mt][1]);
+                            amin2 = __hmin2(amin2, y[ti][mt][1]);
+                        }
+                    } else {
+                        amax2 = __hmax2(amax2, __hmax2(__habs2(y[ti][mt][0]), __habs2(y[ti][mt][1])));
+                    }
                 }
             }
         }
         float amax = warp_max(fmaxf(__low2float(amax2), __high2float(amax2)));
-        if (lane == 0) red[warp] = amax;
+        float amin = ASYM ? warp_min(fminf(__low2float(amin2), __high2float(amin2))) : 0.f;
+        if (lane == 0) {
+            red[0][warp] = amax;
+            red[1][warp] = amin;
+        }
         __syncthreads();
-        amax = red[0];
+        amax = red[0][0];
+        amin = red[1][0];
 #pragma unroll
-        for (int w = 1; w < 14; ++w) amax = fmaxf(amax, red[w]);
-        __half s = __float2half(amax / 7.f);
-        if (clip != 1.f) s = __float2half(__half2float(s) * clip);
-        if (tid == 0) q_scale[row] = s;
+        for (int w = 1; w < 14; ++w) {
+            amax = fmaxf(amax, red[0][w]);
+            amin = fminf(amin, red[1][w]);
+        }
+        __half s;
+        __half2 lo_c, hi_c, magic;
+        uint32_t zero_u = 0;
+        if (!ASYM) {
+            s = __float2half(amax / 7.f);
+            if (clip != 1.f) s = __float2half(__half2float(s) * clip);
+            if (tid == 0) q_scale[row] = s;
+            lo_c = __floats2half2_rn(-8.f, -8.f);
+            hi_c = __floats2half2_rn(7.f, 7.f);
+            magic = __floats2half2_rn(1544.f, 1544.f);   // codes leave as code + 8 until the last step
+        } else {
+            __half hmin = __float2half(amin), hmax = __float2half(amax);
+            if (clip != 1.f) {
+                hmin = __float2half(__half2float(hmin) * clip);
+                hmax = __float2half(__half2float(hmax) * clip);
+            }
+            const __half diff = __float2half(__half2float(hmax) - __half2float(hmin));
+            s = __float2half(__half2float(diff) / 15.f);
+            const __half ratio = __float2half(-__half2float(hmin) / __half2float(s));
+            const __half zero = __float2half(nearbyintf(__half2float(ratio)));
+            if (tid == 0) {
+                q_scale[row] = s;
+                q_zero[row] = zero;
+            }
+            // clamp(rint(v) + z, 0, 15) = rint(clamp(v, -z, 15 - z)) + z for an integer z; z enters modulo 16 after the rounding
+            const float zf = __half2float(zero);
+            lo_c = __floats2half2_rn(-zf, -zf);
+            hi_c = __floats2half2_rn(15.f - zf, 15.f - zf);
+            magic = __floats2half2_rn(1536.f, 1536.f);
+            zero_u = (uint32_t)(__half2int_rn(zero) & 15) * 0x00010001u;
+        }
         // a zero scale would give 0 * inf = NaN (code 0 in the reference): a huge finite factor
         // yields the same codes without the NaN
         const float rcp = fminf(rcp_approx_ftz(__half2float(s)), 3.0e38f);
         const u64 rcp2 = pack2(rcp, rcp);
-        const __half2 lo_c = __floats2half2_rn(-8.f, -8.f), hi_c = __floats2half2_rn(7.f, 7.f);
-        const __half2 magic = __floats2half2_rn(1544.f, 1544.f);   // codes leave as code + 8 until the last step
         // no quotient reaches 7.5 when the scale is a normal fp16 number and nothing was clipped
         const bool safe = LATE && __half2float(s) >= 6.2e-5f;
         if (LATE && !safe) {
@@ -304,7 +351,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                             __half2 qh = __floats2half2_rn(lo, hi);
                             if (!safe) qh = __hmin2(__hmax2(qh, lo_c), hi_c);
                             qh = __hadd2(qh, magic);
-                            const uint32_t r = *reinterpret_cast<uint32_t *>(&qh) & 0x000F000Fu;
+                            const uint32_t r = (*reinterpret_cast<uint32_t *>(&qh) + zero_u) & 0x000F000Fu;
                             ob[(16 * mt + 8 * hh) * OUTP + 56 * ti] = (uint8_t)(r | (r >> 12));
                             if (!LATE && rotated != nullptr)
                                 *reinterpret_cast<__half2 *>(rotated + (size_t)row * N + kp * SEG + 8 * (warp + 14 * ti) + 2 * qd) = p;
@@ -323,7 +370,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
                     // negate where the sign is -1: a code + 8 in 1..15 becomes 16 - it, nibble by nibble without carries
                     w[i] = (w[i] ^ late_mask[i]) + (late_mask[i] & 0x11111111u);
                 }
-                w[i] ^= 0x88888888u;   // code + 8 -> two's complement nibble
+                if (!ASYM) w[i] ^= 0x88888888u;   // code + 8 -> two's complement nibble
             }
             reinterpret_cast<uint4 *>(q + (size_t)row * (N / 2))[tid] = make_uint4(w[0], w[1], w[2], w[3]);
         }
@@ -333,7 +380,8 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
 }  // namespace
 
 int launch_rotate_had28(const RotateArgs &a, cudaStream_t st) {
-    const bool ok = a.n == N && a.K == KH && a.stride == 1 && a.q != nullptr && !a.asym && !a.fp32_mode &&
+    const bool ok = a.n == N && a.K == KH && a.stride == 1 && a.q != nullptr && !a.fp32_mode &&
+                    (!a.asym || a.q_zero != nullptr) &&
                     a.hadk != nullptr && (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) &&
                     aligned16(a.x) && aligned16(a.q) && (a.out == nullptr || (a.out_dtype == SR_F16 && aligned4(a.out)));
     if (!ok) return SR_ERR_UNSUPPORTED;
@@ -345,21 +393,23 @@ int launch_rotate_had28(const RotateArgs &a, cudaStream_t st) {
         if (sm_count <= 0) sm_count = 148;
     }
     const uint32_t grid = a.rows < (uint32_t)(2 * sm_count) ? a.rows : (uint32_t)(2 * sm_count);
-    const bool late = a.clip == 1.f && a.out == nullptr && a.expert_ids == nullptr;
-#define SR_H28(T, LATE)                                                                                    \
+    const bool late = a.clip == 1.f && a.out == nullptr && a.expert_ids == nullptr && !a.asym;
+#define SR_H28(T, LATE, ASYM)                                                                                  \
     do {                                                                                                   \
-        auto kfn = rotate_quant_had28_kernel<T, LATE>;                                                     \
+        auto kfn = rotate_quant_had28_kernel<T, LATE, ASYM>;                                                   \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);\
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));         \
         kfn<<<grid, THREADS, SMEM_BYTES, st>>>((const T *)a.x, (const __half *)a.hadk, a.sign, a.expert_ids, \
-                                               a.rows, a.scale, a.clip, a.q, a.q_scale, (__half *)a.out);  \
+                                               a.rows, a.scale, a.clip, a.q, a.q_scale, a.q_zero, (__half *)a.out); \
     } while (0)
     if (a.in_dtype == SR_F16) {
-        if (late) SR_H28(__half, true);
-        else SR_H28(__half, false);
+        if (late) SR_H28(__half, true, false);
+        else if (a.asym) SR_H28(__half, false, true);
+        else SR_H28(__half, false, false);
     } else {
-        if (late) SR_H28(__nv_bfloat16, true);
-        else SR_H28(__nv_bfloat16, false);
+        if (late) SR_H28(__nv_bfloat16, true, false);
+        else if (a.asym) SR_H28(__nv_bfloat16, false, true);
+        else SR_H28(__nv_bfloat16, false, false);
     }
 #undef SR_H28
     return check_launch("rotate_quant_had28");

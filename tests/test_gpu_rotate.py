@@ -216,3 +216,22 @@ def test_rotate_quant_heads32_symmetric(dtype, rows):
     codes, scale = oracle.sym_quant_dynamic(want_rot)
     same = (pk.scales_x.cpu() == scale).view(-1)
     assert_codes_close(oracle.unpack_i4(pk.quantized_x.cpu())[same], codes[same])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("clip", [1.0, 0.9])
+def test_rotate_quant_had28_asym(dtype, clip):
+    """had28 x 512 rotation with asymmetric codes (zero padding rows of the 28 -> 32 product must not enter the range)."""
+    n = 14336
+    x = _x(21, n, 31, dtype)
+    x = (x.float() + 0.75).to(dtype)          # a range that is not symmetric around zero
+    sign = (torch.randint(0, 2, (n,), generator=torch.Generator().manual_seed(9)) * 2 - 1).to(torch.int8)
+    hadK, K = get_hadK(n)
+    pk, rot = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), asym=True, clip_ratio=clip, return_rotated=True)
+    want_rot = oracle.rotate(x, hadK, K, sign, cast_in_to_f16=True, out_dtype=torch.float16)
+    _ulp_close(rot.cpu(), want_rot)
+    q2, s2, z2 = kernel.asym_quant_dynamic(rot, clip)
+    assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    assert torch.equal(z2.to(torch.int8), pk.zeros_x)
+    pk3 = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), asym=True, clip_ratio=clip)
+    assert torch.equal(pk3.quantized_x, pk.quantized_x) and torch.equal(pk3.zeros_x, pk.zeros_x)
