@@ -642,6 +642,73 @@ def run_sweep():
         print(json.dumps({"case": "moe_block", "tokens": tokens, "experts": E, "top_k": top_k,
                           "block_ms": round(t_moe, 3), "expert_weight_gbs": round(w_bytes / t_moe / 1e6, 1),
                           "tops": round(2 * 3 * tokens * top_k * ffn * hid / t_moe / 1e9, 1)}))
+    del blk, cache
+    torch.cuda.empty_cache()
+    # configs 4 and 5 end to end: the whole 32-layer stack through the decode-graph glue
+    for name, kw, bsz, prompt, steps in (
+            ("decode_model_llama3_8b", {}, 8, 2048, 128),
+            ("decode_model_mixtral_8x7b_shape", {"num_local_experts": 8, "num_experts_per_tok": 2, "vocab_size": 32000},
+             64, 64, 64)):
+        try:
+            run_decode_model(name, kw, bsz, prompt, steps, dev)
+        except Exception as e:
+            print(json.dumps({"case": name, "error": str(e)[:300]}))
+
+
+def run_decode_model(name, cfg_kwargs, bsz, prompt, steps, dev):
+    """Full decoder stack (BASELINE configs 4 and 5): random-init int4 weights, int4 paged KV cache,
+    prefill of `prompt` tokens per request, then `steps` decode steps replayed from one CUDA graph.
+    Prints one JSON line: decode tokens/s (bsz * steps / device time), prefill tokens/s, and the bytes of
+    weights + cache a decode step must read against the measured HBM figure."""
+    from signrot_b200.transformers import kernel_utils as ku
+    hbm = peaks()["hbm_gbs"]
+    cfg = ku.DecoderConfig(**cfg_kwargs)
+    with torch.device(dev):
+        model = ku.KernelDecoderModel(cfg)
+    model = model.to(dev).random_init_(0)
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(1000, 8000, (bsz, prompt), generator=gen).to(dev)
+    cache = ku.build_paged_cache(model, bsz, prompt + steps + 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.no_grad():
+        torch.cuda.synchronize()
+        e0.record()
+        logits = model(ids, past_key_values=cache, last_token_only=True).logits
+        e1.record()
+        torch.cuda.synchronize()
+        t_prefill = e0.elapsed_time(e1)
+        tok = logits[:, -1:].argmax(-1)
+        dec = ku.try_graph_decoder(model, cache, bsz)
+        graphed = dec is not None
+        for _ in range(3):                               # warm-up steps (they advance the cache like real ones)
+            tok = (dec.step(tok) if graphed else model(tok, past_key_values=cache).logits)[:, -1:].argmax(-1)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            tok = (dec.step(tok) if graphed else model(tok, past_key_values=cache).logits)[:, -1:].argmax(-1)
+        e1.record()
+        torch.cuda.synchronize()
+    t_dec = e0.elapsed_time(e1) / steps
+    finite = bool(torch.isfinite(logits).all())
+    hid, ffn, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+    attn_w = (2 * hid * cfg.num_attention_heads * cfg.head_dim + 2 * hid * cfg.num_key_value_heads * cfg.head_dim) / 2
+    if cfg.num_local_experts:
+        mlp_w = 3 * hid * ffn / 2 * min(cfg.num_local_experts, bsz * cfg.num_experts_per_tok)
+    else:
+        mlp_w = 3 * hid * ffn / 2
+    ctx = prompt + 3 + steps / 2
+    kv = bsz * ctx * cfg.num_key_value_heads * 68 * 2
+    step_bytes = L * (attn_w + mlp_w + kv) + cfg.vocab_size * hid * 2
+    print(json.dumps({"case": name, "batch": bsz, "prefill_tokens": prompt, "decode_steps": steps, "layers": L,
+                      "experts": cfg.num_local_experts, "graph_replay": graphed, "finite": finite,
+                      "decode_ms_per_step": round(t_dec, 3), "decode_tokens_per_s": round(bsz / t_dec * 1e3, 1),
+                      "prefill_ms": round(t_prefill, 1), "prefill_tokens_per_s": round(bsz * prompt / t_prefill * 1e3, 1),
+                      "step_bytes_gb": round(step_bytes / 1e9, 3), "step_gbs": round(step_bytes / t_dec / 1e6, 1),
+                      "frac_hbm": round(step_bytes / t_dec / 1e6 / hbm, 3),
+                      "note": "weights (every expert a step can touch), int4 KV at the mean context and the fp16 lm_head "
+                              "counted once per step; prefill time is one cold call, dense prefill attention included"}))
+    del model, cache, dec
+    torch.cuda.empty_cache()
 
 
 def main():
@@ -657,6 +724,9 @@ def main():
                     help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | decode_layer | "
                          "rotate14336 | decode")
     args = ap.parse_args()
+    if args.kernel_case == "decode_model":
+        run_decode_model("decode_model_llama3_8b", {}, 8, 2048, 128, torch.device("cuda", 0))
+        return
     if args.kernel_case:
         run_kernel_case(args.kernel_case)
         return

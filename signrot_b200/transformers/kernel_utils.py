@@ -1,0 +1,488 @@
+"""Decode-graph glue around the quantized-linear path: the kernel branch of the activation-quantized
+linear wrapper, attention and MLP forwards that share one quantization between sibling
+projections, a Llama-shaped decoder stack over those pieces, and a CUDA-graph runner for the decode
+step.
+
+Reference counterparts:
+  * `KernelLinear`             `ActQuantWrapper.enable_kernel / kernel_quantize / kernel_matmul /
+                               shares_kernel_input_with` (fake_quant/quant_utils.py:214-314)
+  * `kernel_attention_forward` fake_quant/kernel_utils.py:86-161
+  * `kernel_mlp_forward`       fake_quant/kernel_utils.py:352-363
+  * `build_paged_cache`        fake_quant/kernel_utils.py:64-83
+  * `GraphedDecoder`, `try_graph_decoder`   fake_quant/kernel_utils.py:164-292
+
+The reference patches these functions onto a Hugging Face model.  Here the same functions drive a
+small self-contained decoder (`KernelDecoderModel`: embedding, N decoder layers, final norm, fp16
+lm_head) so that the path can be run and measured without model files; a Hugging Face layer whose
+projections are `KernelLinear` objects can be driven by the same two forwards.
+
+What differs from the reference by design:
+  * a projection with an online rotation quantizes through ONE launch (`kernel.rotate_quant`:
+    rotation, +-1 sign, per-token scale, int4 codes) instead of Hadamard kernel(s) + quantizer;
+  * the cache takes K/V straight from the projections (`update` runs the fused
+    Hadamard + quantize + page-scatter kernel) and attends grouped-query heads without repeating
+    the cached heads;
+  * prefill attention (dense, fp16, outside the path) is `scaled_dot_product_attention`.
+"""
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass
+
+import torch
+
+from .. import nn as snn
+from ..functional import kernel
+from .kv_cache import MultiLayerPagedKVCache4Bit
+
+# the cache allocates whole pages; a small page also gives the decode kernel several pages per
+# sequence to split its work across (fake_quant/kernel_utils.py:57-61)
+DEFAULT_PAGE_SIZE = 256
+
+
+# ----------------------------------------------------------------------------- linear wrapper
+
+class KernelLinear(torch.nn.Module):
+    """Online rotation (optional) -> activation quantizer -> int4 linear.
+
+    `online_full_had`: Hadamard over the whole input (down_proj), with the optional +-1
+    `had_adj_sign` of the SignRot adjustment.  `online_partial_had`: Hadamard across heads,
+    identity within a head (o_proj); `had_dim` is the head size as in the reference."""
+
+    def __init__(self, in_features, out_features, *, bias=False, online_full_had=False, online_partial_had=False,
+                 had_dim=0, had_adj=False, fp32_had=False, asym=False, clip_ratio=1.0):
+        super().__init__()
+        assert not (online_full_had and online_partial_had)
+        assert not had_adj or online_full_had, "had_adj is only supported on online_full_had layers"
+        self.online_full_had = online_full_had
+        self.online_partial_had = online_partial_had
+        self.had_dim = had_dim
+        self.fp32_had = fp32_had
+        self.use_kernel = True
+        self.kernel_hadamard = None
+        if online_full_had:
+            self.kernel_hadamard = snn.OnlineHadamard(in_features, force_fp32=fp32_had, had_adj=had_adj)
+        elif online_partial_had:
+            assert had_dim > 0 and in_features % had_dim == 0
+            self.kernel_hadamard = snn.OnlineHadamard(in_features // had_dim, force_fp32=fp32_had)
+        self.kernel_quantizer = (snn.AsymQuantizer if asym else snn.Quantizer)(clip_ratio=clip_ratio)
+        self.kernel_module = snn.Linear4bit(in_features, out_features, bias=bias)
+
+    @property
+    def in_features(self):
+        return self.kernel_module.in_features
+
+    @property
+    def out_features(self):
+        return self.kernel_module.out_features
+
+    @property
+    def _asym(self):
+        return isinstance(self.kernel_quantizer, snn.AsymQuantizer)
+
+    def kernel_quantize(self, x) -> kernel.PackedQuantizedTensor:
+        """Rotation (+ sign) and activation quantization only, so that siblings reading the same
+        activation can share it."""
+        had = self.kernel_hadamard
+        if had is None:
+            return self.kernel_quantizer(x if x.dtype == torch.float16 else x.to(torch.float16))
+        if self.fp32_had:
+            # fp32 rotation keeps the reference's operator chain (one rounding after the transform)
+            x = x.to(torch.float16)
+            if self.online_full_had:
+                x = had(x)
+            else:
+                x = kernel.hadamard_heads(x, x.shape[-1] // self.had_dim, fp32_mode=True)
+            return self.kernel_quantizer(x)
+        if x.dtype not in (torch.float16, torch.bfloat16):
+            x = x.to(torch.float16)
+        clip = self.kernel_quantizer.clip_ratio
+        if self.online_full_had:
+            sign = had.had_adj_sign
+            if sign is not None and not had._had_adj_ready_cached:
+                raise RuntimeError("Dynamic hadamard adjustment not implemented yet.")
+            return kernel.rotate_quant(x, had.had_rem_dim, had.rem_dim, sign=sign, clip_ratio=clip, asym=self._asym)
+        return kernel.rotate_quant(x, heads=x.shape[-1] // self.had_dim, clip_ratio=clip, asym=self._asym)
+
+    def kernel_matmul(self, packed_x, x_dtype):
+        out = self.kernel_module(packed_x)
+        return out if out.dtype == x_dtype else out.to(x_dtype)
+
+    def shares_kernel_input_with(self, other) -> bool:
+        return (getattr(other, "use_kernel", False) and self.use_kernel
+                and not (self.online_full_had or self.online_partial_had)
+                and not (other.online_full_had or other.online_partial_had)
+                and type(self.kernel_quantizer) is type(other.kernel_quantizer)
+                and self.kernel_quantizer.clip_ratio == other.kernel_quantizer.clip_ratio
+                and self.in_features == other.in_features)
+
+    def forward(self, x):
+        return self.kernel_matmul(self.kernel_quantize(x), x.dtype)
+
+
+def _shares_input(first, *others):
+    shares = getattr(first, "shares_kernel_input_with", None)
+    return shares is not None and all(shares(o) for o in others)
+
+
+# ----------------------------------------------------------------------------- layer forwards
+
+def kernel_attention_forward(self, hidden_states, position_embeddings, attention_mask=None, past_key_values=None,
+                             cache_position=None, **kwargs):
+    """Attention over the paged int4 cache.  `self` carries q_proj/k_proj/v_proj/o_proj,
+    `head_dim`, `layer_idx` (and optionally q_norm/k_norm).  Returns (output, None)."""
+    input_shape = hidden_states.shape[:-1]
+    hidden_shape = (*input_shape, -1, self.head_dim)
+    dtype = hidden_states.dtype
+
+    if _shares_input(self.q_proj, self.k_proj, self.v_proj):
+        packed = self.q_proj.kernel_quantize(hidden_states)
+        query_states = self.q_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+        key_states = self.k_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+        value_states = self.v_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+    else:
+        query_states = self.q_proj(hidden_states).view(hidden_shape)
+        key_states = self.k_proj(hidden_states).view(hidden_shape)
+        value_states = self.v_proj(hidden_states).view(hidden_shape)
+    if hasattr(self, "q_norm"):
+        query_states = self.q_norm(query_states)
+        key_states = self.k_norm(key_states)
+
+    # the KV kernels and the decode kernel are fp16-only
+    if query_states.dtype != torch.float16:
+        query_states, key_states = query_states.to(torch.float16), key_states.to(torch.float16)
+        value_states = value_states.to(torch.float16)
+    cos, sin = position_embeddings
+    if cos.dtype != torch.float16:
+        cos, sin = cos.to(torch.float16), sin.to(torch.float16)
+    query_states, key_states = query_states.contiguous(), key_states.contiguous()
+    kernel.rope_qk(query_states, key_states, cos, sin)     # in place
+
+    if past_key_values is not None:
+        cache_out = past_key_values.update(key_states, value_states, self.layer_idx,
+                                           {"attention_mask": attention_mask})
+    else:
+        cache_out = (key_states, value_states)
+
+    if isinstance(cache_out, tuple):
+        # prefill: the cache stored the rotated int4 K/V and handed back the fp16 originals
+        key_states, value_states = cache_out
+        attn_output = torch.nn.functional.scaled_dot_product_attention(
+            query_states.transpose(1, 2), key_states.transpose(1, 2), value_states.transpose(1, 2),
+            is_causal=True, enable_gqa=key_states.shape[2] != query_states.shape[2]).transpose(1, 2)
+    else:
+        attn_output = cache_out(query_states)
+
+    attn_output = attn_output.reshape(*input_shape, -1)
+    if attn_output.dtype != dtype:
+        attn_output = attn_output.to(dtype)
+    return self.o_proj(attn_output), None
+
+
+def kernel_mlp_forward(self, x):
+    """SwiGLU MLP: one quantization for gate and up, fused silu*mul, rotation + quantization of
+    the product in one launch inside down_proj."""
+    if _shares_input(self.gate_proj, self.up_proj):
+        packed = self.gate_proj.kernel_quantize(x)
+        gate = self.gate_proj.kernel_matmul(packed, torch.float16)
+        up = self.up_proj.kernel_matmul(packed, torch.float16)
+    else:
+        gate = self.gate_proj(x).to(torch.float16)
+        up = self.up_proj(x).to(torch.float16)
+    out = self.down_proj(kernel.swiglu(gate, up))
+    return out if out.dtype == x.dtype else out.to(x.dtype)
+
+
+# ----------------------------------------------------------------------------- decoder stack
+
+@dataclass
+class DecoderConfig:
+    """Geometry of the stack; the defaults are Llama-3-8B's."""
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    num_local_experts: int = 0        # > 0: every MLP is a sparse block of that many experts
+    num_experts_per_tok: int = 2
+    norm_topk_prob: bool = True
+    a_asym: bool = False
+    a_clip_ratio: float = 1.0
+    had_adj: bool = True              # SignRot sign vector on down_proj's rotation
+
+
+class KernelAttention(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        q_out, kv_out = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+        kw = dict(asym=cfg.a_asym, clip_ratio=cfg.a_clip_ratio)
+        self.head_dim = cfg.head_dim
+        self.layer_idx = layer_idx
+        self.q_proj = KernelLinear(cfg.hidden_size, q_out, **kw)
+        self.k_proj = KernelLinear(cfg.hidden_size, kv_out, **kw)
+        self.v_proj = KernelLinear(cfg.hidden_size, kv_out, **kw)
+        self.o_proj = KernelLinear(q_out, cfg.hidden_size, online_partial_had=True, had_dim=cfg.head_dim, **kw)
+
+    forward = kernel_attention_forward
+
+
+class KernelMLP(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        kw = dict(asym=cfg.a_asym, clip_ratio=cfg.a_clip_ratio)
+        self.gate_proj = KernelLinear(cfg.hidden_size, cfg.intermediate_size, **kw)
+        self.up_proj = KernelLinear(cfg.hidden_size, cfg.intermediate_size, **kw)
+        self.down_proj = KernelLinear(cfg.intermediate_size, cfg.hidden_size, online_full_had=True,
+                                      had_adj=cfg.had_adj, **kw)
+
+    forward = kernel_mlp_forward
+
+
+class KernelDecoderLayer(torch.nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        self.input_layernorm = snn.RMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps)
+        self.post_attention_layernorm = snn.RMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps)
+        self.self_attn = KernelAttention(cfg, layer_idx)
+        self.mlp = KernelMLP(cfg) if cfg.num_local_experts == 0 else None   # sparse block attached later
+
+    def forward(self, hidden_states, position_embeddings, past_key_values=None):
+        attn, _ = self.self_attn(self.input_layernorm(hidden_states), position_embeddings,
+                                 past_key_values=past_key_values)
+        hidden_states = hidden_states + attn
+        mlp_out = self.mlp(self.post_attention_layernorm(hidden_states))
+        if isinstance(mlp_out, tuple):      # sparse block: (output, router logits)
+            mlp_out = mlp_out[0]
+        return hidden_states + mlp_out
+
+
+class _Logits:
+    __slots__ = ("logits",)
+
+    def __init__(self, logits):
+        self.logits = logits
+
+
+class KernelDecoderModel(torch.nn.Module):
+    """Embedding -> decoder layers -> RMSNorm -> fp16 lm_head (the head stays unquantized, as in
+    the reference's pipeline).  `forward(input_ids, past_key_values, cache_position)` follows
+    the call the graph runner makes."""
+
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.config = cfg
+        self.embed_tokens = torch.nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=torch.float16)
+        self.layers = torch.nn.ModuleList(KernelDecoderLayer(cfg, i) for i in range(cfg.num_hidden_layers))
+        self.norm = snn.RMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps)
+        self.lm_head = torch.nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=torch.float16)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
+        self.register_buffer("inv_freq", inv, persistent=False)
+
+    def get_input_embeddings(self):
+        return self.embed_tokens
+
+    def rotary(self, positions):
+        """cos/sin [1, T, head_dim] in fp16 from int64 positions [T] (fp32 angles, then the cast)."""
+        ang = positions.to(torch.float32)[:, None] * self.inv_freq[None, :]
+        emb = torch.cat((ang, ang), dim=-1)
+        return emb.cos().to(torch.float16)[None], emb.sin().to(torch.float16)[None]
+
+    def forward(self, input_ids, past_key_values=None, use_cache=True, cache_position=None, last_token_only=False):
+        t = input_ids.shape[1]
+        if cache_position is None:
+            start = past_key_values.get_seq_length() if past_key_values is not None else 0
+            cache_position = torch.arange(start, start + t, device=input_ids.device)
+        elif cache_position.numel() == 1 and t > 1:
+            cache_position = cache_position + torch.arange(t, device=input_ids.device)
+        pos = self.rotary(cache_position)
+        h = self.embed_tokens(input_ids)
+        for layer in self.layers:
+            h = layer(h, pos, past_key_values)
+        if last_token_only:
+            h = h[:, -1:, :]
+        return _Logits(self.lm_head(self.norm(h)))
+
+    @torch.no_grad()
+    def random_init_(self, seed: int = 0):
+        """Random int4 codes, weight scales about 1/K (keeps fp16 activations finite through many
+        layers; the trick of benchmarks/decode_sweep.py:65-71), random +-1 adjustment signs,
+        N(0, 0.02) embedding and head.  Runs on the module's device."""
+        dev = self.embed_tokens.weight.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        cfg = self.config
+
+        def fill(lin: snn.Linear4bit):
+            n, k = lin.out_features, lin.in_features
+            lin.weight.copy_(torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8, device=dev))
+            lin.weight_scales = ((torch.rand((n, 1), generator=g, device=dev) * 0.5 + 0.5) / k).to(torch.float16)
+
+        def sign(n):
+            return (torch.randint(0, 2, (n,), generator=g, device=dev) * 2 - 1).to(torch.int8)
+
+        for layer in self.layers:
+            at = layer.self_attn
+            for lin in (at.q_proj, at.k_proj, at.v_proj, at.o_proj):
+                fill(lin.kernel_module)
+            if cfg.num_local_experts == 0:
+                for lin in (layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj):
+                    fill(lin.kernel_module)
+                had = layer.mlp.down_proj.kernel_hadamard
+                if had.had_adj_sign is not None:
+                    had.had_adj_sign.copy_(sign(cfg.intermediate_size))
+            else:
+                e, hid, ffn = cfg.num_local_experts, cfg.hidden_size, cfg.intermediate_size
+
+                def stack(n, k):
+                    w = torch.randint(0, 256, (e, n, k // 2), generator=g, dtype=torch.uint8, device=dev)
+                    s = ((torch.rand((e, n), generator=g, device=dev) * 0.5 + 0.5) / k).to(torch.float16)
+                    return w, s
+                wg, sg = stack(ffn, hid)
+                wu, su = stack(ffn, hid)
+                wd, sd = stack(hid, ffn)
+                gate = torch.nn.Linear(hid, e, bias=False, dtype=torch.float16, device=dev)
+                gate.weight.copy_(torch.randn((e, hid), generator=g, device=dev) * 0.02)
+                sd_sign = torch.stack([sign(ffn) for _ in range(e)]).contiguous() if cfg.had_adj else None
+                layer.mlp = snn.SignRotMoEBlock(gate, top_k=cfg.num_experts_per_tok, norm_topk_prob=cfg.norm_topk_prob,
+                                                w_gate=wg, s_gate=sg, w_up=wu, s_up=su, w_down=wd, s_down=sd,
+                                                sign_down=sd_sign, asym=cfg.a_asym, clip_ratio=cfg.a_clip_ratio)
+        self.embed_tokens.weight.copy_(torch.randn(self.embed_tokens.weight.shape, generator=g, device=dev) * 0.02)
+        self.lm_head.weight.copy_(torch.randn(self.lm_head.weight.shape, generator=g, device=dev) * 0.02)
+        return self
+
+
+def build_paged_cache(model, batch_size, max_length, page_size=None):
+    """Paged int4 cache sized for `max_length` tokens per request."""
+    cfg = model.config
+    return MultiLayerPagedKVCache4Bit(
+        batch_size=batch_size, page_size=min(page_size or DEFAULT_PAGE_SIZE, max_length), max_seq_len=max_length,
+        device=model.get_input_embeddings().weight.device, n_layers=cfg.num_hidden_layers,
+        num_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, hadamard_dtype=torch.float16,
+        group_size=cfg.num_attention_heads // cfg.num_key_value_heads)
+
+
+# ----------------------------------------------------------------------------- graph runner
+
+class GraphedDecoder:
+    """Replays one decode step from a captured CUDA graph.
+
+    Everything that changes between tokens lives in fixed buffers refreshed outside the graph:
+    the input token, the cache position (which drives the rotary tables) and the cache's index
+    tensors.  The Python bookkeeping inside the cache's `update` does not run on replay, so the
+    sequence length is advanced here.  Capture writes a throwaway token into the cache and rewinds
+    the length, so the slot is overwritten by the first real step."""
+
+    def __init__(self, model, cache, batch_size):
+        self.model = model
+        self.cache = cache
+        self.inner = getattr(cache, "inner", cache)
+        device = model.get_input_embeddings().weight.device
+        self.input_ids = torch.zeros((batch_size, 1), dtype=torch.long, device=device)
+        self.cache_position = torch.zeros(1, dtype=torch.long, device=device)
+        self.graph = None
+        self.logits = None
+
+    def _forward(self):
+        return self.model(self.input_ids, past_key_values=self.cache, use_cache=True,
+                          cache_position=self.cache_position).logits
+
+    def _prepare_step(self):
+        self.cache_position.fill_(self.inner.length)
+        self.inner.length += 1
+        self.inner.refresh_specs()
+
+    def capture(self, warmup=3):
+        start_length = self.inner.length
+        self.inner.freeze_specs(True)
+        try:
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                for _ in range(warmup):
+                    self.inner.length = start_length
+                    self._prepare_step()
+                    self._forward()
+            torch.cuda.current_stream().wait_stream(stream)
+            self.inner.length = start_length
+            self._prepare_step()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._forward()
+        finally:
+            self.inner.length = start_length
+            self.inner.freeze_specs(False)
+        return self
+
+    def step(self, input_ids):
+        """One decode step; returns the logits buffer (overwritten by the next step)."""
+        if self.graph is None:
+            raise RuntimeError("capture() must run before step()")
+        self.input_ids.copy_(input_ids)
+        self.inner.freeze_specs(True)
+        self._prepare_step()
+        self.graph.replay()
+        self.inner.freeze_specs(False)
+        return self.logits
+
+
+def _graph_matches_eager(model, cache, decoder, batch_size, probes=2, tol=1e-3):
+    """A captured graph freezes every host-side branch at what the capture inputs selected; check
+    it against the eager step on tokens it has not seen."""
+    inner = decoder.inner
+    device = decoder.input_ids.device
+    vocab = model.get_input_embeddings().weight.shape[0]
+    start = inner.length
+    try:
+        for _ in range(probes):
+            token = torch.randint(0, vocab, (batch_size, 1), dtype=torch.long).to(device)
+            inner.length = start
+            eager = model(token, past_key_values=cache, use_cache=True).logits.float()
+            inner.length = start
+            graphed = decoder.step(token).float()
+            rel = (graphed - eager).abs().max() / eager.abs().max().clamp(min=1e-6)
+            if not torch.isfinite(rel) or rel.item() > tol:
+                logging.warning(f"CUDA graph output diverges from eager (relative {rel.item():.3e}); "
+                                f"the decode step is not capture-safe")
+                return False
+    finally:
+        inner.length = start
+    return True
+
+
+def try_graph_decoder(model, cache, batch_size, warmup=3, validate=True):
+    """Captures the decode step, or returns None when capture fails or the replay does not
+    reproduce the eager step (the caller then decodes eagerly: same kernels, launched one by one)."""
+    if not torch.cuda.is_available():
+        return None
+    try:
+        decoder = GraphedDecoder(model, cache, batch_size).capture(warmup=warmup)
+    except Exception as exc:
+        logging.warning(f"CUDA graph capture failed, decoding eagerly: {exc}")
+        torch.cuda.synchronize()
+        return None
+    if validate and not _graph_matches_eager(model, cache, decoder, batch_size):
+        return None
+    return decoder
+
+
+@torch.no_grad()
+def generate(model, input_ids, max_new_tokens, page_size=None, use_graph=True):
+    """Greedy decoding: prefill, then `max_new_tokens - 1` decode steps (graph-replayed when
+    capture succeeds).  Returns int64 tokens [B, max_new_tokens]."""
+    bsz, prompt = input_ids.shape
+    cache = build_paged_cache(model, bsz, prompt + max_new_tokens, page_size)
+    logits = model(input_ids, past_key_values=cache, last_token_only=True).logits
+    token = logits[:, -1:].argmax(-1)
+    out = [token]
+    decoder = try_graph_decoder(model, cache, bsz) if use_graph and max_new_tokens > 1 else None
+    for _ in range(max_new_tokens - 1):
+        if decoder is not None:
+            logits = decoder.step(token)
+        else:
+            logits = model(token, past_key_values=cache).logits
+        token = logits[:, -1:].argmax(-1)
+        out.append(token)
+    return torch.cat(out, dim=1)

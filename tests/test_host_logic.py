@@ -105,3 +105,54 @@ def test_install_as_signrot_aliases():
         for k_ in [k for k in sys.modules if k == "signrot" or k.startswith("signrot.")]:
             del sys.modules[k_]
         sys.modules.update(saved)
+
+
+def test_shared_quantization_rules():
+    """Sibling projections share one quantized activation only when neither rotates its input and
+    both quantize the same way (fake_quant/quant_utils.py:298-308)."""
+    from signrot_b200.transformers import kernel_utils as ku
+    cfg = ku.DecoderConfig(hidden_size=512, intermediate_size=1536, num_hidden_layers=1, num_attention_heads=4,
+                           num_key_value_heads=2, vocab_size=64)
+    layer = ku.KernelDecoderLayer(cfg, 0)
+    at, mlp = layer.self_attn, layer.mlp
+    assert at.q_proj.shares_kernel_input_with(at.k_proj) and at.q_proj.shares_kernel_input_with(at.v_proj)
+    assert mlp.gate_proj.shares_kernel_input_with(mlp.up_proj)
+    assert not at.o_proj.shares_kernel_input_with(at.q_proj)        # rotated input
+    assert not mlp.down_proj.shares_kernel_input_with(mlp.gate_proj)
+    assert not at.q_proj.shares_kernel_input_with(ku.KernelLinear(512, 64, clip_ratio=0.9))
+    assert not at.q_proj.shares_kernel_input_with(ku.KernelLinear(512, 64, asym=True))
+    assert mlp.down_proj.kernel_hadamard.rem_dim == 12 and mlp.down_proj.kernel_hadamard.had_adj_sign is not None
+
+
+def test_oracle_decoder_prefill_then_decode_is_consistent():
+    """The oracle's stack: decoding token T over a cache of T prompt tokens lands near a prefill of
+    T+1 tokens (they differ by the int4 rounding of the cached K/V and by the dense prefill
+    attention), and the cache advances by one."""
+    import math
+    from oracle.decoder import DecoderRef
+    from oracle import quant as Q
+    from signrot_b200.functional.hadamard import get_hadK
+    g = torch.Generator().manual_seed(0)
+    hid, ffn, heads, kvh, D, V = 256, 768, 2, 1, 128, 64
+    def lin(n, k):
+        return (Q.pack_codes(torch.randint(0, 16, (n, k), generator=g).to(torch.int32)),
+                ((torch.rand((n, 1), generator=g) * 0.5 + 0.5) / math.sqrt(k) / 4).half())
+    L = {}
+    for tag, (n, k) in dict(q=(heads * D, hid), k=(kvh * D, hid), v=(kvh * D, hid), o=(hid, heads * D),
+                            g=(ffn, hid), u=(ffn, hid), d=(hid, ffn)).items():
+        L["w" + tag], L["s" + tag] = lin(n, k)
+    L["sign_d"] = (torch.randint(0, 2, (ffn,), generator=g) * 2 - 1).to(torch.int8)
+    hadK, K = get_hadK(ffn)
+    cfg = dict(hidden=hid, heads=heads, kv_heads=kvh, head_dim=D, ffn=ffn, eps=1e-5, theta=10000.0,
+               hadK=hadK.half(), K=K)
+    state = {"embed": (torch.randn((V, hid), generator=g)).half(), "lm_head": (torch.randn((V, hid), generator=g) * 0.05).half(),
+             "layers": [L]}
+    ids = torch.randint(0, V, (1, 9), generator=g)
+    a = DecoderRef(state, cfg, 1, 4, 16)
+    a.forward(ids[:, :8])
+    step = a.forward(ids[:, 8:9])
+    b = DecoderRef(state, cfg, 1, 4, 16)
+    full = b.forward(ids)
+    assert a.length == b.length == 9
+    num = (step[:, 0].float() - full[:, 8].float()).norm()
+    assert torch.isfinite(step).all() and num / full[:, 8].float().norm() < 0.35
