@@ -64,6 +64,16 @@ int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, 
 int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
                    const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream);
 
+/* Fused edge of the path for decode: gate_proj and up_proj of a SwiGLU MLP and the activation in
+ * one launch.  W = [2N, K/2]: the N gate rows followed by the N up rows (w_scale [2N], w_sum [2N]
+ * and bias [2N] likewise); out[M, N] fp16 = rn_h(rn_h(silu(gate)) * up) with gate/up the fp16
+ * results sr_w4a4_linear would give (signrot/nn/linear.py:36-50) and the SwiGLU arithmetic of
+ * _CUDA.swiglu (signrot/kernels/fused.cu:367-381): the same bits as the three separate calls
+ * (fake_quant/kernel_utils.py:352-363).  At most 32 rows (SR_ERR_UNSUPPORTED beyond: larger
+ * batches run the two projections and sr_swiglu). */
+int sr_w4a4_swiglu(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                   const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream);
+
 /* P problems C_p = A_p * B_p^T in one launch.  problem_sizes int32 [P,3] rows (m, n, k);
  * ptr_* int64 [P] device addresses; ld* int64 [P] leading dimensions in elements.  All of
  * these arrays live in device memory and are never read on the host.  max_k > 0 promises
@@ -173,6 +183,18 @@ int sr_rotate_quant(const void *x, int dtype, int64_t rows, int64_t n, const voi
 
 /* Replaces _CUDA.rmsnorm (bindings.cpp:420-434, fused.cu:278-309). */
 int sr_rmsnorm(const void *x, int64_t rows, int64_t cols, float eps, int64_t mean_dim, void *out, void *stream);
+
+/* Fused edge of the path: residual add -> RMSNorm -> per-token int4 quantizer in one pass over the
+ * row.  Replaces three launches of the decode graph: the fp16 `hidden + branch` add of the decoder
+ * layer, _CUDA.rmsnorm (fused.cu:278-309) and _CUDA.sym_quant_dynamic / asym_quant_dynamic
+ * (fused.cu:68-198), with the same rounding points (one fp16 rounding after the add, one after the
+ * normalisation), so codes and scales equal those of the three separate calls bit for bit.
+ * delta may be NULL (no add).  sum_out (fp16 [rows, cols], needs delta) receives x + delta;
+ * normed_out (fp16, optional) the normalised row.  asym = 1 also writes zero (fp16 [rows]).
+ * cols must be a multiple of 8 and at most 16384 (SR_ERR_UNSUPPORTED otherwise). */
+int sr_add_rmsnorm_quant(const void *x, const void *delta, int64_t rows, int64_t cols, float eps, int64_t mean_dim,
+                         float clip_ratio, int asym, void *sum_out, void *normed_out, void *q, void *scale,
+                         void *zero, void *stream);
 /* In-place rotary embedding on q [B,T,Hq,D], k [B,T,Hk,D]; cos/sin [cos_seqs,T,D].
  * Replaces _CUDA.rope_qk (bindings.cpp:383-409, fused.cu:316-362). */
 int sr_rope_qk(void *q, void *k, const void *cosv, const void *sinv, int64_t n_seqs, int64_t seq_len,
@@ -209,6 +231,20 @@ int sr_kv_append_quant(void *kv_data, void *kv_param, const void *kv_indptr, con
                        const void *last_page_offset, const void *k, const void *v, int64_t batch_size,
                        int64_t new_tokens, int64_t num_layers, int64_t layer_idx, int64_t num_heads,
                        int64_t page_size, int64_t head_dim, int hadamard_k, void *stream);
+/* Fused edge of the path: rotary embedding on q and k (_CUDA.rope_qk, signrot/kernels/fused.cu:316-349),
+ * then the K/V chain of sr_kv_append_quant, in one launch; same bits as sr_rope_qk followed by
+ * sr_kv_append_quant (fake_quant/kernel_utils.py:118-141 + signrot/transformers/kv_cache.py:308-415).
+ * q, k, v are fp16, addressed as base + token * stride + head * 128 (strides in elements, multiples
+ * of 4), so they may be column ranges of one fused q/k/v projection output.  cos, sin fp16
+ * [cos_seqs (1 or batch), new_tokens, 128].  q_out fp16 [batch * new_tokens, num_qo_heads, 128]
+ * receives the rotated q (it may alias q when q_stride = num_qo_heads * 128); k_out (optional,
+ * [batch * new_tokens, num_kv_heads, 128]) the rotated k for a dense prefill attention. */
+int sr_rope_kv_append(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                      const void *last_page_offset, const void *q, const void *k, const void *v, int64_t q_stride,
+                      int64_t k_stride, int64_t v_stride, const void *cos, const void *sin, int64_t cos_seqs,
+                      void *q_out, void *k_out, int64_t batch_size, int64_t new_tokens, int64_t num_layers,
+                      int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                      int64_t head_dim, int hadamard_k, void *stream);
 /* o, q fp16 [batch, num_qo_heads, 128]; one new token per request attends to its cached
  * sequence.  num_qo_heads is a multiple (1, 2, 4, 8) of num_kv_heads: q head h reads KV head
  * h / (num_qo_heads / num_kv_heads).  tmp fp32 [batch, num_qo_heads, num_chunks, 132] is the

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "sr_device_status": [ctypes.POINTER(ctypes.c_int), _I],
     "sr_matmul_i4": [_P, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_w4a4_linear": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
+    "sr_w4a4_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
     "sr_grouped_linear": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P],
     "sr_matmul_grouped": [_P, _I64, _P, _P, _P, _P, _P, _P, _I, _I64, _P],
     "sr_set_gemm_kernel": [_I],
@@ -49,12 +50,14 @@ _SIGNATURES = {
     "sr_hadamard_heads": [_P, _I, _I64, _I64, _I64, _F, _I, _P, _I, _P],
     "sr_rotate_quant": [_P, _I, _I64, _I64, _P, _I64, _F, _P, _P, _I64, _F, _I, _P, _P, _P, _P, _P],
     "sr_rmsnorm": [_P, _I64, _I64, _F, _I64, _P, _P],
+    "sr_add_rmsnorm_quant": [_P, _P, _I64, _I64, _F, _I64, _F, _I, _P, _P, _P, _P, _P, _P],
     "sr_rope_qk": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     "sr_swiglu": [_P, _P, _I64, _P, _P],
     "sr_kv_quant_pack": [_P, _I64, _I64, _P, _P, _P],
     "sr_append_kv_i4": [_P] * 9 + [_I64] * 6 + [_P],
     "sr_init_kv_i4": [_P] * 10 + [_I64] * 7 + [_P],
     "sr_kv_append_quant": [_P] * 7 + [_I64] * 7 + [_I, _P],
+    "sr_rope_kv_append": [_P] * 8 + [_I64] * 3 + [_P, _P, _I64, _P, _P] + [_I64] * 8 + [_I, _P],
     "sr_batch_decode_i4": [_P] * 7 + [_I64] * 7 + [_P, _I64, _I, _P],
     "sr_batch_decode_i4_static": [_P] * 7 + [_I64] * 7 + [_I64, _I, _P],
 }
@@ -133,16 +136,17 @@ def device_status(clear: bool = True) -> int:
     return out.value
 
 
-def require_cuda(name: str, *tensors: torch.Tensor | None) -> torch.device:
+def require_cuda(name: str, *tensors: torch.Tensor | None, strided: tuple = ()) -> torch.device:
     """All given tensors must be contiguous CUDA tensors on one device
-    (signrot/kernels/bindings.cpp:15-20)."""
+    (signrot/kernels/bindings.cpp:15-20).  Tensors also listed in `strided` may be views whose
+    strides the caller passes to the library."""
     dev = None
     for t in tensors:
         if t is None:
             continue
         if not t.is_cuda:
             raise RuntimeError(f"{name}: expected a CUDA tensor, got {t.device} (no CPU fallback)")
-        if not t.is_contiguous():
+        if not t.is_contiguous() and not any(t is s for s in strided):
             raise RuntimeError(f"{name}: tensor must be contiguous")
         if dev is None:
             dev = t.device

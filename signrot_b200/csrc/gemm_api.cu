@@ -91,6 +91,26 @@ int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const
     return run_gemm(A, W, M, N, K, a_zero != nullptr, ep, stream, "w4a4_linear");
 }
 
+int sr_w4a4_swiglu(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                   const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream) {
+    SR_REQUIRE(M >= 0 && N >= 0 && K >= 0, SR_ERR_INVALID, "w4a4_swiglu: negative size");
+    if (M == 0 || N == 0) return SR_OK;
+    SR_REQUIRE(out && A && W && a_scale && w_scale, SR_ERR_INVALID, "w4a4_swiglu: null pointer");
+    SR_REQUIRE(a_zero == nullptr || w_sum != nullptr, SR_ERR_INVALID,
+               "w4a4_swiglu: asymmetric activations need the int4 row sums of the weight");
+    SR_REQUIRE(K > 0 && 2 * N < (1ll << 31), SR_ERR_INVALID, "w4a4_swiglu: size out of range");
+    Epilogue ep = {};
+    ep.mode = 1;
+    ep.out = (__half *)out;
+    ep.a_scale = (const __half *)a_scale;
+    ep.w_scale = (const __half *)w_scale;
+    ep.a_zero = (const int8_t *)a_zero;
+    ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
+    ep.bias = (const __half *)bias;
+    return launch_gemm_skinny_swiglu((const uint8_t *)A, (const uint8_t *)W, M, N, K, a_zero != nullptr, ep,
+                                     as_stream(stream));
+}
+
 int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
                       const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
                       int64_t num_experts, int64_t N, int64_t K, void *out, void *stream) {

@@ -68,11 +68,16 @@ struct SkItem {
 // NT = token blocks of 8 (at most 8 * NT activation rows per pass), MT = blocks of 16 weight rows a warp
 // multiplies per step (the activation fragments of a step are unpacked once for all of them).
 // A = activations [M, K/2], B = weights [N, K/2] (grouped: [E * N, K/2], row_off[E + 1] on the device).
-template <int NT, int MT, bool A_UNSIGNED, bool GROUPED>
+// SWIGLU (dense, MT = 2): B holds the gate rows [0, N) followed by the up rows [N, 2N) (w_scale likewise);
+// a block is 16 gate rows plus the 16 up rows of the same columns, and the epilogue writes
+// rn_h(silu(gate) * up) as [M, N] (the arithmetic of swiglu_kernel on the two dequantized fp16 values), so
+// the two projections and the activation of a SwiGLU MLP are one launch.
+template <int NT, int MT, bool A_UNSIGNED, bool GROUPED, bool SWIGLU = false>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
                    const int32_t *__restrict__ row_off, int num_experts, Epilogue ep) {
-    constexpr int ROWS = SK_ROWS * MT;                  // weight rows per block
+    static_assert(!SWIGLU || (MT == 2 && !GROUPED), "the SwiGLU epilogue pairs the two m-tiles of a dense block");
+    constexpr int ROWS = SWIGLU ? SK_ROWS : SK_ROWS * MT;   // output columns per block
     constexpr int STAGE = 1024 * MT;                    // bytes per warp and step
     constexpr int DEPTH = SK_RING_BYTES / STAGE;        // steps in flight per warp
     constexpr int RED_BUFS = NT <= 2 ? 2 : 1;
@@ -145,8 +150,11 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
             const uint32_t dst = ring_u32 + (uint32_t)slot * STAGE;
 #pragma unroll
             for (int r = 0; r < 2 * MT; ++r) {
-                const bool ok = k_ok && iss_n0 + g + 8 * r < N;
-                cp_async16(dst + r * 512, ok ? iss_ptr + (size_t)(8 * r) * kp : B, ok ? 16u : 0u);
+                // SWIGLU: slots 0, 1 are gate rows n0 + g (+ 8), slots 2, 3 the up rows N further down
+                const uint32_t rr = SWIGLU ? (uint32_t)(8 * (r & 1)) : (uint32_t)(8 * r);
+                const size_t jump = SWIGLU && r >= 2 ? (size_t)N : 0;
+                const bool ok = k_ok && iss_n0 + g + rr < N;
+                cp_async16(dst + r * 512, ok ? iss_ptr + ((size_t)rr + jump) * kp : B, ok ? 16u : 0u);
             }
             iss_step += SK_WARPS;
             iss_ptr += SK_WARPS * SK_STEP;
@@ -235,6 +243,25 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
         __syncthreads();
         // fragment slot i of lane (g, q) in m-tile m: weight row 16 m + g + 8 * (i >> 1), token 2 * q + (i & 1) of its
         // block.  With two buffers the one written two blocks later is this one: the barrier in between orders it.
+        if (SWIGLU) {
+            for (int idx = tid; idx < NT * 128; idx += SK_WARPS * 32) {
+                const int l = idx & 31, i = (idx >> 5) & 3, t = idx >> 7;
+                int sg = 0, su = 0;
+#pragma unroll
+                for (int w = 0; w < SK_WARPS; ++w) {
+                    sg += rb[(((w * MT + 0) * NT + t) * 4 + i) * 32 + l];
+                    su += rb[(((w * MT + 1) * NT + t) * 4 + i) * 32 + l];
+                }
+                const uint32_t n = cur.n0 + (l >> 2) + 8 * (i >> 1);
+                const uint32_t mm = cur.x_row0 + 8 * t + 2 * (l & 3) + (i & 1);
+                if (n < N && mm < cur.x_end) {
+                    const __half gv = ep.dequant(mm, n, sg >> 8, 2 * N), uv = ep.dequant(mm, n + N, su >> 8, 2 * N);
+                    const float gf = __half2float(gv);
+                    const __half sv = __float2half(gf / (1.f + expf(-gf)));
+                    ep.out[(size_t)mm * N + n] = __float2half(__half2float(sv) * __half2float(uv));
+                }
+            }
+        } else
         for (int idx = tid; idx < MT * NT * 128; idx += SK_WARPS * 32) {
             const int l = idx & 31, i = (idx >> 5) & 3, t = (idx >> 7) % NT, m = idx / (NT * 128);
             int sum = 0;
@@ -297,6 +324,41 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     }
 #undef SR_SK
     return check_launch("gemm_skinny");
+}
+
+// gate/up pair + SwiGLU: B = [2N, K/2] (gate rows then up rows), ep.w_scale = [2N], ep.out = [M, N]
+int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
+                              const Epilogue &ep, cudaStream_t st) {
+    SR_REQUIRE(M >= 1 && M <= 32, SR_ERR_UNSUPPORTED, "w4a4_swiglu: the fused kernel takes at most 32 rows");
+    SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "w4a4_swiglu: operands must be 16-byte aligned");
+    SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "w4a4_swiglu: K = %lld must be a multiple of 32", (long long)K);
+    SR_REQUIRE(ep.mode == 1 && !ep.expert_ids, SR_ERR_INVALID, "w4a4_swiglu: dense dequant epilogue only");
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    const int64_t blocks = cdiv<int64_t>(N, SK_ROWS);
+    int64_t ctas = 2 * (int64_t)sm_count;
+    if (blocks < ctas) ctas = blocks;
+    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas));
+    const unsigned grid = (unsigned)ctas;
+#define SR_SKS(NT)                                                                                             \
+    do {                                                                                                       \
+        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, 2, true, false, true> : gemm_skinny_kernel<NT, 2, false, false, true>; \
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
+                                             (int)skinny_smem(NT, 2));                                         \
+        if (e != cudaSuccess) return fail(SR_ERR_CUDA, "w4a4_swiglu: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
+        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, 2), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, nullptr, 0, ep); \
+    } while (0)
+    if (nt == 1) SR_SKS(1);
+    else if (nt == 2) SR_SKS(2);
+    else SR_SKS(4);
+#undef SR_SKS
+    return check_launch("gemm_skinny_swiglu");
 }
 
 int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,

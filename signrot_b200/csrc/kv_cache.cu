@@ -162,6 +162,99 @@ kv_append_quant_kernel(PagedKV kv, const __half *__restrict__ k, const __half *_
     }
 }
 
+// ------------------------------------------------------------------ fused RoPE + append
+//
+// One pass over the projections of the new tokens: rotary embedding on q and k (the arithmetic of
+// rope_qk_kernel: both products rounded to fp16 before the add, signrot/kernels/fused.cu:316-349),
+// roped q written to q_out (and roped k to k_out when the caller needs it for a dense prefill
+// attention), roped K rotated by the head_dim Hadamard and quantized, V quantized, both written to
+// their page slots (the arithmetic of kv_append_quant_kernel).  q, k, v are addressed as
+// base + token * stride + head * 128, so they may be column ranges of one fused q/k/v projection.
+// One warp per 128-wide head vector; lane l holds dims 4l .. 4l+3, whose rotate-half partner lives
+// in lane l ^ 16.
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(PagedKV kv, const __half *__restrict__ q, const __half *__restrict__ k,
+                      const __half *__restrict__ v, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                      const __half *__restrict__ cosv, const __half *__restrict__ sinv, uint32_t cos_seqs,
+                      __half *__restrict__ q_out, __half *__restrict__ k_out, uint32_t batch, uint32_t T, uint32_t hq,
+                      int had_k, float had_scale) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t per_tok = hq + 2 * kv.heads;
+    const uint32_t total = batch * T * per_tok;
+    const uint32_t warps = gridDim.x * 8;
+    for (uint32_t w = blockIdx.x * 8 + (threadIdx.x >> 5); w < total; w += warps) {
+        const uint32_t token = w / per_tok, slot = w % per_tok;
+        const int type = slot < hq ? 0 : (slot < hq + kv.heads ? 1 : 2);   // q, k, v (uniform across the warp)
+        const uint32_t head = type == 0 ? slot : (type == 1 ? slot - hq : slot - hq - kv.heads);
+        const __half *src = type == 0 ? q + (size_t)token * q_stride : (type == 1 ? k + (size_t)token * k_stride
+                                                                                   : v + (size_t)token * v_stride);
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)head * HD + lane * 4));
+        __half h[4];
+        *reinterpret_cast<uint2 *>(h) = raw;
+        if (type < 2) {
+            const uint32_t p0 = __shfl_xor_sync(0xffffffffu, raw.x, 16), p1 = __shfl_xor_sync(0xffffffffu, raw.y, 16);
+            __half pb[4];
+            *reinterpret_cast<uint2 *>(pb) = make_uint2(p0, p1);
+            const size_t ct = (cos_seqs == 1 ? token % T : token) * HD + lane * 4;
+            __half c[4], sn[4];
+            *reinterpret_cast<uint2 *>(c) = __ldg(reinterpret_cast<const uint2 *>(cosv + ct));
+            *reinterpret_cast<uint2 *>(sn) = __ldg(reinterpret_cast<const uint2 *>(sinv + ct));
+            const bool first_half = lane < 16;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half p = __float2half(__half2float(h[j]) * __half2float(c[j]));
+                const float bf = first_half ? -__half2float(pb[j]) : __half2float(pb[j]);
+                const __half r = __float2half(bf * __half2float(sn[j]));
+                h[j] = __float2half(__half2float(p) + __half2float(r));
+            }
+            __half *dst = type == 0 ? q_out + ((size_t)token * hq + head) * HD : (k_out ? k_out + ((size_t)token * kv.heads + head) * HD : nullptr);
+            if (dst) *reinterpret_cast<uint2 *>(dst + lane * 4) = *reinterpret_cast<const uint2 *>(h);
+            if (type == 0) continue;
+        }
+        float a[4] = {__half2float(h[0]), __half2float(h[1]), __half2float(h[2]), __half2float(h[3])};
+        if (type == 1 && had_k) {
+            const float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
+            a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float o = __shfl_xor_sync(0xffffffffu, a[j], m);
+                    a[j] = (lane & m) ? (o - a[j]) : (a[j] + o);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
+        }
+        float vmax = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+        float vmin = fminf(fminf(a[0], a[1]), fminf(a[2], a[3]));
+        vmax = warp_max(vmax);
+        vmin = warp_min(vmin);
+        __half scale, zero;
+        kv_params_dev(vmin, vmax, scale, zero);
+        const float fs = __half2float(scale), fz = __half2float(zero);
+        uint32_t code = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half shifted = __float2half(a[j] + fz);
+            const __half scaled = __float2half(__half2float(shifted) / fs);
+            code |= (uint32_t)clampi((int)nearbyintf(__half2float(scaled)), 0, 15) << (4 * j);
+        }
+        const uint32_t t = token % T, b = token / T;
+        const uint32_t pos = kv.seq_len(b) - T + t;
+        const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
+        const uint32_t entry = pos % kv.page_size;
+        const size_t vi = kv.vec_index(page, (uint32_t)(type - 1), head, entry);
+        reinterpret_cast<uint16_t *>(kv.data + vi * 64)[lane] = (uint16_t)code;
+        if (lane == 0) {
+            __half2 pr;
+            pr.x = scale;
+            pr.y = zero;
+            kv.param[vi] = pr;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ decode attention
 
 // 4-bit code -> fp32 without the conversion pipe (2^23 + n has n in its low mantissa bits).
@@ -452,6 +545,37 @@ int sr_kv_append_quant(void *kv_data, void *kv_param, const void *kv_indptr, con
     kv_append_quant_kernel<<<(unsigned)ctas, 256, 0, as_stream(stream)>>>(
         kv, (const __half *)k, (const __half *)v, (uint32_t)batch_size, (uint32_t)new_tokens, hadamard_k, had_scale);
     return check_launch("kv_append_quant");
+}
+
+int sr_rope_kv_append(void *kv_data, void *kv_param, const void *kv_indptr, const void *kv_indices,
+                      const void *last_page_offset, const void *q, const void *k, const void *v, int64_t q_stride,
+                      int64_t k_stride, int64_t v_stride, const void *cos, const void *sin, int64_t cos_seqs,
+                      void *q_out, void *k_out, int64_t batch_size, int64_t new_tokens, int64_t num_layers,
+                      int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                      int64_t head_dim, int hadamard_k, void *stream) {
+    SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "rope_kv_append: head_dim must be 128, got %lld", (long long)head_dim);
+    if (batch_size == 0 || new_tokens == 0) return SR_OK;
+    PagedKV kv;
+    int rc = fill_kv(kv, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                     num_kv_heads, page_size, "rope_kv_append");
+    if (rc) return rc;
+    SR_REQUIRE(q && k && v && cos && sin && q_out, SR_ERR_INVALID, "rope_kv_append: null pointer");
+    SR_REQUIRE(num_qo_heads >= 1, SR_ERR_INVALID, "rope_kv_append: no q heads");
+    SR_REQUIRE(cos_seqs == 1 || cos_seqs == batch_size, SR_ERR_INVALID, "rope_kv_append: cos/sin must be [1 or batch, T, 128]");
+    SR_REQUIRE(q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                     reinterpret_cast<uintptr_t>(cos) | reinterpret_cast<uintptr_t>(sin) | reinterpret_cast<uintptr_t>(q_out) |
+                     reinterpret_cast<uintptr_t>(k_out)) & 7u) == 0,
+               SR_ERR_INVALID, "rope_kv_append: rows must be 8-byte aligned");
+    const int64_t warps = batch_size * new_tokens * (num_qo_heads + 2 * num_kv_heads);
+    SR_REQUIRE(warps < (1ll << 31), SR_ERR_UNSUPPORTED, "rope_kv_append: too many tokens");
+    int64_t ctas = cdiv<int64_t>(warps, 8);
+    if (ctas > 148 * 8) ctas = 148 * 8;
+    rope_kv_append_kernel<<<(unsigned)ctas, 256, 0, as_stream(stream)>>>(
+        kv, (const __half *)q, (const __half *)k, (const __half *)v, q_stride, k_stride, v_stride, (const __half *)cos,
+        (const __half *)sin, (uint32_t)cos_seqs, (__half *)q_out, (__half *)k_out, (uint32_t)batch_size,
+        (uint32_t)new_tokens, (uint32_t)num_qo_heads, hadamard_k, (float)(1.0 / sqrt(128.0)));
+    return check_launch("rope_kv_append");
 }
 
 int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,

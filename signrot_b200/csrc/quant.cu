@@ -18,12 +18,23 @@ namespace sr {
 
 // One row is owned by TPR threads (TPR <= 32: part of a warp, several rows per
 // warp; TPR == 256: the whole CTA).  Each thread keeps NV 16-byte vectors.
-template <int TPR, int NV, bool ASYM>
+// NORM (whole-CTA rows only): the row is first formed as x (+ delta, one fp16 addition, stored to
+// sum_out) and normalised as rmsnorm_kernel does it (same thread-to-vector mapping, same summation
+// order, so the codes equal those of the separate add / RMSNorm / quantizer launches bit for bit).
+struct NormArgs {
+    const __half *delta;   // optional addend (the residual branch)
+    __half *sum_out;       // optional: x + delta
+    __half *normed_out;    // optional: the normalised row
+    float eps, mean_dim;
+};
+
+template <int TPR, int NV, bool ASYM, bool NORM = false>
 __global__ void __launch_bounds__(256)
 act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict__ sign,
                          const int32_t *__restrict__ expert_ids, uint32_t rows, uint32_t cols,
                          float clip, __half *__restrict__ scale_out, __half *__restrict__ zero_out,
-                         uint8_t *__restrict__ q) {
+                         uint8_t *__restrict__ q, NormArgs na = NormArgs{}) {
+    static_assert(!NORM || TPR == 256, "the fused normalisation owns a whole CTA per row");
     constexpr int ROWS_PER_CTA = 256 / TPR;
     const int tid = threadIdx.x;
     const int sub = tid % TPR;  // index inside the row team
@@ -37,7 +48,58 @@ act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict_
     float vmax = ASYM ? -FLT_MAX : 0.f, vmin = FLT_MAX;
     __half2 hmax2 = __floats2half2_rn(ASYM ? -65504.f : 0.f, ASYM ? -65504.f : 0.f);
     __half2 hmin2 = __floats2half2_rn(65504.f, 65504.f);
-    if (live) {
+    if constexpr (NORM) {
+        __shared__ float nred[8];
+        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
+        const uint4 *dr = na.delta ? reinterpret_cast<const uint4 *>(na.delta + (size_t)row * cols) : nullptr;
+        uint4 *sr_o = na.sum_out ? reinterpret_cast<uint4 *>(na.sum_out + (size_t)row * cols) : nullptr;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t vi = sub + i * TPR;
+            if (vi < nvec) {
+                v[i].u = __ldg(xr + vi);
+                if (dr) {
+                    Vec16 d;
+                    d.u = __ldg(dr + vi);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[i].h2[j] = __hadd2(v[i].h2[j], d.h2[j]);
+                    if (sr_o) sr_o[vi] = v[i].u;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float f = __half2float(v[i].h[j]);
+                    acc += f * f;
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        if ((tid & 31) == 0) nred[tid >> 5] = acc;
+        __syncthreads();
+        acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) acc += nred[w];
+        const float inv = rsqrtf(acc / na.mean_dim + na.eps);
+        uint4 *nr_o = na.normed_out ? reinterpret_cast<uint4 *>(na.normed_out + (size_t)row * cols) : nullptr;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t vi = sub + i * TPR;
+            if (vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i].h[j] = __float2half(__half2float(v[i].h[j]) * inv);
+                if (nr_o) nr_o[vi] = v[i].u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (ASYM) {
+                        hmax2 = __hmax2(hmax2, v[i].h2[j]);
+                        hmin2 = __hmin2(hmin2, v[i].h2[j]);
+                    } else {
+                        hmax2 = __hmax2(hmax2, __habs2(v[i].h2[j]));
+                    }
+                }
+            }
+        }
+    } else if (live) {
         const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
         const int8_t *sr_ = sign ? sign + (size_t)(expert_ids ? expert_ids[row] : 0) * cols : nullptr;
 #pragma unroll
@@ -443,6 +505,37 @@ int sr_asym_quant_dynamic(const void *x, int64_t rows, int64_t cols, float clip_
                "asym_quant_dynamic: null pointer");
     return launch_act_quant<true>((const __half *)x, nullptr, nullptr, rows, cols, clip_ratio, (__half *)scale,
                                   (__half *)zero, (uint8_t *)q, as_stream(stream));
+}
+
+int sr_add_rmsnorm_quant(const void *x, const void *delta, int64_t rows, int64_t cols, float eps, int64_t mean_dim,
+                         float clip_ratio, int asym, void *sum_out, void *normed_out, void *q, void *scale,
+                         void *zero, void *stream) {
+    SR_REQUIRE(rows >= 0 && cols >= 0, SR_ERR_INVALID, "add_rmsnorm_quant: negative size");
+    if (rows == 0 || cols == 0) return SR_OK;
+    SR_REQUIRE(x && q && scale && (!asym || zero), SR_ERR_INVALID, "add_rmsnorm_quant: null pointer");
+    SR_REQUIRE(!sum_out || delta, SR_ERR_INVALID, "add_rmsnorm_quant: sum_out without an addend");
+    SR_REQUIRE(cols % 8 == 0 && cols <= 16384 && aligned16(x) && aligned4(q) && (!delta || aligned16(delta)) &&
+                   (!sum_out || aligned16(sum_out)) && (!normed_out || aligned16(normed_out)),
+               SR_ERR_UNSUPPORTED, "add_rmsnorm_quant: rows must be 16-byte aligned, cols a multiple of 8 and <= 16384");
+    const uint32_t r = (uint32_t)rows, c = (uint32_t)cols;
+    cudaStream_t st = (cudaStream_t)stream;
+    NormArgs na{(const __half *)delta, (__half *)sum_out, (__half *)normed_out, eps, (float)mean_dim};
+    const int64_t nvec = cols / 8;
+#define SR_LAUNCH_NQ(NV)                                                                                         \
+    do {                                                                                                         \
+        if (asym)                                                                                                \
+            act_quant_dynamic_kernel<256, NV, true, true><<<r, 256, 0, st>>>(                                    \
+                (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, (__half *)zero, (uint8_t *)q, na); \
+        else                                                                                                     \
+            act_quant_dynamic_kernel<256, NV, false, true><<<r, 256, 0, st>>>(                                   \
+                (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, nullptr, (uint8_t *)q, na); \
+    } while (0)
+    if (nvec <= 256) SR_LAUNCH_NQ(1);
+    else if (nvec <= 512) SR_LAUNCH_NQ(2);
+    else if (nvec <= 1024) SR_LAUNCH_NQ(4);
+    else SR_LAUNCH_NQ(8);
+#undef SR_LAUNCH_NQ
+    return check_launch("add_rmsnorm_quant");
 }
 
 int sr_sym_quant_dynamic_moe(const void *x, const void *sign, const void *expert_ids, int64_t rows, int64_t cols,

@@ -27,6 +27,7 @@ __all__ = [
     "kv_quant_pack", "rope_qk", "swiglu", "rmsnorm", "sym_dequant",
     "asym_quant_f16_si4", "asym_quant_f16_ui4", "sum_i4", "matmul_colrow_i8_i32",
     "w4a4_linear", "grouped_linear", "rotate_quant", "hadamard", "hadamard_heads",
+    "add_rmsnorm_quant", "w4a4_swiglu",
 ]
 
 
@@ -291,6 +292,34 @@ def rmsnorm(x, eps, mean_dim):
     return out
 
 
+def add_rmsnorm_quant(x, delta, eps, mean_dim, clip_ratio=1.0, asym=False, return_normed=False):
+    """Residual add -> RMSNorm -> per-token int4 quantizer in one launch: what a decoder layer does
+    between a branch's output projection and the next quantized projections (`hidden + branch`,
+    signrot.nn.RMSNorm, signrot.nn.Quantizer / AsymQuantizer), with the same rounding points.
+    `delta` may be None.  Returns (x + delta or x itself, PackedQuantizedTensor[, normalised row])."""
+    if x.dtype != torch.float16 or (delta is not None and delta.dtype != torch.float16):
+        raise RuntimeError("add_rmsnorm_quant expects fp16 input")
+    x = x.contiguous()
+    if delta is not None:
+        delta = delta.contiguous()
+        if delta.shape != x.shape:
+            raise RuntimeError("x and delta must have the same shape")
+    dev = require_cuda("add_rmsnorm_quant", x, delta)
+    x2, lead = _rows(x)
+    rows, cols = x2.shape
+    q = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    scale = torch.empty((rows, 1), dtype=torch.float16, device=dev)
+    zero = torch.empty((rows, 1), dtype=torch.float16, device=dev) if asym else None
+    total = torch.empty_like(x) if delta is not None else None
+    normed = torch.empty_like(x) if return_normed else None
+    run(dev, "sr_add_rmsnorm_quant", ptr(x), ptr(delta), rows, cols, float(eps), int(mean_dim), float(clip_ratio),
+        int(bool(asym)), ptr(total), ptr(normed), ptr(q), ptr(scale), ptr(zero))
+    packed = PackedQuantizedTensor(q.view(*lead, -1), scale.view(*lead, 1),
+                                   zero.view(*lead, 1).to(torch.int8) if asym else None)
+    out = (total if delta is not None else x, packed)
+    return out + (normed,) if return_normed else out
+
+
 def sym_dequant(q, scale_row, scale_col, bits=32):
     """fp16 `q * scale_row * scale_col` from int32 accumulators (kernel.py:179-185)."""
     assert q.dtype == torch.int32
@@ -430,6 +459,44 @@ def w4a4_linear(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum
         _check_dtype("w4a4_linear", bias, torch.float16)
     out = torch.empty((M, N), dtype=torch.float16, device=dev)
     run(dev, "sr_w4a4_linear", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
+        ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out))
+    return out.view(*lead, N)
+
+
+def w4a4_swiglu(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum=None, bias=None):
+    """gate_proj, up_proj and SwiGLU of an MLP in one launch for up to 32 rows.  `weight` is
+    [2N, K/2]: the gate rows followed by the up rows (scales, sums and bias likewise).  Same bits
+    as `swiglu(w4a4_linear(gate half), w4a4_linear(up half))`; larger batches take exactly that
+    route here."""
+    qx, sx, zx = packed.quantized_x, packed.scales_x, packed.zeros_x
+    qx = qx.contiguous()
+    q2, lead = _rows(qx)
+    M, N2, K = q2.shape[0], weight.shape[0], q2.shape[1] * 2
+    N = N2 // 2
+    if N2 % 2 or weight.shape[1] != q2.shape[1] or weight_scales.numel() != N2 or sx.numel() != M:
+        raise RuntimeError("w4a4_swiglu: shapes of activations, weight and scales do not match")
+    if M > 32:
+        ws = weight_scales.reshape(-1)
+        wsum = weight_sum.reshape(-1) if weight_sum is not None else None
+        half = lambda t, a: None if t is None else t[a * N:(a + 1) * N]
+        gate = w4a4_linear(packed, weight[:N], ws[:N], half(wsum, 0), half(bias, 0))
+        up = w4a4_linear(packed, weight[N:], ws[N:], half(wsum, 1), half(bias, 1))
+        return swiglu(gate, up)
+    sx = sx.reshape(-1)
+    ws = weight_scales.reshape(-1)
+    if zx is not None:
+        zx = zx.reshape(-1)
+        if weight_sum is None:
+            raise RuntimeError("w4a4_swiglu: asymmetric activations need weight_sum")
+        weight_sum = weight_sum.reshape(-1)
+    dev = require_cuda("w4a4_swiglu", q2, sx, zx, weight, ws, weight_sum if zx is not None else None, bias)
+    for name, t, dt in (("codes", q2, torch.uint8), ("weight", weight, torch.uint8), ("scales", sx, torch.float16),
+                        ("weight scales", ws, torch.float16)):
+        _check_dtype("w4a4_swiglu", t, dt)
+    if not weight.is_contiguous():
+        raise RuntimeError("w4a4_swiglu: weight must be contiguous")
+    out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    run(dev, "sr_w4a4_swiglu", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
         ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out))
     return out.view(*lead, N)
 

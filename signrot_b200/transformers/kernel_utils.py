@@ -128,19 +128,36 @@ def _shares_input(first, *others):
 # ----------------------------------------------------------------------------- layer forwards
 
 def kernel_attention_forward(self, hidden_states, position_embeddings, attention_mask=None, past_key_values=None,
-                             cache_position=None, **kwargs):
+                             cache_position=None, packed_input=None, **kwargs):
     """Attention over the paged int4 cache.  `self` carries q_proj/k_proj/v_proj/o_proj,
-    `head_dim`, `layer_idx` (and optionally q_norm/k_norm).  Returns (output, None)."""
+    `head_dim`, `layer_idx` (and optionally q_norm/k_norm).  Returns (output, None).
+
+    `packed_input`: the already quantized activation (the caller fused the quantizer with the
+    normalisation in front of it); `hidden_states` then only gives shape and dtype.  When the
+    module carries `qkv_fused` (see `fuse_projections_`), the three projections are one GEMM and
+    q/k/v are column ranges of its output; with a cache that offers `update_with_rope`, the rotary
+    embedding, the K rotation, the K/V quantizers and the page scatter are one launch."""
     input_shape = hidden_states.shape[:-1]
     hidden_shape = (*input_shape, -1, self.head_dim)
     dtype = hidden_states.dtype
 
     if _shares_input(self.q_proj, self.k_proj, self.v_proj):
-        packed = self.q_proj.kernel_quantize(hidden_states)
-        query_states = self.q_proj.kernel_matmul(packed, dtype).view(hidden_shape)
-        key_states = self.k_proj.kernel_matmul(packed, dtype).view(hidden_shape)
-        value_states = self.v_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+        packed = packed_input if packed_input is not None else self.q_proj.kernel_quantize(hidden_states)
+        fused = getattr(self, "qkv_fused", None)
+        if fused is not None:
+            qkv = fused(packed)
+            if qkv.dtype != dtype:
+                qkv = qkv.to(dtype)
+            nq, nk = self.q_proj.out_features, self.k_proj.out_features
+            query_states = qkv[..., :nq].unflatten(-1, (-1, self.head_dim))
+            key_states = qkv[..., nq:nq + nk].unflatten(-1, (-1, self.head_dim))
+            value_states = qkv[..., nq + nk:].unflatten(-1, (-1, self.head_dim))
+        else:
+            query_states = self.q_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+            key_states = self.k_proj.kernel_matmul(packed, dtype).view(hidden_shape)
+            value_states = self.v_proj.kernel_matmul(packed, dtype).view(hidden_shape)
     else:
+        assert packed_input is None
         query_states = self.q_proj(hidden_states).view(hidden_shape)
         key_states = self.k_proj(hidden_states).view(hidden_shape)
         value_states = self.v_proj(hidden_states).view(hidden_shape)
@@ -155,14 +172,19 @@ def kernel_attention_forward(self, hidden_states, position_embeddings, attention
     cos, sin = position_embeddings
     if cos.dtype != torch.float16:
         cos, sin = cos.to(torch.float16), sin.to(torch.float16)
-    query_states, key_states = query_states.contiguous(), key_states.contiguous()
-    kernel.rope_qk(query_states, key_states, cos, sin)     # in place
 
-    if past_key_values is not None:
-        cache_out = past_key_values.update(key_states, value_states, self.layer_idx,
-                                           {"attention_mask": attention_mask})
+    if past_key_values is not None and attention_mask is None and hasattr(past_key_values, "update_with_rope") \
+            and getattr(self, "fuse_rope_append", True):
+        query_states, cache_out = past_key_values.update_with_rope(query_states, key_states, value_states, cos, sin,
+                                                                   self.layer_idx)
     else:
-        cache_out = (key_states, value_states)
+        query_states, key_states = query_states.contiguous(), key_states.contiguous()
+        kernel.rope_qk(query_states, key_states, cos, sin)     # in place
+        if past_key_values is not None:
+            cache_out = past_key_values.update(key_states, value_states, self.layer_idx,
+                                               {"attention_mask": attention_mask})
+        else:
+            cache_out = (key_states, value_states)
 
     if isinstance(cache_out, tuple):
         # prefill: the cache stored the rotated int4 K/V and handed back the fp16 originals
@@ -179,18 +201,64 @@ def kernel_attention_forward(self, hidden_states, position_embeddings, attention
     return self.o_proj(attn_output), None
 
 
-def kernel_mlp_forward(self, x):
+def kernel_mlp_forward(self, x, packed_input=None):
     """SwiGLU MLP: one quantization for gate and up, fused silu*mul, rotation + quantization of
-    the product in one launch inside down_proj."""
+    the product in one launch inside down_proj.  With `gate_up_fused` (see `fuse_projections_`)
+    the two projections and the activation are one launch for up to 32 rows."""
     if _shares_input(self.gate_proj, self.up_proj):
-        packed = self.gate_proj.kernel_quantize(x)
-        gate = self.gate_proj.kernel_matmul(packed, torch.float16)
-        up = self.up_proj.kernel_matmul(packed, torch.float16)
+        packed = packed_input if packed_input is not None else self.gate_proj.kernel_quantize(x)
+        fused = getattr(self, "gate_up_fused", None)
+        if fused is not None:
+            wsum = fused._weight_sum() if packed.zeros_x is not None else None
+            inter = kernel.w4a4_swiglu(packed, fused.weight, fused.weight_scales, wsum, fused.bias)
+        else:
+            gate = self.gate_proj.kernel_matmul(packed, torch.float16)
+            up = self.up_proj.kernel_matmul(packed, torch.float16)
+            inter = kernel.swiglu(gate, up)
     else:
-        gate = self.gate_proj(x).to(torch.float16)
-        up = self.up_proj(x).to(torch.float16)
-    out = self.down_proj(kernel.swiglu(gate, up))
+        assert packed_input is None
+        inter = kernel.swiglu(self.gate_proj(x).to(torch.float16), self.up_proj(x).to(torch.float16))
+    out = self.down_proj(inter)
     return out if out.dtype == x.dtype else out.to(x.dtype)
+
+
+def _stack_linears(linears):
+    """One Linear4bit whose weight is the row-wise concatenation of `linears`' weights; the
+    originals' buffers become views of it, so nothing is stored twice and state_dict keeps the
+    per-projection names."""
+    mods = [lin.kernel_module for lin in linears]
+    if any(m.bias is not None for m in mods) and not all(m.bias is not None for m in mods):
+        return None
+    k = mods[0].in_features
+    fused = snn.Linear4bit(k, sum(m.out_features for m in mods), bias=mods[0].bias is not None)
+    fused.weight = torch.cat([m.weight for m in mods], dim=0).contiguous()
+    fused.weight_scales = torch.cat([m.weight_scales.to(torch.float16) for m in mods], dim=0).contiguous()
+    if mods[0].bias is not None:
+        fused.bias = torch.cat([m.bias for m in mods], dim=0).contiguous()
+    row = 0
+    for m in mods:
+        m.weight = fused.weight[row:row + m.out_features]
+        m.weight_scales = fused.weight_scales[row:row + m.out_features]
+        if m.bias is not None:
+            m.bias = fused.bias[row:row + m.out_features]
+        if hasattr(m, "weight_sum"):
+            del m.weight_sum
+        row += m.out_features
+    return fused
+
+
+def fuse_projections_(layer):
+    """Concatenates q/k/v into one GEMM and gate/up into one (SwiGLU-fused for decode) where the
+    siblings share their quantized input.  Call after the weights are loaded and on their final
+    device (moving the module afterwards would split the views again; call it once more then)."""
+    at = layer.self_attn
+    if _shares_input(at.q_proj, at.k_proj, at.v_proj):
+        object.__setattr__(at, "qkv_fused", _stack_linears([at.q_proj, at.k_proj, at.v_proj]))
+    mlp = getattr(layer, "mlp", None)
+    if hasattr(mlp, "gate_proj") and _shares_input(mlp.gate_proj, mlp.up_proj) \
+            and mlp.gate_proj.out_features == mlp.up_proj.out_features:
+        object.__setattr__(mlp, "gate_up_fused", _stack_linears([mlp.gate_proj, mlp.up_proj]))
+    return layer
 
 
 # ----------------------------------------------------------------------------- decoder stack
@@ -213,6 +281,7 @@ class DecoderConfig:
     a_asym: bool = False
     a_clip_ratio: float = 1.0
     had_adj: bool = True              # SignRot sign vector on down_proj's rotation
+    fuse_edges: bool = True           # fused launches across the path's edges (same bits as the separate ones)
 
 
 class KernelAttention(torch.nn.Module):
@@ -249,15 +318,39 @@ class KernelDecoderLayer(torch.nn.Module):
         self.post_attention_layernorm = snn.RMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps)
         self.self_attn = KernelAttention(cfg, layer_idx)
         self.mlp = KernelMLP(cfg) if cfg.num_local_experts == 0 else None   # sparse block attached later
+        self.fuse_edges = cfg.fuse_edges
+        self.self_attn.fuse_rope_append = cfg.fuse_edges
 
-    def forward(self, hidden_states, position_embeddings, past_key_values=None):
-        attn, _ = self.self_attn(self.input_layernorm(hidden_states), position_embeddings,
-                                 past_key_values=past_key_values)
-        hidden_states = hidden_states + attn
-        mlp_out = self.mlp(self.post_attention_layernorm(hidden_states))
-        if isinstance(mlp_out, tuple):      # sparse block: (output, router logits)
-            mlp_out = mlp_out[0]
-        return hidden_states + mlp_out
+    def _fusable(self, x):
+        return (self.fuse_edges and x.dtype == torch.float16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384)
+
+    def forward(self, hidden_states, position_embeddings, past_key_values=None, delta=None):
+        """`delta`: the previous layer's MLP output, not yet added to the residual stream (the add
+        is fused into this layer's first normalisation).  Returns (hidden, delta) in the same form."""
+        at, mlp = self.self_attn, self.mlp
+        q = at.q_proj.kernel_quantizer
+        if self._fusable(hidden_states) and _shares_input(at.q_proj, at.k_proj, at.v_proj):
+            # residual add + RMSNorm + quantizer of q/k/v: one launch
+            hidden_states, packed = kernel.add_rmsnorm_quant(
+                hidden_states, delta, self.input_layernorm.eps, self.input_layernorm.mean_dim, q.clip_ratio,
+                asym=isinstance(q, snn.AsymQuantizer))
+            attn, _ = at(hidden_states, position_embeddings, past_key_values=past_key_values, packed_input=packed)
+        else:
+            if delta is not None:
+                hidden_states = hidden_states + delta
+            attn, _ = at(self.input_layernorm(hidden_states), position_embeddings, past_key_values=past_key_values)
+        norm2 = self.post_attention_layernorm
+        if self._fusable(hidden_states) and hasattr(mlp, "gate_proj") and _shares_input(mlp.gate_proj, mlp.up_proj):
+            q = mlp.gate_proj.kernel_quantizer
+            hidden_states, packed = kernel.add_rmsnorm_quant(hidden_states, attn, norm2.eps, norm2.mean_dim,
+                                                             q.clip_ratio, asym=isinstance(q, snn.AsymQuantizer))
+            mlp_out = mlp(hidden_states, packed_input=packed)
+        else:
+            hidden_states = hidden_states + attn
+            mlp_out = mlp(norm2(hidden_states))
+            if isinstance(mlp_out, tuple):      # sparse block: (output, router logits)
+                mlp_out = mlp_out[0]
+        return hidden_states, mlp_out
 
 
 class _Logits:
@@ -299,12 +392,18 @@ class KernelDecoderModel(torch.nn.Module):
         elif cache_position.numel() == 1 and t > 1:
             cache_position = cache_position + torch.arange(t, device=input_ids.device)
         pos = self.rotary(cache_position)
-        h = self.embed_tokens(input_ids)
+        h, delta = self.embed_tokens(input_ids), None
         for layer in self.layers:
-            h = layer(h, pos, past_key_values)
+            h, delta = layer(h, pos, past_key_values, delta)
         if last_token_only:
-            h = h[:, -1:, :]
-        return _Logits(self.lm_head(self.norm(h)))
+            h, delta = h[:, -1:, :], delta[:, -1:, :]
+        return _Logits(self.lm_head(self.norm(h + delta)))
+
+    def fuse_projections_(self):
+        if self.config.fuse_edges:
+            for layer in self.layers:
+                fuse_projections_(layer)
+        return self
 
     @torch.no_grad()
     def random_init_(self, seed: int = 0):
@@ -351,7 +450,7 @@ class KernelDecoderModel(torch.nn.Module):
                                                 sign_down=sd_sign, asym=cfg.a_asym, clip_ratio=cfg.a_clip_ratio)
         self.embed_tokens.weight.copy_(torch.randn(self.embed_tokens.weight.shape, generator=g, device=dev) * 0.02)
         self.lm_head.weight.copy_(torch.randn(self.lm_head.weight.shape, generator=g, device=dev) * 0.02)
-        return self
+        return self.fuse_projections_()
 
 
 def build_paged_cache(model, batch_size, max_length, page_size=None):

@@ -160,6 +160,43 @@ def kv_append_quant(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, 
         int(bool(hadamard_k)))
 
 
+def _token_stride(name, t, heads, D):
+    """Element stride between consecutive tokens of a [B, T, H, D] tensor whose heads are dense
+    (it may be a column range of a wider projection output)."""
+    if t.dtype != torch.float16 or t.dim() != 4 or t.size(2) != heads or t.size(3) != D:
+        raise RuntimeError(f"rope_kv_append expects fp16 [B, T, {heads}, {D}] {name}")
+    B, T = t.size(0), t.size(1)
+    # the stride of a size-1 dimension carries no information
+    stride = t.stride(1) if T > 1 else (t.stride(0) if B > 1 else heads * D)
+    if t.stride(3) != 1 or (heads > 1 and t.stride(2) != D) or (B > 1 and T > 1 and t.stride(0) != T * stride):
+        raise RuntimeError(f"rope_kv_append: {name} must have dense heads and a uniform token stride")
+    return stride
+
+
+def rope_kv_append(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, q, k, v, cos, sin, layer_idx,
+                   hadamard_k=True, want_k=False):
+    """Rotary embedding on q and k, then the fused K/V append, in one launch.  q/k/v fp16
+    [B, T, H, D], possibly column ranges of one fused projection output; cos/sin fp16
+    [1 or B, T, D].  Returns (rotated q, contiguous; rotated k or None)."""
+    dev = require_cuda("rope_kv_append", kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, q, k, v, cos, sin,
+                       strided=(q, k, v))
+    L, H, P, D = _geometry(kv_data)
+    B, T, hq = q.size(0), q.size(1), q.size(2)
+    qs, ks, vs = _token_stride("q", q, hq, D), _token_stride("k", k, H, D), _token_stride("v", v, H, D)
+    if k.shape[:2] != (B, T) or v.shape[:2] != (B, T):
+        raise RuntimeError("rope_kv_append: q, k and v must agree on batch and sequence")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    if cos.dtype != torch.float16 or cos.shape != sin.shape or cos.dim() != 3 or cos.size(1) != T or cos.size(2) != D \
+            or cos.size(0) not in (1, B):
+        raise RuntimeError("rope_kv_append expects fp16 cos/sin of shape [1 or B, T, head_dim]")
+    q_out = torch.empty((B, T, hq, D), dtype=torch.float16, device=dev)
+    k_out = torch.empty((B, T, H, D), dtype=torch.float16, device=dev) if want_k else None
+    run(dev, "sr_rope_kv_append", ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices), ptr(last_page_offset),
+        ptr(q), ptr(k), ptr(v), qs, ks, vs, ptr(cos), ptr(sin), cos.size(0), ptr(q_out), ptr(k_out), B, T, L,
+        int(layer_idx), hq, H, P, D, int(bool(hadamard_k)))
+    return q_out, k_out
+
+
 # ----------------------------------------------------------------------------- cache object
 
 class _AttentionStub:
@@ -265,10 +302,22 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
         original K/V for the caller's dense attention; decode returns a callable that attends a
         query [B, 1, q_heads, 128] to the cache (kv_cache.py:295-415)."""
         bsz, added, heads, hd = key_states.shape
-        assert bsz == self.batch_size
         cache_kwargs = cache_kwargs or {}
         if cache_kwargs.get("attention_mask") is not None:
             raise NotImplementedError("padded (masked) prefill is not supported by the fused append")
+        specs, first = self._advance(bsz, added, layer_idx)
+        k16 = key_states if key_states.dtype == torch.float16 else key_states.to(torch.float16)
+        v16 = value_states if value_states.dtype == torch.float16 else value_states.to(torch.float16)
+        kv_append_quant(**specs, k=k16.contiguous(), v=v16.contiguous(), layer_idx=layer_idx,
+                        hadamard_k=self.hadamard_dtype is not None)
+        if first:
+            return key_states, value_states
+        return functools.partial(self._stub.forward, num_kv_heads=heads, attention_kwargs=specs,
+                                 layer_idx=layer_idx)
+
+    def _advance(self, bsz, added, layer_idx):
+        """Host-side bookkeeping of one `update`: length, pages, index tensors, first-call flag."""
+        assert bsz == self.batch_size
         if layer_idx == 0:
             new_len = self.length + added
             self._ensure_page_cnt_per_batch(self.page_cnt_from_length(new_len))
@@ -279,14 +328,22 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
             self._needs_init[layer_idx] = False
         else:
             assert added == 1
-        k16 = key_states if key_states.dtype == torch.float16 else key_states.to(torch.float16)
-        v16 = value_states if value_states.dtype == torch.float16 else value_states.to(torch.float16)
-        kv_append_quant(**specs, k=k16.contiguous(), v=v16.contiguous(), layer_idx=layer_idx,
-                        hadamard_k=self.hadamard_dtype is not None)
+        return specs, first
+
+    def update_with_rope(self, query_states, key_states, value_states, cos, sin, layer_idx: int):
+        """`rope_qk` + `update` in one launch (kernel_utils.py:118-141 of the reference's glue calls
+        them back to back).  q/k/v are the projections BEFORE the rotary embedding, fp16
+        [B, T, H, 128], possibly column ranges of one fused projection.  Returns
+        (rotated q, what `update` returns: (rotated k, v) on the first call of a layer, the
+        attention callable afterwards)."""
+        bsz, added, heads, hd = key_states.shape
+        specs, first = self._advance(bsz, added, layer_idx)
+        q_rot, k_rot = rope_kv_append(**specs, q=query_states, k=key_states, v=value_states, cos=cos, sin=sin,
+                                      layer_idx=layer_idx, hadamard_k=self.hadamard_dtype is not None, want_k=first)
         if first:
-            return key_states, value_states
-        return functools.partial(self._stub.forward, num_kv_heads=heads, attention_kwargs=specs,
-                                 layer_idx=layer_idx)
+            return q_rot, (k_rot, value_states)
+        return q_rot, functools.partial(self._stub.forward, num_kv_heads=heads, attention_kwargs=specs,
+                                        layer_idx=layer_idx)
 
     def _set_page_cnt(self, page_cnt: int):
         torch.mul(self._indptr_base, page_cnt, out=self._kv_indptr_buf)

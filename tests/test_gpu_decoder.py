@@ -99,3 +99,26 @@ def test_generate_graph_and_eager_agree():
     a = ku.generate(model, prompt, 6, page_size=16, use_graph=True)
     b = ku.generate(model, prompt, 6, page_size=16, use_graph=False)
     assert a.shape == (2, 6) and torch.equal(a, b)
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("experts", [0, 4])
+def test_fused_edges_give_the_bits_of_the_separate_launches(experts):
+    """add+RMSNorm+quantizer, one q/k/v GEMM, rope+append, gate/up+SwiGLU: every fused launch keeps
+    the rounding points of the launches it replaces, so logits agree bit for bit."""
+    cfg_kw = dict(hidden_size=512, intermediate_size=1536, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=128, vocab_size=512, num_local_experts=experts)
+    models = []
+    for fuse in (True, False):
+        with torch.device(DEV):
+            m = ku.KernelDecoderModel(ku.DecoderConfig(fuse_edges=fuse, **cfg_kw))
+        models.append(m.to(DEV).random_init_(5))
+    fused, plain = models
+    assert hasattr(fused.layers[0].self_attn, "qkv_fused") and not hasattr(plain.layers[0].self_attn, "qkv_fused")
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, 512, (2, 21), generator=g).to(DEV)
+    toks = [torch.randint(0, 512, (2, 1), generator=g).to(DEV) for _ in range(3)]
+    ca, cb = (ku.build_paged_cache(m, 2, 32, page_size=16) for m in models)
+    assert torch.equal(fused(prompt, past_key_values=ca).logits, plain(prompt, past_key_values=cb).logits)
+    for t in toks:
+        assert torch.equal(fused(t, past_key_values=ca).logits, plain(t, past_key_values=cb).logits)

@@ -149,3 +149,28 @@ def test_grouped_matches_dense():
                 assert torch.equal(got[row:row + m], want)
                 row += m
         assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16, 32, 40])
+@pytest.mark.parametrize("F,K", [(1536, 512), (14336, 4096), (104, 256)])
+@pytest.mark.parametrize("asym", [False, True])
+def test_w4a4_swiglu_equals_two_linears_and_swiglu(M, F, K, asym):
+    """gate_proj + up_proj + SwiGLU in one launch: the bits of the three separate launches (rows
+    beyond 32 take the separate route inside the wrapper)."""
+    g = torch.Generator().manual_seed(M * 131 + F)
+    w = torch.randint(0, 256, (2 * F, K // 2), generator=g, dtype=torch.uint8).to(DEV)
+    ws = ((torch.rand((2 * F, 1), generator=g) * 0.5 + 0.5) / K).half().to(DEV)
+    x = torch.randn((M, K), generator=g).half().to(DEV)
+    if asym:
+        q, s, z = kernel.asym_quant_dynamic(x)
+        packed = kernel.PackedQuantizedTensor(q, s, z.to(torch.int8))
+        wsum = kernel.sum_i4(w)
+    else:
+        q, s = kernel.sym_quant_dynamic(x)
+        packed = kernel.PackedQuantizedTensor(q, s)
+        wsum = None
+    got = kernel.w4a4_swiglu(packed, w, ws, wsum)
+    gate = kernel.w4a4_linear(packed, w[:F], ws[:F], wsum[:F] if asym else None)
+    up = kernel.w4a4_linear(packed, w[F:], ws[F:], wsum[F:] if asym else None)
+    want = kernel.swiglu(gate, up)
+    assert got.shape == (M, F) and torch.equal(got, want)

@@ -118,3 +118,54 @@ def test_cache_reset_and_graph_friendly_specs():
     cache.reset()
     assert cache.get_seq_length() == 0
     assert isinstance(cache.update(k, k, 0), tuple)
+
+
+@pytest.mark.parametrize("T,start,fused_input", [(1, 37, True), (1, 0, False), (20, 0, True), (33, 0, False)])
+def test_rope_kv_append_equals_rope_then_append(T, start, fused_input):
+    """One launch for rotary embedding + K rotation + K/V quantizers + page scatter: same cache
+    bytes and same rotated q as `rope_qk` followed by `update`; q/k/v may be column ranges of one
+    fused projection output."""
+    B, Hq, Hkv, D, page, L = 3, 8, 2, 128, 16, 2
+    g = torch.Generator().manual_seed(T * 7 + start)
+    total = (Hq + 2 * Hkv) * D
+    qkv = torch.randn((B, T, total), generator=g).half().to(DEV)
+    q = qkv[..., :Hq * D].unflatten(-1, (Hq, D))
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].unflatten(-1, (Hkv, D))
+    v = qkv[..., (Hq + Hkv) * D:].unflatten(-1, (Hkv, D))
+    if not fused_input:
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    ang = torch.rand((1, T, D), generator=g) * 6.0
+    cos, sin = ang.cos().half().to(DEV), ang.sin().half().to(DEV)
+
+    def fresh():
+        c = kvc.MultiLayerPagedKVCache4Bit(B, page, start + T + 4, DEV, L, Hkv, D, group_size=Hq // Hkv)
+        if start:
+            pk = torch.randn((B, start, Hkv, D), generator=torch.Generator().manual_seed(1)).half().to(DEV)
+            for layer in range(L):
+                c.update(pk, pk, layer)
+        return c
+    a, b = fresh(), fresh()
+    layer = 1
+    # reference route: rope in place on copies, then the fused append
+    q2, k2 = q.contiguous().clone(), k.contiguous().clone()
+    kernel.rope_qk(q2, k2, cos, sin)
+    a.update(k2, v.contiguous(), 0)
+    out_a = a.update(k2, v.contiguous(), layer)
+    q_rot, _ = b.update_with_rope(q, k, v, cos, sin, 0)
+    q_rot, out_b = b.update_with_rope(q, k, v, cos, sin, layer)
+    assert torch.equal(q_rot, q2)
+    if start == 0:
+        assert isinstance(out_a, tuple) and isinstance(out_b, tuple)
+        assert torch.equal(out_b[0], k2) and torch.equal(out_b[1], v)
+    else:
+        assert callable(out_b)
+        assert torch.equal(out_b(q_rot), out_a(q2))
+    pages = a.page_cnt_from_length(start + T) * B
+    # slots past the sequence end are never written: compare through a decode-independent mask
+    pa, pb = a.pages[:pages, layer], b.pages[:pages, layer]
+    sa, sb = a.scales[:pages, layer], b.scales[:pages, layer]
+    n = start + T
+    for pos in range(start, n):
+        for bb in range(B):
+            pg, e = (pos // page) * B + bb, pos % page
+            assert torch.equal(pa[pg, :, :, e], pb[pg, :, :, e]) and torch.equal(sa[pg, :, :, e], sb[pg, :, :, e])

@@ -193,3 +193,35 @@ def test_swiglu():
     d = (y.float() - want.float()).abs()
     assert bool((d <= want.float().abs() * 2 ** -10 + 1e-7).all())
     assert (y != want).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 4096), (16, 4096), (37, 512), (300, 2048), (5, 14336), (3, 8192)])
+@pytest.mark.parametrize("with_delta", [True, False])
+@pytest.mark.parametrize("asym", [False, True])
+def test_add_rmsnorm_quant_equals_the_three_launches(rows, cols, with_delta, asym):
+    """The fused residual add + RMSNorm + quantizer gives the bits of `x + delta`, `rmsnorm`,
+    `sym/asym_quant_dynamic` run one after the other."""
+    x = _x(rows, cols, seed=rows + cols).to(DEV)
+    delta = _x(rows, cols, seed=7, scale=0.5).to(DEV) if with_delta else None
+    total, packed, normed = kernel.add_rmsnorm_quant(x, delta, 1e-5, cols, clip_ratio=0.9 if asym else 1.0,
+                                                      asym=asym, return_normed=True)
+    want_total = x + delta if with_delta else x
+    want_normed = kernel.rmsnorm(want_total, 1e-5, cols)
+    assert torch.equal(total, want_total) and torch.equal(normed, want_normed)
+    if asym:
+        q, s, z = kernel.asym_quant_dynamic(want_normed, 0.9)
+        assert torch.equal(packed.zeros_x, z.to(torch.int8))
+    else:
+        q, s = kernel.sym_quant_dynamic(want_normed, 1.0)
+        assert packed.zeros_x is None
+    assert torch.equal(packed.quantized_x, q) and torch.equal(packed.scales_x, s)
+    # and the oracle's statement of the normalisation (row sum reduced in another order: one fp16 ulp)
+    want_h = oracle.rmsnorm(want_total.cpu(), 1e-5, cols)
+    ulp = (want_h.float().abs() * 2 ** -10).clamp_min(2 ** -24)
+    assert bool(((normed.cpu().float() - want_h.float()).abs() <= ulp).all())
+
+
+def test_add_rmsnorm_quant_rejects_odd_widths():
+    x = _x(2, 100).to(DEV)
+    with pytest.raises(RuntimeError):
+        kernel.add_rmsnorm_quant(x, None, 1e-5, 100)
