@@ -671,6 +671,8 @@ def run_decode_model(name, cfg_kwargs, bsz, prompt, steps, dev):
     cache = ku.build_paged_cache(model, bsz, prompt + steps + 8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.no_grad():
+        model(ids, past_key_values=cache, last_token_only=True)      # warm-up prefill (first-use costs)
+        cache.reset()
         torch.cuda.synchronize()
         e0.record()
         logits = model(ids, past_key_values=cache, last_token_only=True).logits
@@ -706,7 +708,7 @@ def run_decode_model(name, cfg_kwargs, bsz, prompt, steps, dev):
                       "step_bytes_gb": round(step_bytes / 1e9, 3), "step_gbs": round(step_bytes / t_dec / 1e6, 1),
                       "frac_hbm": round(step_bytes / t_dec / 1e6 / hbm, 3),
                       "note": "weights (every expert a step can touch), int4 KV at the mean context and the fp16 lm_head "
-                              "counted once per step; prefill time is one cold call, dense prefill attention included"}))
+                              "counted once per step; prefill time is the second of two calls, dense prefill attention included"}))
     del model, cache, dec
     torch.cuda.empty_cache()
 
@@ -724,6 +726,22 @@ def main():
                     help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | decode_layer | "
                          "rotate14336 | decode")
     args = ap.parse_args()
+    if args.kernel_case == "decode_model_small":
+        # two Llama-3-8B-shaped layers, batch 8 at context 2048: three eager decode steps (launch lists)
+        from signrot_b200.transformers import kernel_utils as ku
+        dev = torch.device("cuda", 0)
+        with torch.device(dev):
+            model = ku.KernelDecoderModel(ku.DecoderConfig(num_hidden_layers=2, vocab_size=4096))
+        model = model.to(dev).random_init_(0)
+        cache = ku.build_paged_cache(model, 8, 2048 + 16)
+        with torch.no_grad():
+            model(torch.randint(0, 4096, (8, 2048), device=dev), past_key_values=cache, last_token_only=True)
+            tok = torch.randint(0, 4096, (8, 1), device=dev)
+            for _ in range(3):
+                model(tok, past_key_values=cache)
+        torch.cuda.synchronize()
+        print("kernel case decode_model_small: done")
+        return
     if args.kernel_case == "decode_model":
         run_decode_model("decode_model_llama3_8b", {}, 8, 2048, 128, torch.device("cuda", 0))
         return

@@ -38,6 +38,36 @@ inline int check_launch(const char *what) {
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// ---- programmatic dependent launch (decode-graph kernels)
+//
+// A kernel launched through launch_pdl may be scheduled while the kernel before it on the stream is
+// still running; it must execute pdl_wait() (every thread, before any early exit) ahead of its
+// first access to memory that an earlier kernel writes or reads, and everything before that point
+// may only touch memory no kernel of the stream writes (weights, tables).  pdl_wait() returns once
+// all earlier kernels have completed and their writes are visible, so ordering is transitive as
+// long as every kernel launched this way waits.  pdl_trigger() lets the next kernel be scheduled
+// early; without the launch attribute both are no-ops.  SIGNROT_B200_PDL=0 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();   // elementwise.cu
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 template <typename T>
 __host__ __device__ __forceinline__ T cdiv(T a, T b) { return (a + b - 1) / b; }
 

@@ -4,8 +4,18 @@
 // is vectorised (128-bit) and rows are held in registers.
 #include "common.cuh"
 #include <cfloat>
+#include <cstdlib>
 
 namespace sr {
+
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("SIGNROT_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
 
 // ------------------------------------------------------------------ RMSNorm
 // out = rn_h(x * rsqrtf(sum(x^2) / mean_dim + eps)), fp32 accumulation (fused.cu:278-302)

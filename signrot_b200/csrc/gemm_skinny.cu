@@ -83,6 +83,11 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     constexpr int RED_BUFS = NT <= 2 ? 2 : 1;
     extern __shared__ __align__(16) uint8_t sk_smem[];
     __shared__ uint32_t item_start[GROUPED ? SK_MAX_EXPERTS + 1 : 1];   // first item of every expert
+    // Launched with programmatic serialization (launch_pdl): the weight stream below does not depend on
+    // the kernel before this one, so the first ring of copies is in flight while that kernel finishes;
+    // activations, scales and (grouped) the row offsets are read only after pdl_wait().
+    pdl_trigger();
+    if (GROUPED) pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     // ring[warp][stage][row slot 0 .. 2 MT - 1][lane] (16 bytes each)
@@ -168,6 +173,7 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     };
 #pragma unroll 1
     for (int d = 0; d < DEPTH; ++d) issue(d);
+    if (!GROUPED) pdl_wait();
 
     // activation fragments of the step after the current one (they come from L1/L2, one step ahead is enough)
     auto load_x = [&](const SkItem &it, uint32_t step, uint4 (&x)[NT]) {
@@ -306,8 +312,8 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                              (int)skinny_smem(NT, MT));                                        \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, MT), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, row_off, \
-                                                               num_experts, ep);                               \
+        launch_pdl(kfn, dim3(grid), dim3(SK_WARPS * 32), skinny_smem(NT, MT), st, A, B, (uint32_t)M, (uint32_t)N,   \
+                   (uint32_t)K, row_off, num_experts, ep);                                                     \
     } while (0)
     if (grouped) {
         if (mt == 2) SR_SK(4, 2, true);
@@ -352,7 +358,8 @@ int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                              (int)skinny_smem(NT, 2));                                         \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "w4a4_swiglu: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
-        kfn<<<grid, SK_WARPS * 32, skinny_smem(NT, 2), st>>>(A, B, (uint32_t)M, (uint32_t)N, (uint32_t)K, nullptr, 0, ep); \
+        launch_pdl(kfn, dim3(grid), dim3(SK_WARPS * 32), skinny_smem(NT, 2), st, A, B, (uint32_t)M, (uint32_t)N,    \
+                   (uint32_t)K, (const int32_t *)nullptr, 0, ep);                                              \
     } while (0)
     if (nt == 1) SR_SKS(1);
     else if (nt == 2) SR_SKS(2);

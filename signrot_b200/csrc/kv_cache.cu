@@ -178,6 +178,8 @@ rope_kv_append_kernel(PagedKV kv, const __half *__restrict__ q, const __half *__
                       const __half *__restrict__ cosv, const __half *__restrict__ sinv, uint32_t cos_seqs,
                       __half *__restrict__ q_out, __half *__restrict__ k_out, uint32_t batch, uint32_t T, uint32_t hq,
                       int had_k, float had_scale) {
+    pdl_trigger();   // launched with programmatic serialization: see launch_pdl
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint32_t per_tok = hq + 2 * kv.heads;
     const uint32_t total = batch * T * per_tok;
@@ -448,6 +450,8 @@ decode_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, 
 // grid (batch, q heads), 128 threads: combine the per-chunk states (decode.cuh:726-751).
 __global__ void __launch_bounds__(128)
 decode_merge_kernel(const float *__restrict__ tmp, __half *__restrict__ o, uint32_t num_chunks) {
+    pdl_trigger();   // launched with programmatic serialization: see launch_pdl
+    pdl_wait();
     const uint32_t b = blockIdx.x, h = blockIdx.y, H = gridDim.y;
     const int tid = threadIdx.x;
     const float *src = tmp + ((size_t)b * H + h) * num_chunks * (HD + 4);
@@ -571,7 +575,7 @@ int sr_rope_kv_append(void *kv_data, void *kv_param, const void *kv_indptr, cons
     SR_REQUIRE(warps < (1ll << 31), SR_ERR_UNSUPPORTED, "rope_kv_append: too many tokens");
     int64_t ctas = cdiv<int64_t>(warps, 8);
     if (ctas > 148 * 8) ctas = 148 * 8;
-    rope_kv_append_kernel<<<(unsigned)ctas, 256, 0, as_stream(stream)>>>(
+    launch_pdl(rope_kv_append_kernel, dim3((unsigned)ctas), dim3(256), 0, as_stream(stream),
         kv, (const __half *)q, (const __half *)k, (const __half *)v, q_stride, k_stride, v_stride, (const __half *)cos,
         (const __half *)sin, (uint32_t)cos_seqs, (__half *)q_out, (__half *)k_out, (uint32_t)batch_size,
         (uint32_t)new_tokens, (uint32_t)num_qo_heads, hadamard_k, (float)(1.0 / sqrt(128.0)));
@@ -620,7 +624,7 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
     if (rc) return rc;
     if (num_chunks > 1) {
         dim3 mgrid((unsigned)batch_size, (unsigned)num_qo_heads);
-        decode_merge_kernel<<<mgrid, 128, 0, st>>>(tp, op, nc);
+        launch_pdl(decode_merge_kernel, mgrid, dim3(128), 0, st, (const float *)tp, op, nc);
         rc = check_launch("batch_decode_i4 (merge)");
     }
     return rc;

@@ -58,6 +58,8 @@ template <int G>
 __global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
                  uint32_t num_chunks, int had_q, float had_scale) {
+    pdl_trigger();   // launched with programmatic serialization (launch_pdl); everything read here is produced upstream
+    pdl_wait();
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
     const uint32_t hq_total = gridDim.y * G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -359,7 +361,7 @@ bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __ha
         auto kfn = decode_tc_kernel<GG>;                                                                       \
         if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
             return false;                                                                                      \
-        kfn<<<grid, DT_WARPS * 32, DT_RING_BYTES, st>>>(q, kv, o, tmp, num_chunks, had_q, had_scale);          \
+        launch_pdl(kfn, grid, dim3(DT_WARPS * 32), (size_t)DT_RING_BYTES, st, q, kv, o, tmp, num_chunks, had_q, had_scale); \
     } while (0)
     switch (G) {
         case 1: SR_DT(1); break;

@@ -36,6 +36,10 @@ act_quant_dynamic_kernel(const __half *__restrict__ x, const int8_t *__restrict_
                          uint8_t *__restrict__ q, NormArgs na = NormArgs{}) {
     static_assert(!NORM || TPR == 256, "the fused normalisation owns a whole CTA per row");
     constexpr int ROWS_PER_CTA = 256 / TPR;
+    if (NORM) {   // launched with programmatic serialization: see launch_pdl
+        pdl_trigger();
+        pdl_wait();
+    }
     const int tid = threadIdx.x;
     const int sub = tid % TPR;  // index inside the row team
     const uint32_t row = blockIdx.x * ROWS_PER_CTA + tid / TPR;
@@ -524,11 +528,11 @@ int sr_add_rmsnorm_quant(const void *x, const void *delta, int64_t rows, int64_t
 #define SR_LAUNCH_NQ(NV)                                                                                         \
     do {                                                                                                         \
         if (asym)                                                                                                \
-            act_quant_dynamic_kernel<256, NV, true, true><<<r, 256, 0, st>>>(                                    \
-                (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, (__half *)zero, (uint8_t *)q, na); \
+            launch_pdl(act_quant_dynamic_kernel<256, NV, true, true>, dim3(r), dim3(256), 0, st,                 \
+                       (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, (__half *)zero, (uint8_t *)q, na); \
         else                                                                                                     \
-            act_quant_dynamic_kernel<256, NV, false, true><<<r, 256, 0, st>>>(                                   \
-                (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, nullptr, (uint8_t *)q, na); \
+            launch_pdl(act_quant_dynamic_kernel<256, NV, false, true>, dim3(r), dim3(256), 0, st,                \
+                       (const __half *)x, nullptr, nullptr, r, c, clip_ratio, (__half *)scale, nullptr, (uint8_t *)q, na); \
     } while (0)
     if (nvec <= 256) SR_LAUNCH_NQ(1);
     else if (nvec <= 512) SR_LAUNCH_NQ(2);

@@ -67,6 +67,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, qd = lane & 3;  // mma fragment coordinates
+    pdl_trigger();   // launched with programmatic serialization (launch_pdl): the tables below are weights
 
     // ---- A fragments of H (28 x 28 padded with zeros to 32 x 32), row-major fp16
     uint32_t afr[2][2][4];
@@ -144,6 +145,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
     };
     // rows 28..31 of Z are the zero padding of the k dimension (written once: nothing else touches them)
     if (tid < 4 * PZ / 8) reinterpret_cast<uint4 *>(zbuf + KH * PZ)[tid] = make_uint4(0, 0, 0, 0);
+    pdl_wait();      // x and expert_ids come from the kernels before this one
     if (blockIdx.x < rows) fetch(blockIdx.x);
 
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -399,8 +401,8 @@ int launch_rotate_had28(const RotateArgs &a, cudaStream_t st) {
         auto kfn = rotate_quant_had28_kernel<T, LATE, ASYM>;                                                   \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);\
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));         \
-        kfn<<<grid, THREADS, SMEM_BYTES, st>>>((const T *)a.x, (const __half *)a.hadk, a.sign, a.expert_ids, \
-                                               a.rows, a.scale, a.clip, a.q, a.q_scale, a.q_zero, (__half *)a.out); \
+        launch_pdl(kfn, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, st, (const T *)a.x, (const __half *)a.hadk,   \
+                   a.sign, a.expert_ids, a.rows, a.scale, a.clip, a.q, a.q_scale, a.q_zero, (__half *)a.out); \
     } while (0)
     if (a.in_dtype == SR_F16) {
         if (late) SR_H28(__half, true, false);

@@ -62,6 +62,7 @@ rotate_quant_heads32_tc_kernel(const InT *__restrict__ x, const int8_t *__restri
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pair = warp >> 1, half = warp & 1;
+    pdl_trigger();   // launched with programmatic serialization (launch_pdl): the sign table is a weight
     const int g = lane >> 2, qd = lane & 3;
     uint32_t *sgn_all = reinterpret_cast<uint32_t *>(tc_smem + (size_t)TC_PAIRS * 2 * TC_ROW_BYTES);
     float2 *exch = reinterpret_cast<float2 *>(sgn_all + TC_SIGN_WORDS);   // [warp]: (max, min) of its half row
@@ -108,6 +109,7 @@ rotate_quant_heads32_tc_kernel(const InT *__restrict__ x, const int8_t *__restri
         }
     };
 
+    pdl_wait();      // x comes from the kernel before this one
     uint32_t row = row_begin + pair;
     int which = 0;
     if (row < row_end) fetch(row, 0);
@@ -306,8 +308,8 @@ int launch_rotate_heads32(const RotateArgs &a, cudaStream_t st) {
         auto kfn = rotate_quant_heads32_tc_kernel<T, ASYM>;                                                     \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);   \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));              \
-        kfn<<<grid, TC_WARPS * 32, TC_SMEM, st>>>((const T *)a.x, a.sign, a.rows, scale4, a.clip, a.q, a.q_scale, \
-                                                  a.q_zero, (__half *)a.out);                                   \
+        launch_pdl(kfn, dim3(grid), dim3(TC_WARPS * 32), (size_t)TC_SMEM, st, (const T *)a.x, a.sign, a.rows, scale4, \
+                   a.clip, a.q, a.q_scale, a.q_zero, (__half *)a.out);                                         \
     } while (0)
     if (a.in_dtype == SR_F16) {
         if (a.asym) SR_RQ(__half, true);
