@@ -16,6 +16,7 @@ What differs from the reference is how the work is done, not what is stored or r
 from __future__ import annotations
 
 import functools
+import os
 import math
 from typing import Any, Dict, Optional
 
@@ -266,7 +267,8 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
         are in flight; bounded by the page count (a chunk is a page range)."""
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         ctas = self.batch_size * self.num_heads
-        chunks = max(1, -(-2 * sms // ctas))
+        per_sm = int(os.environ.get("SIGNROT_B200_DECODE_CTAS_PER_SM", "2"))
+        chunks = max(1, -(-per_sm * sms // ctas))
         chunks = min(chunks, max(1, max_pages))
         self._stub.num_chunks = chunks
         if chunks > 1:

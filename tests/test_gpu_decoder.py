@@ -122,3 +122,15 @@ def test_fused_edges_give_the_bits_of_the_separate_launches(experts):
     assert torch.equal(fused(prompt, past_key_values=ca).logits, plain(prompt, past_key_values=cb).logits)
     for t in toks:
         assert torch.equal(fused(t, past_key_values=ca).logits, plain(t, past_key_values=cb).logits)
+
+
+@torch.no_grad()
+def test_checkpoint_reload_gives_the_same_logits(tmp_path):
+    from signrot_b200 import checkpoint as ck
+    model, cfg = small_model(seed=11)
+    ck.save_packed_checkpoint(model, str(tmp_path))
+    back = ck.load_packed_checkpoint(str(tmp_path), device=DEV)
+    prompt = torch.randint(0, cfg.vocab_size, (2, 19), generator=torch.Generator().manual_seed(4)).to(DEV)
+    a = model(prompt, past_key_values=ku.build_paged_cache(model, 2, 24, page_size=16)).logits
+    b = back(prompt, past_key_values=ku.build_paged_cache(back, 2, 24, page_size=16)).logits
+    assert torch.equal(a, b)
