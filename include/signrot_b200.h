@@ -179,6 +179,19 @@ int sr_rotate_quant(const void *x, int dtype, int64_t rows, int64_t n, const voi
                     const void *sign, const void *expert_ids, int64_t heads, float clip_ratio, int asym, void *q,
                     void *q_scale, void *q_zero, void *rotated, void *stream);
 
+/* ------------------------------------------------------------------ offline weight preparation */
+
+/* Per-channel symmetric int4 round-to-nearest of a weight matrix W [N, K] (dtype SR_F16, SR_BF16 or
+ * SR_F32), straight to packed codes [N, K/2] and fp16 scales [N].  Replaces, for one linear, the
+ * chain rtn_fwrd (fake_quant/gptq_utils.py:411-465: WeightQuantizer.find_params + quantize, with the
+ * SignRot sign unfolded before and refolded after on the symmetric grid [-7, 7]) ->
+ * ActQuantWrapper.enable_kernel -> Linear4bit.from_float (signrot/nn/linear.py:52-73: round(W / scale),
+ * pack_i4).  sign int8 [K] (+-1) or NULL; mse != 0 runs the clipping search of
+ * quant_utils.py:488-512 (80 candidates, error norm 2.4; error sums in fp64, so a row whose two best
+ * candidates tie within fp32 summation noise may pick the other one). */
+int sr_rtn_pack(const void *W, int dtype, int64_t N, int64_t K, const void *sign, int mse, void *packed, void *scale,
+                void *stream);
+
 /* ------------------------------------------------------------------ adjacent fused ops */
 
 /* Replaces _CUDA.rmsnorm (bindings.cpp:420-434, fused.cu:278-309). */

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "sr_hadamard": [_P, _I, _I64, _I64, _P, _I64, _F, _P, _I, _P, _I, _P],
     "sr_hadamard_heads": [_P, _I, _I64, _I64, _I64, _F, _I, _P, _I, _P],
     "sr_rotate_quant": [_P, _I, _I64, _I64, _P, _I64, _F, _P, _P, _I64, _F, _I, _P, _P, _P, _P, _P],
+    "sr_rtn_pack": [_P, _I, _I64, _I64, _P, _I, _P, _P, _P],
     "sr_rmsnorm": [_P, _I64, _I64, _F, _I64, _P, _P],
     "sr_add_rmsnorm_quant": [_P, _P, _I64, _I64, _F, _I64, _F, _I, _P, _P, _P, _P, _P, _P],
     "sr_rope_qk": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],

@@ -80,8 +80,8 @@ def matmul_hadUt_cuda(X, hadK, K):
 
 
 def apply_exact_had_to_linear(module, had_dim=-1, output=False):
-    """Folds an exact Hadamard into a Linear's weight, offline (hadamard.py:95-128).  Runs in
-    fp32 on the weight's own device with the butterfly above."""
+    """Folds an exact Hadamard into a Linear's weight, offline (hadamard.py:95-128), in fp32 on the
+    weight's own device."""
     assert isinstance(module, torch.nn.Linear)
     in_features, out_features = module.in_features, module.out_features
     if had_dim != -1:
@@ -89,18 +89,26 @@ def apply_exact_had_to_linear(module, had_dim=-1, output=False):
     W = module.weight.data
     dtype = W.dtype
     Wf = W.float()
+
+    def transform(x, hadK, K):
+        # on the GPU the fold runs through the library's fp32 transform (one launch per matrix),
+        # on the CPU through the torch butterfly
+        if x.is_cuda:
+            return _kernel.hadamard(x.contiguous(), hadK, K, fp32_mode=True)
+        return matmul_hadU(x, hadK=hadK, K=K)
+
     if had_dim == -1:
         if output:
             hadK, K = get_hadK(out_features)
-            Wf = matmul_hadU(Wf.t().contiguous(), hadK=hadK, K=K).t()
+            Wf = transform(Wf.t().contiguous(), hadK, K).t()
         else:
             hadK, K = get_hadK(in_features)
-            Wf = matmul_hadU(Wf, hadK=hadK, K=K)
+            Wf = transform(Wf, hadK, K)
     else:
         if not output:
             raise NotImplementedError("Not implemented (or tested) yet!")
         Wt = Wf.t().contiguous()
         shape = Wt.shape
-        Wt = matmul_hadU(Wt.reshape(-1, shape[-1] // had_dim, had_dim), hadK=None, K=1)
+        Wt = transform(Wt.reshape(-1, shape[-1] // had_dim, had_dim), None, 1)
         Wf = Wt.reshape(shape).t()
     module.weight.data = Wf.contiguous().to(dtype=dtype)

@@ -27,7 +27,7 @@ __all__ = [
     "kv_quant_pack", "rope_qk", "swiglu", "rmsnorm", "sym_dequant",
     "asym_quant_f16_si4", "asym_quant_f16_ui4", "sum_i4", "matmul_colrow_i8_i32",
     "w4a4_linear", "grouped_linear", "rotate_quant", "hadamard", "hadamard_heads",
-    "add_rmsnorm_quant", "w4a4_swiglu",
+    "add_rmsnorm_quant", "w4a4_swiglu", "rtn_pack",
 ]
 
 
@@ -499,6 +499,28 @@ def w4a4_swiglu(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum
     run(dev, "sr_w4a4_swiglu", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
         ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out))
     return out.view(*lead, N)
+
+
+def rtn_pack(weight, sign=None, mse=False):
+    """Offline weight preparation on the GPU: per-channel symmetric int4 round-to-nearest of a
+    float weight [N, K] with the SignRot sign unfolded before and refolded after (rtn_fwrd,
+    fake_quant/gptq_utils.py:411-465), written as the packed codes and fp16 scales that
+    `Linear4bit.from_float` (signrot/nn/linear.py:52-73) would store.  Returns
+    (uint8 [N, K/2], fp16 [N, 1])."""
+    if weight.dim() != 2 or weight.dtype not in _lib.DTYPE_TAG:
+        raise RuntimeError("rtn_pack expects a 2-D fp16, bf16 or fp32 weight")
+    weight = weight.contiguous()
+    if sign is not None:
+        sign = sign.to(device=weight.device, dtype=torch.int8).contiguous()
+        if sign.numel() != weight.shape[1]:
+            raise RuntimeError("rtn_pack: one sign per input channel")
+    dev = require_cuda("rtn_pack", weight, sign)
+    n, k = weight.shape
+    packed = torch.empty((n, k // 2), dtype=torch.uint8, device=dev)
+    scale = torch.empty((n, 1), dtype=torch.float16, device=dev)
+    run(dev, "sr_rtn_pack", ptr(weight), _lib.DTYPE_TAG[weight.dtype], n, k, ptr(sign), int(bool(mse)), ptr(packed),
+        ptr(scale))
+    return packed, scale
 
 
 def had_scale(n: int) -> float:

@@ -69,6 +69,22 @@ class Linear4bit(torch.nn.Module):
         return new
 
 
+def linear4bit_from_float_rtn(module: torch.nn.Linear, sign=None, mse=False) -> Linear4bit:
+    """A float Linear on the GPU -> Linear4bit in one kernel: per-channel symmetric RTN (optionally
+    with the MSE clipping search), SignRot sign refold, packing.  The route through the reference
+    is rtn_fwrd (fake_quant/gptq_utils.py:411-465) -> ActQuantWrapper.enable_kernel
+    (fake_quant/quant_utils.py:214-276) -> Linear4bit.from_float."""
+    W = module.weight.data
+    new = Linear4bit(module.in_features, module.out_features, bias=module.bias is not None, dtype=torch.float16)
+    new = new.to(W.device)
+    packed, scales = kernel.rtn_pack(W, sign=sign, mse=mse)
+    new.weight = packed
+    new.weight_scales = scales
+    if module.bias is not None:
+        new.bias = module.bias.data.to(torch.float16)
+    return new
+
+
 class AsymSymmLinear4bit(torch.nn.Module):
     """Variant whose activation codes are signed and whose zero term is always subtracted
     (linear.py:75-135)."""
