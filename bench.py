@@ -742,6 +742,21 @@ def main():
         torch.cuda.synchronize()
         print("kernel case decode_model_small: done")
         return
+    if args.kernel_case == "moe_decode":
+        # one Mixtral-shaped sparse block, 64 tokens: three forwards (launch lists)
+        from signrot_b200.transformers import kernel_utils as ku
+        dev = torch.device("cuda", 0)
+        with torch.device(dev):
+            model = ku.KernelDecoderModel(ku.DecoderConfig(num_hidden_layers=1, vocab_size=4096, num_local_experts=8))
+        model = model.to(dev).random_init_(0)
+        blk = model.layers[0].mlp
+        x = torch.randn((64, 1, 4096), device=dev).half()
+        with torch.no_grad():
+            for _ in range(3):
+                blk(x)
+        torch.cuda.synchronize()
+        print("kernel case moe_decode: done")
+        return
     if args.kernel_case == "decode_model":
         run_decode_model("decode_model_llama3_8b", {}, 8, 2048, 128, torch.device("cuda", 0))
         return

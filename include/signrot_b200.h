@@ -179,6 +179,25 @@ int sr_rotate_quant(const void *x, int dtype, int64_t rows, int64_t n, const voi
                     const void *sign, const void *expert_ids, int64_t heads, float clip_ratio, int asym, void *q,
                     void *q_scale, void *q_zero, void *rotated, void *stream);
 
+/* ------------------------------------------------------------------ MoE routing */
+
+/* Routing of a sparse block in one launch (signrot/nn/moe.py:159-190: softmax in fp32, top-k,
+ * optional renormalisation, cast, counting and the stable sort of the (token, choice) rows by
+ * expert).  logits fp16 [tokens, num_experts].  Outputs: weights fp16 [tokens, top_k]; chosen int32
+ * [tokens, top_k] (ties: the lower expert index); for the R = tokens * top_k routed rows in sorted
+ * order: tok int32 [R] (source token), eid int32 [R] (expert); inv int32 [R] (sorted position of row
+ * t * top_k + j); row_offsets int32 [num_experts + 1].  At most 512 experts and top-8. */
+int sr_moe_route(const void *logits, int64_t tokens, int64_t num_experts, int64_t top_k, int renormalize,
+                 void *weights, void *chosen, void *tok, void *eid, void *inv, void *row_offsets, void *stream);
+/* One copy of a token's packed codes (row_bytes per row, a multiple of 16), scale (fp16) and optional
+ * zero (int8) per routed row: q_out[r] = q[tok[r]] (moe.py:192-194). */
+int sr_moe_gather(const void *q, const void *scale, const void *zero, const void *tok, int64_t rows, int64_t row_bytes,
+                  void *q_out, void *scale_out, void *zero_out, void *stream);
+/* out[t] = sum_j rn_h(y[inv[t * top_k + j]] * weights[t, j]) over fp16 rows of `hidden` values, fp32
+ * sum, one fp16 rounding: the un-permute and weighted sum of moe.py:231-235. */
+int sr_moe_combine(const void *y, const void *weights, const void *inv, int64_t tokens, int64_t top_k, int64_t hidden,
+                   void *out, void *stream);
+
 /* ------------------------------------------------------------------ offline weight preparation */
 
 /* Per-channel symmetric int4 round-to-nearest of a weight matrix W [N, K] (dtype SR_F16, SR_BF16 or

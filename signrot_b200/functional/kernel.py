@@ -27,7 +27,7 @@ __all__ = [
     "kv_quant_pack", "rope_qk", "swiglu", "rmsnorm", "sym_dequant",
     "asym_quant_f16_si4", "asym_quant_f16_ui4", "sum_i4", "matmul_colrow_i8_i32",
     "w4a4_linear", "grouped_linear", "rotate_quant", "hadamard", "hadamard_heads",
-    "add_rmsnorm_quant", "w4a4_swiglu", "rtn_pack",
+    "add_rmsnorm_quant", "w4a4_swiglu", "rtn_pack", "moe_route", "moe_gather", "moe_combine",
 ]
 
 
@@ -499,6 +499,52 @@ def w4a4_swiglu(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum
     run(dev, "sr_w4a4_swiglu", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
         ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out))
     return out.view(*lead, N)
+
+
+def moe_route(router_logits, top_k, renormalize=True):
+    """Softmax (fp32), top-k, renormalisation and the sort of the routed rows by expert in one launch
+    (signrot/nn/moe.py:159-190).  router_logits fp16 [T, E].  Returns (weights fp16 [T, k],
+    chosen int32 [T, k], tok int32 [R], eid int32 [R], inv int32 [R], row_offsets int32 [E + 1])."""
+    if router_logits.dtype != torch.float16 or router_logits.dim() != 2:
+        raise RuntimeError("moe_route expects fp16 [tokens, experts] logits")
+    logits = router_logits.contiguous()
+    dev = require_cuda("moe_route", logits)
+    T, E = logits.shape
+    R = T * top_k
+    weights = torch.empty((T, top_k), dtype=torch.float16, device=dev)
+    chosen = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    tok = torch.empty((R,), dtype=torch.int32, device=dev)
+    eid = torch.empty((R,), dtype=torch.int32, device=dev)
+    inv = torch.empty((R,), dtype=torch.int32, device=dev)
+    row_off = torch.empty((E + 1,), dtype=torch.int32, device=dev)
+    run(dev, "sr_moe_route", ptr(logits), T, E, int(top_k), int(bool(renormalize)), ptr(weights), ptr(chosen),
+        ptr(tok), ptr(eid), ptr(inv), ptr(row_off))
+    return weights, chosen, tok, eid, inv, row_off
+
+
+def moe_gather(packed: PackedQuantizedTensor, tok):
+    """Per routed row a copy of its token's codes, scale and zero (moe.py:192-194)."""
+    q, s, z = packed.quantized_x.contiguous(), packed.scales_x.contiguous(), packed.zeros_x
+    if z is not None:
+        z = z.contiguous()
+    dev = require_cuda("moe_gather", q, s, z, tok)
+    R = tok.numel()
+    q_out = torch.empty((R, q.shape[-1]), dtype=torch.uint8, device=dev)
+    s_out = torch.empty((R, 1), dtype=torch.float16, device=dev)
+    z_out = torch.empty((R, 1), dtype=torch.int8, device=dev) if z is not None else None
+    run(dev, "sr_moe_gather", ptr(q), ptr(s), ptr(z), ptr(tok), R, q.shape[-1], ptr(q_out), ptr(s_out), ptr(z_out))
+    return PackedQuantizedTensor(q_out, s_out, z_out)
+
+
+def moe_combine(y, weights, inv):
+    """Un-permute and weighted sum of the expert outputs (moe.py:231-235): y fp16 [R, hidden] in
+    sorted row order, weights fp16 [T, k], inv int32 [T * k] -> fp16 [T, hidden]."""
+    y = y.contiguous()
+    dev = require_cuda("moe_combine", y, weights, inv)
+    T, k = weights.shape
+    out = torch.empty((T, y.shape[-1]), dtype=torch.float16, device=dev)
+    run(dev, "sr_moe_combine", ptr(y), ptr(weights), ptr(inv), T, k, y.shape[-1], ptr(out))
+    return out
 
 
 def rtn_pack(weight, sign=None, mse=False):

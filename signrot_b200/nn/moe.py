@@ -14,7 +14,9 @@ it is the equivalence check for the grouped path, bit-identical by construction.
 
 The grouped GEMM + dequant pair runs as ONE launch (`kernel.grouped_linear`): the library takes the
 weight-streaming mma.sync kernel when the routed rows average at most 16 per expert (decode) and
-the CTA-pair tcgen05 kernel otherwise.  The reference's two calls (`matmul_grouped` followed by
+the CTA-pair tcgen05 kernel otherwise.  With `fused_routing` (default, fp16, at most 512 experts,
+top-8) the softmax / top-k / sort-by-expert chain, the gathers and the final weighted un-permute
+are one launch each (`kernel.moe_route / moe_gather / moe_combine`).  The reference's two calls (`matmul_grouped` followed by
 `sym_dequant_moe`) remain for more than 512 experts.  All of them produce the same bits: the int32
 accumulators are exact either way and the dequant arithmetic is shared.
 """
@@ -30,8 +32,9 @@ class SignRotMoEBlock(torch.nn.Module):
     def __init__(self, gate, *, top_k, norm_topk_prob,
                  w_gate, s_gate, w_up, s_up, w_down, s_down,
                  sign_down=None, wsum_gate=None, wsum_up=None, wsum_down=None,
-                 asym=False, clip_ratio=1.0, fp32_had=False, use_grouped=True):
+                 asym=False, clip_ratio=1.0, fp32_had=False, use_grouped=True, fused_routing=True):
         super().__init__()
+        self.fused_routing = fused_routing
         self.gate = gate
         self.top_k = top_k
         self.norm_topk_prob = norm_topk_prob
@@ -132,11 +135,34 @@ class SignRotMoEBlock(torch.nn.Module):
 
     # ------------------------------------------------------------------ forward
 
+    def _forward_fused_routing(self, hidden_states):
+        """The grouped path with the routing glue as three launches (`moe_route`, `moe_gather`,
+        `moe_combine`) instead of the tensor-library chain below: ten launches per block."""
+        bsz, seq, hid = hidden_states.shape
+        x = hidden_states.reshape(-1, hid)
+        router_logits = self.gate(x)
+        weights, _, tok, eid, inv, row_off = kernel.moe_route(router_logits, self.top_k, self.norm_topk_prob)
+        q_tok, s_tok, z_tok = self._quantize(x)
+        routed = kernel.moe_gather(kernel.PackedQuantizedTensor(q_tok, s_tok, z_tok), tok)
+        gate_h = kernel.grouped_linear(routed, eid, row_off, self.w_gate, self.s_gate, self.wsum_gate)
+        up_h = kernel.grouped_linear(routed, eid, row_off, self.w_up, self.s_up, self.wsum_up)
+        inter = kernel.swiglu(gate_h, up_h)
+        pk = kernel.rotate_quant(inter, self.had_K, self.K, sign=self.sign_down,
+                                 expert_ids=eid if self.sign_down is not None else None,
+                                 clip_ratio=self.clip_ratio, asym=self.asym)
+        y = kernel.grouped_linear(pk, eid, row_off, self.w_down, self.s_down, self.wsum_down)
+        out = kernel.moe_combine(y, weights, inv)
+        return out.view(bsz, seq, hid), router_logits
+
     def forward(self, hidden_states: torch.Tensor):
         bsz, seq, hid = hidden_states.shape
         x = hidden_states.view(-1, hid)
         dt = x.dtype
         self._ensure_wsum()
+        if (self.fused_routing and self.use_grouped and not self.fp32_had and dt == torch.float16
+                and self.num_experts <= 512 and self.top_k <= 8 and hid % 8 == 0
+                and self.gate.weight.dtype == torch.float16):
+            return self._forward_fused_routing(hidden_states)
 
         router_logits = self.gate(x)
         probs = torch.softmax(router_logits, dim=1, dtype=torch.float)

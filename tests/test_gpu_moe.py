@@ -34,6 +34,7 @@ def _block(E, hidden, inter, top_k, seed, asym=False, use_grouped=True, sign=Tru
 @pytest.mark.parametrize("asym", [False, True])
 def test_grouped_equals_loop(E, hidden, inter, top_k, tokens, asym):
     blk = _block(E, hidden, inter, top_k, 1, asym=asym)
+    blk.fused_routing = False          # same routing arithmetic (the tensor library's) on both sides
     x = (torch.randn((2, tokens // 2, hidden), generator=torch.Generator().manual_seed(3))).half().to(DEV)
     y1, logits1 = blk(x)
     blk.use_grouped = False
@@ -126,3 +127,76 @@ def test_grouped_linear_bit_exact(counts, N, K, asym, which):
     _lib.call_nostream("sr_set_gemm_kernel", 0)
     assert _lib.device_status() == 0
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("T,E,k,renorm", [(64, 8, 2, True), (5, 4, 1, True), (300, 128, 8, True), (33, 16, 4, False),
+                                          (1, 8, 2, True), (2000, 8, 2, True)])
+def test_moe_route_matches_the_tensor_chain(T, E, k, renorm):
+    """One-launch routing against softmax / topk / stable argsort (signrot/nn/moe.py:159-190)."""
+    g = torch.Generator().manual_seed(T + E)
+    logits = torch.randn((T, E), generator=g).half().to(DEV)
+    w, chosen, tok, eid, inv, row_off = kernel.moe_route(logits, k, renorm)
+    probs = torch.softmax(logits, dim=1, dtype=torch.float)
+    pw, sel = torch.topk(probs, k, dim=-1)
+    if renorm:
+        pw = pw / pw.sum(dim=-1, keepdim=True)
+    # equal fp16 logits are common among 128 experts: the chosen experts may differ there, their
+    # probabilities may not
+    picked = probs.gather(1, chosen.long())
+    assert torch.equal(picked, torch.topk(probs, k, dim=-1)[0])
+    assert bool((chosen.long().sort(dim=1)[0].diff(dim=1) != 0).all()) or k == 1     # k distinct experts
+    ulp = pw.abs() * 2 ** -10 + 2 ** -24
+    assert bool(((w.float() - pw.half().float()).abs() <= ulp).all())
+    flat = chosen.long().reshape(-1)
+    perm = torch.argsort(flat, stable=True)
+    assert torch.equal(tok.long(), perm // k)
+    assert torch.equal(eid.long(), flat[perm])
+    assert torch.equal(inv.long(), torch.argsort(perm))
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(row_off.long(), torch.cat([counts.new_zeros(1), counts.cumsum(0)]))
+
+
+def test_moe_route_breaks_ties_by_index():
+    logits = torch.zeros((3, 8), dtype=torch.float16, device=DEV)
+    logits[1, 5] = 1.0
+    w, chosen, tok, eid, inv, row_off = kernel.moe_route(logits, 2, True)
+    assert chosen.tolist() == [[0, 1], [5, 0], [0, 1]]
+    assert row_off.tolist() == [0, 3, 5, 5, 5, 5, 6, 6, 6]
+
+
+@pytest.mark.parametrize("asym", [False, True])
+def test_moe_gather_and_combine(asym):
+    T, k, hid = 37, 2, 512
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((T, hid), generator=g).half().to(DEV)
+    if asym:
+        q, s, z = kernel.asym_quant_dynamic(x)
+        packed = kernel.PackedQuantizedTensor(q, s, z.to(torch.int8))
+    else:
+        q, s = kernel.sym_quant_dynamic(x)
+        packed = kernel.PackedQuantizedTensor(q, s)
+    logits = torch.randn((T, 8), generator=g).half().to(DEV)
+    w, chosen, tok, eid, inv, row_off = kernel.moe_route(logits, k, True)
+    routed = kernel.moe_gather(packed, tok)
+    assert torch.equal(routed.quantized_x, packed.quantized_x[tok.long()])
+    assert torch.equal(routed.scales_x, packed.scales_x[tok.long()])
+    assert (routed.zeros_x is None) == (not asym)
+    if asym:
+        assert torch.equal(routed.zeros_x, packed.zeros_x[tok.long()])
+    y = torch.randn((T * k, hid), generator=g).half().to(DEV)
+    got = kernel.moe_combine(y, w, inv)
+    want = (y[inv.long()].view(T, k, hid) * w.unsqueeze(-1)).sum(dim=1)
+    assert torch.equal(got, want)                          # two addends: one rounding either way
+
+
+@pytest.mark.parametrize("E,hidden,inter,top_k,tokens", [(16, 256, 192, 4, 40), (8, 512, 768, 2, 64)])
+@pytest.mark.parametrize("asym", [False, True])
+def test_fused_routing_block_equals_tensor_chain_block(E, hidden, inter, top_k, tokens, asym):
+    blk = _block(E, hidden, inter, top_k, 6, asym=asym)
+    x = (torch.randn((1, tokens, hidden), generator=torch.Generator().manual_seed(8))).half().to(DEV)
+    y1, l1 = blk(x)
+    blk.fused_routing = False
+    y2, l2 = blk(x)
+    assert torch.equal(l1, l2)
+    # routing weights may differ by one fp16 ulp (softmax summation order); everything else is the same
+    assert rel_l2(y1.cpu(), y2.cpu()) <= 1e-3
