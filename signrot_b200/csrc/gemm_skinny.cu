@@ -18,6 +18,7 @@
 // 0xF0F0F0F0 for the odd ones), which reorders k inside a word in the same way for both operands,
 // so the dot product is unchanged; every product carries a factor 256 that the epilogue removes
 // with an exact shift.  The eight partial accumulators of a block meet in shared memory.
+#include <cstdlib>
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -72,7 +73,10 @@ struct SkItem {
 // a block is 16 gate rows plus the 16 up rows of the same columns, and the epilogue writes
 // rn_h(silu(gate) * up) as [M, N] (the arithmetic of swiglu_kernel on the two dequantized fp16 values), so
 // the two projections and the activation of a SwiGLU MLP are one launch.
-template <int NT, int MT, bool A_UNSIGNED, bool GROUPED, bool SWIGLU = false>
+// KW = warps that split the K steps of one row block (8: the whole CTA works on one block; 2: four groups
+// of two warps work on four blocks, so the per-block reduction and epilogue are paid once per 16 steps
+// of a K = 4096 row instead of once per 4).
+template <int NT, int MT, bool A_UNSIGNED, bool GROUPED, bool SWIGLU = false, int KW = SK_WARPS>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B, uint32_t M, uint32_t N, uint32_t K,
                    const int32_t *__restrict__ row_off, int num_experts, Epilogue ep) {
@@ -90,15 +94,22 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     if (GROUPED) pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
+    constexpr int GROUPS = SK_WARPS / KW;
+    const int grp = warp / KW, kw = warp % KW, gtid = tid - grp * KW * 32;
+    auto group_sync = [&]() {
+        if (KW == SK_WARPS) __syncthreads();
+        else asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(KW * 32) : "memory");
+    };
     // ring[warp][stage][row slot 0 .. 2 MT - 1][lane] (16 bytes each)
     const uint4 *ring = reinterpret_cast<const uint4 *>(sk_smem + (size_t)warp * SK_RING_BYTES) + lane;
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
-    int *red = reinterpret_cast<int *>(sk_smem + (size_t)SK_WARPS * SK_RING_BYTES);
+    int *red = reinterpret_cast<int *>(sk_smem + (size_t)SK_WARPS * SK_RING_BYTES) +
+               (size_t)grp * RED_BUFS * KW * MT * NT * 128;
 
     const uint32_t kp = K >> 1;                         // packed bytes per row
     const uint32_t steps = (kp + SK_STEP - 1) / SK_STEP;
     const uint32_t blocks = (N + ROWS - 1) / ROWS;
-    const bool has_steps = (uint32_t)warp < steps;
+    const bool has_steps = (uint32_t)kw < steps;
 
     uint32_t total_items = blocks;
     if (GROUPED) {
@@ -138,14 +149,15 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     };
 
     // queue of (item, step) of this warp, in the order they are consumed
-    uint32_t iss_item = blockIdx.x, iss_step = warp;
+    const uint32_t first_item = blockIdx.x * GROUPS + grp, item_stride = gridDim.x * GROUPS;
+    uint32_t iss_item = first_item, iss_step = kw;
     uint32_t iss_n0 = 0;
     const uint8_t *iss_ptr = B;
     auto iss_open = [&]() {
         if (iss_item < total_items) {
             const SkItem it = decode(iss_item);
             iss_n0 = it.n0;
-            iss_ptr = B + ((size_t)it.w_row + g) * kp + (size_t)warp * SK_STEP + 16 * q;
+            iss_ptr = B + ((size_t)it.w_row + g) * kp + (size_t)kw * SK_STEP + 16 * q;
         }
     };
     iss_open();
@@ -161,11 +173,11 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 const bool ok = k_ok && iss_n0 + g + rr < N;
                 cp_async16(dst + r * 512, ok ? iss_ptr + ((size_t)rr + jump) * kp : B, ok ? 16u : 0u);
             }
-            iss_step += SK_WARPS;
-            iss_ptr += SK_WARPS * SK_STEP;
+            iss_step += KW;
+            iss_ptr += KW * SK_STEP;
             if (iss_step >= steps) {
-                iss_step = warp;
-                iss_item += gridDim.x;
+                iss_step = kw;
+                iss_item += item_stride;
                 iss_open();
             }
         }
@@ -184,16 +196,16 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
             x[t] = k_ok && it.x_row0 + g + 8 * t < it.x_end ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * kp))
                                                            : make_uint4(0, 0, 0, 0);
     };
-    uint32_t item = blockIdx.x;
+    uint32_t item = first_item;
     SkItem cur = decode(item < total_items ? item : 0u);
     uint4 xn[NT];
-    if (has_steps && item < total_items) load_x(cur, warp, xn);
+    if (has_steps && item < total_items) load_x(cur, kw, xn);
 
     int slot = 0;
     uint32_t parity = 0;
-    for (; item < total_items; item += gridDim.x, parity ^= (RED_BUFS - 1)) {
-        const bool more = item + gridDim.x < total_items;
-        const SkItem nxt = decode(more ? item + gridDim.x : item);
+    for (; item < total_items; item += item_stride, parity ^= (RED_BUFS - 1)) {
+        const bool more = item + item_stride < total_items;
+        const SkItem nxt = decode(more ? item + item_stride : item);
         int acc[MT][NT][4];
 #pragma unroll
         for (int m = 0; m < MT; ++m)
@@ -203,12 +215,12 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 for (int i = 0; i < 4; ++i) acc[m][t][i] = 0;
         if (has_steps) {
 #pragma unroll 1
-            for (uint32_t s = warp; s < steps; s += SK_WARPS) {
+            for (uint32_t s = kw; s < steps; s += KW) {
                 uint4 x[NT];
 #pragma unroll
                 for (int t = 0; t < NT; ++t) x[t] = xn[t];
-                if (s + SK_WARPS < steps) load_x(cur, s + SK_WARPS, xn);
-                else if (more) load_x(nxt, warp, xn);
+                if (s + KW < steps) load_x(cur, s + KW, xn);
+                else if (more) load_x(nxt, kw, xn);
                 asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
                 uint4 w[2 * MT];
 #pragma unroll
@@ -238,23 +250,23 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 slot = slot + 1 == DEPTH ? 0 : slot + 1;
             }
         }
-        if (RED_BUFS == 1) __syncthreads();   // the previous block's sums have been read
-        int *rb = red + (size_t)parity * SK_WARPS * MT * NT * 128;
+        if (RED_BUFS == 1) group_sync();   // the previous block's sums have been read
+        int *rb = red + (size_t)parity * KW * MT * NT * 128;
 #pragma unroll
         for (int m = 0; m < MT; ++m)
 #pragma unroll
             for (int t = 0; t < NT; ++t)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) rb[(((warp * MT + m) * NT + t) * 4 + i) * 32 + lane] = acc[m][t][i];
-        __syncthreads();
+                for (int i = 0; i < 4; ++i) rb[(((kw * MT + m) * NT + t) * 4 + i) * 32 + lane] = acc[m][t][i];
+        group_sync();
         // fragment slot i of lane (g, q) in m-tile m: weight row 16 m + g + 8 * (i >> 1), token 2 * q + (i & 1) of its
         // block.  With two buffers the one written two blocks later is this one: the barrier in between orders it.
         if (SWIGLU) {
-            for (int idx = tid; idx < NT * 128; idx += SK_WARPS * 32) {
+            for (int idx = gtid; idx < NT * 128; idx += KW * 32) {
                 const int l = idx & 31, i = (idx >> 5) & 3, t = idx >> 7;
                 int sg = 0, su = 0;
 #pragma unroll
-                for (int w = 0; w < SK_WARPS; ++w) {
+                for (int w = 0; w < KW; ++w) {
                     sg += rb[(((w * MT + 0) * NT + t) * 4 + i) * 32 + l];
                     su += rb[(((w * MT + 1) * NT + t) * 4 + i) * 32 + l];
                 }
@@ -268,11 +280,11 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 }
             }
         } else
-        for (int idx = tid; idx < MT * NT * 128; idx += SK_WARPS * 32) {
+        for (int idx = gtid; idx < MT * NT * 128; idx += KW * 32) {
             const int l = idx & 31, i = (idx >> 5) & 3, t = (idx >> 7) % NT, m = idx / (NT * 128);
             int sum = 0;
 #pragma unroll
-            for (int w = 0; w < SK_WARPS; ++w) sum += rb[(((w * MT + m) * NT + t) * 4 + i) * 32 + l];
+            for (int w = 0; w < KW; ++w) sum += rb[(((w * MT + m) * NT + t) * 4 + i) * 32 + l];
             const uint32_t n = cur.n0 + 16 * m + (l >> 2) + 8 * (i >> 1);
             const uint32_t mm = cur.x_row0 + 8 * t + 2 * (l & 3) + (i & 1);
             if (n < N && mm < cur.x_end) ep.store(mm, n, sum >> 8, N);
@@ -283,6 +295,21 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
 }
 
 }  // namespace
+
+// Warps that share one row block.  Two (four blocks in flight per CTA) pays when there are enough blocks to
+// occupy every warp group of the grid and K is short, so that the per-block reduction and epilogue
+// would otherwise weigh as much as the block's own steps; eight otherwise.
+static int skinny_kw(int64_t blocks, int64_t K, int sm_count, bool grouped = false) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *e = getenv("SIGNROT_B200_SKINNY_KW");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced == 2 || forced == 8) return forced;
+    // measured: dense launches lose with two (too few blocks for four groups per CTA); the MoE gate/up shape
+    // (8 experts x 14336 rows, K = 4096) gains 5 %
+    return grouped && K <= 8192 && blocks >= 8ll * sm_count ? 2 : 8;
+}
 
 static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                          const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
@@ -301,19 +328,28 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     // two m-tiles per warp step when there are enough row blocks to keep every SM busy and the sums fit
     const int mt = (nt <= 4 && (N >= 8192 || (N >= 4096 && nt >= 2))) ? 2 : 1;   // measured crossover
     const int64_t blocks = cdiv<int64_t>(N, SK_ROWS * mt) * (grouped ? num_experts : 1);
-    // two CTAs per SM; the row blocks are dealt round-robin, so shrink the grid to even the deal out
+    // warps per row block: SIGNROT_B200_SKINNY_KW = 2 | 8 pins it (A/B runs); see skinny_kw()
+    const int kw = skinny_kw(blocks, K, sm_count, grouped);
+    const int groups = SK_WARPS / kw;
+    // two CTAs per SM; the row blocks are dealt round-robin to the warp groups, so shrink the grid to even the deal out
     int64_t ctas = 2 * (int64_t)sm_count;
-    if (blocks < ctas) ctas = blocks;
-    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas));
+    if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
+    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
-#define SR_SK(NT, MT, GR)                                                                                      \
+#define SR_SK_KW(NT, MT, GR, KWV)                                                                              \
     do {                                                                                                       \
-        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, MT, true, GR> : gemm_skinny_kernel<NT, MT, false, GR>;  \
+        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, MT, true, GR, false, KWV>                               \
+                              : gemm_skinny_kernel<NT, MT, false, GR, false, KWV>;                             \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                              (int)skinny_smem(NT, MT));                                        \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         launch_pdl(kfn, dim3(grid), dim3(SK_WARPS * 32), skinny_smem(NT, MT), st, A, B, (uint32_t)M, (uint32_t)N,   \
                    (uint32_t)K, row_off, num_experts, ep);                                                     \
+    } while (0)
+#define SR_SK(NT, MT, GR)                                                                                      \
+    do {                                                                                                       \
+        if (kw == 2) SR_SK_KW(NT, MT, GR, 2);                                                                  \
+        else SR_SK_KW(NT, MT, GR, 8);                                                                          \
     } while (0)
     if (grouped) {
         if (mt == 2) SR_SK(4, 2, true);
@@ -326,8 +362,9 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
         if (nt == 1) SR_SK(1, 1, false);
         else if (nt == 2) SR_SK(2, 1, false);
         else if (nt == 4) SR_SK(4, 1, false);
-        else SR_SK(8, 1, false);
+        else SR_SK_KW(8, 1, false, 8);
     }
+#undef SR_SK_KW
 #undef SR_SK
     return check_launch("gemm_skinny");
 }
@@ -348,23 +385,32 @@ int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int
     }
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     const int64_t blocks = cdiv<int64_t>(N, SK_ROWS);
+    const int kw = skinny_kw(blocks, K, sm_count);
+    const int groups = SK_WARPS / kw;
     int64_t ctas = 2 * (int64_t)sm_count;
-    if (blocks < ctas) ctas = blocks;
-    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas));
+    if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
+    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
-#define SR_SKS(NT)                                                                                             \
+#define SR_SKS_KW(NT, KWV)                                                                                     \
     do {                                                                                                       \
-        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, 2, true, false, true> : gemm_skinny_kernel<NT, 2, false, false, true>; \
+        auto kfn = a_unsigned ? gemm_skinny_kernel<NT, 2, true, false, true, KWV>                              \
+                              : gemm_skinny_kernel<NT, 2, false, false, true, KWV>;                            \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                              (int)skinny_smem(NT, 2));                                         \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "w4a4_swiglu: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); \
         launch_pdl(kfn, dim3(grid), dim3(SK_WARPS * 32), skinny_smem(NT, 2), st, A, B, (uint32_t)M, (uint32_t)N,    \
                    (uint32_t)K, (const int32_t *)nullptr, 0, ep);                                              \
     } while (0)
+#define SR_SKS(NT)                                                                                             \
+    do {                                                                                                       \
+        if (kw == 2) SR_SKS_KW(NT, 2);                                                                         \
+        else SR_SKS_KW(NT, 8);                                                                                 \
+    } while (0)
     if (nt == 1) SR_SKS(1);
     else if (nt == 2) SR_SKS(2);
     else SR_SKS(4);
 #undef SR_SKS
+#undef SR_SKS_KW
     return check_launch("gemm_skinny_swiglu");
 }
 
