@@ -207,6 +207,11 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t *mt_start = reinterpret_cast<uint32_t *>(base_ptr + off_pk_b + SP * PK_B + BAR_BYTES);
     uint8_t *epi_stage = base_ptr + off_pk_b + SP * PK_B + BAR_BYTES + SCHED_BYTES;
 
+    // Launched with programmatic serialization (launch_pdl): barrier set-up and the TMEM allocation below overlap
+    // the tail of the kernel before this one; only the TMA producer and the epilogue warps touch memory that an
+    // earlier kernel may have written (grouped launches also read the row offsets right here).
+    pdl_trigger();
+    if (grouped) pdl_wait();
     if (tid == 0) {
         if (grouped) {
             uint32_t acc = 0;
@@ -287,6 +292,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (own rows only)
             if (lane == 0) {
+                if (!grouped) pdl_wait();
                 Ring pr;
                 bool ok = true;
                 for (uint32_t item = cluster; item < num_items && ok; item += clusters) {
@@ -339,6 +345,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t quarter = warp & 3;
             uint32_t it = 0;
             bool ok = true;
+            if (!grouped) pdl_wait();
             for (uint32_t item = cluster; item < num_items && ok; item += clusters, ++it) {
                 const uint32_t buf = it & 1;
                 const TileCoord tc = coord(item);
@@ -548,8 +555,8 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     else kfn = a_unsigned ? gemm_tc3_kernel<true, 4> : gemm_tc3_kernel<false, 4>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<(unsigned)(2 * clusters), THREADS, smem_bytes(sp, su), st>>>(ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, sp,
-                                                                        su, row_off, num_experts, ep);
+    launch_pdl(kfn, dim3((unsigned)(2 * clusters)), dim3(THREADS), smem_bytes(sp, su), st, ma, mb, (uint32_t)M, (uint32_t)N,
+               (uint32_t)K, sp, su, row_off, num_experts, ep);
     return check_launch("gemm_tc3");
 }
 

@@ -103,6 +103,7 @@ rotate_quant_4096_tc_kernel(const InT *__restrict__ x, const int8_t *__restrict_
     extern __shared__ __align__(16) uint8_t tc_smem[];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_trigger();   // launched with programmatic serialization (launch_pdl): the sign table is a weight
     const int pair = warp >> 1, half = warp & 1;
     const int g = lane >> 2, qd = lane & 3;
     uint32_t *sgn_all = reinterpret_cast<uint32_t *>(tc_smem + (size_t)TC_PAIRS * 2 * TC_ROW_BYTES);
@@ -156,6 +157,7 @@ rotate_quant_4096_tc_kernel(const InT *__restrict__ x, const int8_t *__restrict_
         }
     };
 
+    pdl_wait();      // x comes from the kernel before this one
     uint32_t row = row_begin + pair;
     int which = 0;
     if (row < row_end) fetch(row, 0);
@@ -404,8 +406,8 @@ int launch_rotate_tc4096(const RotateArgs &a, cudaStream_t st) {
         auto kfn = rotate_quant_4096_tc_kernel<T, ASYM>;                                                        \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);   \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));              \
-        kfn<<<grid, TC_WARPS * 32, TC_SMEM, st>>>((const T *)a.x, a.sign, a.rows, a.clip, a.q, a.q_scale,       \
-                                                  a.q_zero, (__half *)a.out);                                   \
+        launch_pdl(kfn, dim3(grid), dim3(TC_WARPS * 32), (size_t)TC_SMEM, st, (const T *)a.x, a.sign, a.rows, a.clip, \
+                   a.q, a.q_scale, a.q_zero, (__half *)a.out);                                                 \
     } while (0)
     if (a.in_dtype == SR_F16) {
         if (a.asym) SR_RQ(__half, true);
