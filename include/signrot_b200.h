@@ -287,6 +287,17 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
                        const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
                        int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
                        int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream);
+/* The same call with the split-KV merge folded into the attention kernel: the CTA of a
+ * (request, KV head) that finishes last combines the chunks (same arithmetic, same chunk order as the
+ * separate merge pass: identical output).  counters int32 [batch * num_kv_heads] must be zero before
+ * the first call; the kernel leaves them zero, so the buffer is reused across calls, layers and
+ * CUDA-graph replays on one stream.  Page sizes the tensor-core kernel does not take fall back to
+ * the two-launch form. */
+int sr_batch_decode_i4_merged(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                              const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                              int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                              int64_t head_dim, int64_t batch_size, void *tmp, int64_t num_chunks, void *counters,
+                              int hadamard_q, void *stream);
 
 /* sr_batch_decode_i4 for callers that cannot hand over a workspace.  It has no counterpart in
  * the reference.  Some hosts of this library never get to call cudaMalloc: an inference

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "sr_kv_append_quant": [_P] * 7 + [_I64] * 7 + [_I, _P],
     "sr_rope_kv_append": [_P] * 8 + [_I64] * 3 + [_P, _P, _I64, _P, _P] + [_I64] * 8 + [_I, _P],
     "sr_batch_decode_i4": [_P] * 7 + [_I64] * 7 + [_P, _I64, _I, _P],
+    "sr_batch_decode_i4_merged": [_P] * 7 + [_I64] * 7 + [_P, _I64, _P, _I, _P],
     "sr_batch_decode_i4_static": [_P] * 7 + [_I64] * 7 + [_I64, _I, _P],
 }
 

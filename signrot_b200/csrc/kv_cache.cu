@@ -582,10 +582,11 @@ int sr_rope_kv_append(void *kv_data, void *kv_param, const void *kv_indptr, cons
     return check_launch("rope_kv_append");
 }
 
-int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
-                       const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
-                       int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
-                       int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream) {
+static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                             const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
+                             int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                             int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream,
+                             int32_t *counters) {
     SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "batch_decode_i4: CHECK_EQ(head_dim, 128) failed. %lld vs 128", (long long)head_dim);
     if (batch_size == 0) return SR_OK;
     PagedKV kv;
@@ -613,7 +614,7 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
         const char *e = getenv("SIGNROT_B200_DECODE");
         use_tc = (e && !strcmp(e, "scalar")) ? 0 : 1;
     }
-    const bool took = use_tc && launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st);
+    const bool took = use_tc && launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
     if (!took) switch (G) {
         case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
@@ -622,12 +623,33 @@ int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, co
     }
     rc = check_launch("batch_decode_i4");
     if (rc) return rc;
-    if (num_chunks > 1) {
+    if (num_chunks > 1 && !(took && counters)) {   // the tensor-core kernel merges by itself when it has counters
         dim3 mgrid((unsigned)batch_size, (unsigned)num_qo_heads);
         launch_pdl(decode_merge_kernel, mgrid, dim3(128), 0, st, (const float *)tp, op, nc);
         rc = check_launch("batch_decode_i4 (merge)");
     }
     return rc;
+}
+
+int sr_batch_decode_i4(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                       const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
+                       int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                       int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream) {
+    return batch_decode_impl(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                             num_qo_heads, num_kv_heads, page_size, head_dim, batch_size, tmp, num_chunks, hadamard_q,
+                             stream, nullptr);
+}
+
+int sr_batch_decode_i4_merged(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,
+                              const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                              int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
+                              int64_t head_dim, int64_t batch_size, void *tmp, int64_t num_chunks, void *counters,
+                              int hadamard_q, void *stream) {
+    SR_REQUIRE(counters != nullptr || num_chunks <= 1 || tmp == nullptr, SR_ERR_INVALID,
+               "batch_decode_i4_merged: the arrival counters are missing");
+    return batch_decode_impl(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                             num_qo_heads, num_kv_heads, page_size, head_dim, batch_size, tmp, num_chunks, hadamard_q,
+                             stream, (int32_t *)counters);
 }
 
 // ------------------------------------------------------------------ decode without a caller workspace

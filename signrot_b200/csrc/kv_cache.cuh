@@ -34,6 +34,6 @@ __device__ __forceinline__ float ex2(float x) {
 // Tensor-core decode kernel (kv_decode_tc.cu): same arguments and workspace format as decode_kernel.
 // Returns false when the geometry is not one it handles (page_size % 16 != 0).
 bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
-                      int had_q, float had_scale, cudaStream_t st);
+                      int had_q, float had_scale, cudaStream_t st, int32_t *counters = nullptr);
 
 }  // namespace sr

@@ -57,7 +57,7 @@ __device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
 template <int G>
 __global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
-                 uint32_t num_chunks, int had_q, float had_scale) {
+                 uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters) {
     pdl_trigger();   // launched with programmatic serialization (launch_pdl); everything read here is produced upstream
     pdl_wait();
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
@@ -349,19 +349,50 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
             }
         }
     }
+    // ---- merge across chunks by whichever CTA of this (request, KV head) finishes last: the arithmetic and the
+    // chunk order of decode_merge_kernel, without its launch.  counters[b * kv_heads + hk] starts at zero and is
+    // put back to zero by the CTA that merges, so the buffer needs no reset between calls (or graph replays).
+    if (counters != nullptr && num_chunks > 1) {
+        __shared__ int is_last;
+        __threadfence();      // this CTA's partial state is visible device-wide before its arrival is counted
+        __syncthreads();
+        if (tid == 0) {
+            int32_t *cnt = counters + (size_t)b * gridDim.y + hk;
+            const int prev = atomicAdd(cnt, 1);
+            is_last = prev == (int)num_chunks - 1;
+            if (is_last) *cnt = 0;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int gg = 0; gg < G; ++gg) {
+                const uint32_t hq = hk * G + gg;
+                const float *src = tmp + ((size_t)b * hq_total + hq) * num_chunks * (HD + 4);
+                float mm = -5e4f;
+                for (uint32_t c = 0; c < num_chunks; ++c) mm = fmaxf(mm, __ldcg(src + c * (HD + 4) + HD));
+                float dd = 0.f, oo = 0.f;
+                for (uint32_t c = 0; c < num_chunks; ++c) {
+                    const float sc = ex2(__ldcg(src + c * (HD + 4) + HD) - mm);
+                    dd += __ldcg(src + c * (HD + 4) + HD + 1) * sc;
+                    oo += __ldcg(src + c * (HD + 4) + tid) * sc;
+                }
+                o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+            }
+        }
+    }
 }
 
 }  // namespace
 
 bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
-                      int had_q, float had_scale, cudaStream_t st) {
+                      int had_q, float had_scale, cudaStream_t st, int32_t *counters) {
     if (kv.page_size % DT_BLOCK != 0) return false;
 #define SR_DT(GG)                                                                                              \
     do {                                                                                                       \
         auto kfn = decode_tc_kernel<GG>;                                                                       \
         if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
             return false;                                                                                      \
-        launch_pdl(kfn, grid, dim3(DT_WARPS * 32), (size_t)DT_RING_BYTES, st, q, kv, o, tmp, num_chunks, had_q, had_scale); \
+        launch_pdl(kfn, grid, dim3(DT_WARPS * 32), (size_t)DT_RING_BYTES, st, q, kv, o, tmp, num_chunks, had_q, had_scale, counters); \
     } while (0)
     switch (G) {
         case 1: SR_DT(1); break;

@@ -126,10 +126,12 @@ def append_kv_i4(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, k, 
 
 
 def batch_decode_i4(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, layer_idx, tmp=None,
-                    num_chunks=1, hadamard_q=False):
+                    num_chunks=1, hadamard_q=False, counters=None):
     """Decode attention of one new token per request over the int4 cache (kv_cache.py:101-107).
-    o, q: fp16 [batch, q_heads, 128]; q_heads may be a multiple of the cache's head count."""
-    dev = require_cuda("batch_decode_i4", o, q, kv_data, kv_indptr, kv_indices, last_page_offset, tmp)
+    o, q: fp16 [batch, q_heads, 128]; q_heads may be a multiple of the cache's head count.
+    `counters` (int32 [batch * kv_heads], zero): the split-KV merge runs inside the attention kernel
+    instead of as a second launch; the kernel leaves the counters zero."""
+    dev = require_cuda("batch_decode_i4", o, q, kv_data, kv_indptr, kv_indices, last_page_offset, tmp, counters)
     if o.dim() != 3 or q.dim() != 3 or o.shape != q.shape:
         raise RuntimeError("o and q must be [B, N, D] tensors of the same shape")
     if kv_data.dtype != torch.uint8 or kv_param.dtype != torch.float16:
@@ -143,6 +145,13 @@ def batch_decode_i4(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_of
             raise RuntimeError("tmp must be fp32 [batch, heads, chunks, head_dim + 4]")
     else:
         tmp, num_chunks = None, 1
+    if counters is not None and num_chunks > 1:
+        if counters.dtype != torch.int32 or counters.numel() < batch * H:
+            raise RuntimeError("counters must be int32 [batch * kv_heads]")
+        run(dev, "sr_batch_decode_i4_merged", ptr(o), ptr(q), ptr(kv_data), ptr(kv_param), ptr(kv_indptr),
+            ptr(kv_indices), ptr(last_page_offset), L, int(layer_idx), hq, H, P, D, batch, ptr(tmp), int(num_chunks),
+            ptr(counters), int(bool(hadamard_q)))
+        return
     run(dev, "sr_batch_decode_i4", ptr(o), ptr(q), ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices),
         ptr(last_page_offset), L, int(layer_idx), hq, H, P, D, batch, ptr(tmp), int(num_chunks), int(bool(hadamard_q)))
 
@@ -207,6 +216,7 @@ class _AttentionStub:
         self.hadamard_dtype = hadamard_dtype
         self.num_chunks = 1
         self.tmp = None
+        self.counters = None     # arrival counters of the in-kernel split-KV merge (zero between calls)
 
     def forward(self, q, num_kv_heads, attention_kwargs, layer_idx):
         bsz, q_len, hq, hd = q.shape
@@ -218,7 +228,7 @@ class _AttentionStub:
         out = torch.empty_like(q)
         # the Hadamard on q (kv_cache.py:157-158) is applied inside the decode kernel
         batch_decode_i4(out, q, **attention_kwargs, layer_idx=layer_idx, tmp=self.tmp, num_chunks=self.num_chunks,
-                        hadamard_q=self.hadamard_dtype is not None)
+                        hadamard_q=self.hadamard_dtype is not None, counters=self.counters)
         return out.unsqueeze(1)
 
 
@@ -274,6 +284,12 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
         if chunks > 1:
             self._stub.tmp = torch.empty((self.batch_size, self.num_heads * self.group_size, chunks,
                                           self.head_dim + 4), dtype=torch.float32, device=self.device)
+            # measured on B200 (batch 8, context 2100, 5 chunks): the in-kernel merge costs 5 us per layer
+            # more than the separate merge launch (one CTA merges four heads one after the other behind
+            # device-wide fences), so it is opt-in
+            if os.environ.get("SIGNROT_B200_DECODE_MERGE", "separate") == "fused":
+                self._stub.counters = torch.zeros(self.batch_size * self.num_heads, dtype=torch.int32,
+                                                  device=self.device)
 
     def page_cnt_from_length(self, length):
         return (length + self.page_size - 1) // self.page_size

@@ -169,3 +169,24 @@ def test_rope_kv_append_equals_rope_then_append(T, start, fused_input):
         for bb in range(B):
             pg, e = (pos // page) * B + bb, pos % page
             assert torch.equal(pa[pg, :, :, e], pb[pg, :, :, e]) and torch.equal(sa[pg, :, :, e], sb[pg, :, :, e])
+
+
+@pytest.mark.parametrize("T,page,Hq,Hkv,chunks", [(513, 128, 32, 8, 3), (1000, 16, 8, 2, 7), (300, 32, 4, 4, 2)])
+def test_in_kernel_merge_equals_merge_pass(T, page, Hq, Hkv, chunks):
+    """Split-KV merge by the last CTA of each (request, KV head) against the separate merge launch:
+    same bits, and the arrival counters are back at zero after every call."""
+    B, L = 3, 1
+    k, v, ref, pages = _fill(B, L, Hkv, page, T, T + 1)
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, L, Hkv, 128, group_size=Hq // Hkv)
+    cache.update(k.to(DEV), v.to(DEV), 0)
+    specs = cache.refresh_specs()
+    g = torch.Generator().manual_seed(3)
+    tmp = torch.empty((B, Hq, chunks, 132), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        q = torch.randn((B, Hq, 128), generator=g).half().to(DEV)
+        a, b = torch.empty_like(q), torch.empty_like(q)
+        kvc.batch_decode_i4(a, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks, hadamard_q=True)
+        kvc.batch_decode_i4(b, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks, hadamard_q=True, counters=counters)
+        assert torch.equal(a, b)
+        assert int(counters.abs().sum()) == 0
