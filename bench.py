@@ -144,13 +144,13 @@ def make_cpu_cases(rows: int):
     return cases
 
 
-def cpu_baseline(budget_s: float = 12.0, rows: int = 256):
+def cpu_baseline(time_limit_s: float = 12.0, rows: int = 256):
     threads = os.cpu_count() or 1
     cases = make_cpu_cases(rows)
     cpu_fake_quant_step(min(rows, 32), cases, threads)  # warm-up
     times = []
     t_start = time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_start < budget_s and len(times) < 20):
+    while len(times) < 3 or (time.perf_counter() - t_start < time_limit_s and len(times) < 20):
         times.append(cpu_fake_quant_step(rows, cases, threads))
     best = sorted(times)[len(times) // 2]
     return {"value": round(ops_per_step(rows) / best / 1e12, 4), "unit": "TOP/s", "cores": threads, "kind": "port",

@@ -21,7 +21,7 @@
 // same even/odd nibble order inside a 32-bit word, so the permutation of k inside a
 // word cancels in the dot product.
 //
-// Every mbarrier wait is bounded by a cycle budget; on expiry the CTA raises the
+// Every mbarrier wait is bounded by a cycle limit; on expiry the CTA raises the
 // abort flag, the other roles leave their loops, TMEM is released and the device
 // status word records the failure (read with sr_device_status()).
 #include "common.cuh"
@@ -80,7 +80,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when the budget ran out or another role aborted.
+// Bounded wait.  Returns false when the limit was reached or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();

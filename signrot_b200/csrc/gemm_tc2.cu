@@ -17,7 +17,7 @@
 //   warps 1..4   epilogue: tcgen05.ld of the finished accumulator while the next tile's MMAs
 //                run into the other one; exact shift by 8, dequant, fp16/int32 stores
 //   warps 5..    unpack (512 threads by default: three 16-byte packed chunks each per k-block)
-// Every mbarrier wait is bounded by a cycle budget (abort flag + device status word).
+// Every mbarrier wait is bounded by a cycle limit (abort flag + device status word).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cstdlib>

@@ -19,7 +19,7 @@
 //               so the next tile's MMAs overlap the epilogue)
 //   warps 6..13 unpack: packed nibble n -> int8 byte 16*n in the 128-byte-swizzled K-major layout
 // Cross-CTA signalling uses mbarrier arrives on the leader's barriers through mapa addresses.
-// Every wait is bounded by a cycle budget; on expiry the CTA aborts, both CTAs fall through to
+// Every wait is bounded by a cycle limit; on expiry the CTA aborts, both CTAs fall through to
 // the cluster barrier at the end, TMEM is released and the device status word records the code.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"

@@ -357,12 +357,12 @@ rotate_quant_4096_tc_kernel(const InT *__restrict__ x, const int8_t *__restrict_
                     w[1] ^= 0x88888888u;
                 }
                 // lane qd holds bytes 4 * nt + qd (nt = 0..7) of the 32-byte line; gather bytes 8 qd .. 8 qd + 7
-                // round 1 (partner qd ^ 2): lanes 0,1 collect the words of nt 0..3, lanes 2,3 those of nt 4..7
+                // exchange 1 (partner qd ^ 2): lanes 0,1 collect the words of nt 0..3, lanes 2,3 those of nt 4..7
                 const bool upper = (qd & 2) != 0;
                 const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? w[0] : w[1], 2);
                 const uint32_t wa = upper ? got : w[0];    // from lane (qd & 1)
                 const uint32_t wb = upper ? w[1] : got;    // from lane (qd & 1) + 2
-                // round 2 (partner qd ^ 1): even lanes need bytes 0,1 of all four source lanes, odd lanes bytes 2,3
+                // exchange 2 (partner qd ^ 1): even lanes need bytes 0,1 of all four source lanes, odd lanes bytes 2,3
                 const bool odd = (qd & 1) != 0;
                 const uint32_t keep = odd ? __byte_perm(wa, wb, 0x7632) : __byte_perm(wa, wb, 0x5410);
                 const uint32_t give = odd ? __byte_perm(wa, wb, 0x5410) : __byte_perm(wa, wb, 0x7632);
