@@ -585,3 +585,78 @@ def generate(model, input_ids, max_new_tokens, page_size=None, use_graph=True):
         token = logits[:, -1:].argmax(-1)
         out.append(token)
     return torch.cat(out, dim=1)
+
+
+# ----------------------------------------------------------------------------- tensor parallelism
+
+class TPRowLinear(torch.nn.Module):
+    """o_proj / down_proj of a tensor-parallel layer: this rank holds the input channels of its own
+    heads (or of its slice of the MLP width).  The online rotation and the per-token scale span the
+    whole input, so the fp16 shards are all-gathered, every rank rotates and quantizes the full row,
+    multiplies its K-slice of the codes and the int32 partial sums are all-reduced: integer addition
+    is associative, so every TP degree gives the bits of one GPU (`signrot_b200.tp`)."""
+
+    def __init__(self, lin: KernelLinear, group, heads=0):
+        super().__init__()
+        from .. import tp
+        had = lin.kernel_hadamard
+        full = lin.online_full_had
+        self.use_kernel = True
+        self.online_full_had, self.online_partial_had = lin.online_full_had, lin.online_partial_had
+        self.out_features = lin.out_features
+        self.row = tp.RowParallelLinear4bit(
+            lin.kernel_module.weight, lin.kernel_module.weight_scales,
+            hadK=had.had_rem_dim if full else None, K_had=had.rem_dim if full else 1,
+            sign=had.had_adj_sign if full else None, heads=heads, clip_ratio=lin.kernel_quantizer.clip_ratio, group=group)
+
+    def forward(self, x_local):
+        lead = x_local.shape[:-1]
+        out = self.row.forward(x_local.reshape(-1, x_local.shape[-1]).contiguous())
+        return out.view(*lead, self.out_features)
+
+
+def _slice_linear(lin: KernelLinear, begin, end):
+    """Output rows [begin, end) of a projection without an online rotation (column parallelism)."""
+    new = KernelLinear(lin.in_features, end - begin, asym=lin._asym, clip_ratio=lin.kernel_quantizer.clip_ratio)
+    new = new.to(lin.kernel_module.weight.device)
+    new.kernel_module.weight = lin.kernel_module.weight[begin:end].contiguous()
+    new.kernel_module.weight_scales = lin.kernel_module.weight_scales[begin:end].contiguous()
+    return new
+
+
+def shard_decoder_(model: "KernelDecoderModel", group=None):
+    """Turns a (replicated) dense `KernelDecoderModel` into this rank's tensor-parallel shard, in place:
+    q/k/v and gate/up column-parallel by heads / MLP width (no collective), o_proj and down_proj
+    row-parallel (`TPRowLinear`: one all-gather and one int32 all-reduce each), residual stream,
+    norms, embedding and head replicated, KV cache per rank over its own KV heads.  The reference keeps
+    this path on one device (fake_quant/kernel_utils.py:365-366)."""
+    import torch.distributed as dist
+    cfg = model.config
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if cfg.num_local_experts:
+        raise NotImplementedError("expert-parallel sparse stacks are not built")
+    hq, hkv, d, ffn = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+    if hq % world or hkv % world or (ffn // world) % 64 or ffn % world:
+        raise ValueError(f"{hq} q heads / {hkv} kv heads / MLP width {ffn} do not split {world} ways")
+    ql, kl, fl = hq // world * d, hkv // world * d, ffn // world
+    for layer in model.layers:
+        at, mlp = layer.self_attn, layer.mlp
+        for name in ("qkv_fused",):
+            if name in at.__dict__:
+                object.__delattr__(at, name)
+        if "gate_up_fused" in mlp.__dict__:
+            object.__delattr__(mlp, "gate_up_fused")
+        o_row = TPRowLinear(at.o_proj, group, heads=hq)
+        down_row = TPRowLinear(mlp.down_proj, group)
+        at.q_proj = _slice_linear(at.q_proj, rank * ql, (rank + 1) * ql)
+        at.k_proj = _slice_linear(at.k_proj, rank * kl, (rank + 1) * kl)
+        at.v_proj = _slice_linear(at.v_proj, rank * kl, (rank + 1) * kl)
+        at.o_proj = o_row
+        mlp.gate_proj = _slice_linear(mlp.gate_proj, rank * fl, (rank + 1) * fl)
+        mlp.up_proj = _slice_linear(mlp.up_proj, rank * fl, (rank + 1) * fl)
+        mlp.down_proj = down_row
+    # the cache and the attention see this rank's heads only
+    from dataclasses import replace
+    model.config = replace(cfg, num_attention_heads=hq // world, num_key_value_heads=hkv // world)
+    model.tp_world = world
+    return model.fuse_projections_()
