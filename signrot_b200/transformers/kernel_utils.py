@@ -455,12 +455,19 @@ class KernelDecoderModel(torch.nn.Module):
 
 def build_paged_cache(model, batch_size, max_length, page_size=None):
     """Paged int4 cache sized for `max_length` tokens per request."""
+    from .kv_cache import decode_split
     cfg = model.config
+    page = min(page_size or DEFAULT_PAGE_SIZE, max_length)
+    device = model.get_input_embeddings().weight.device
+    chunks = None
+    tp_world = getattr(model, "tp_world", 1)
+    if tp_world > 1:   # the split of the unsharded model: same merge order, same bits
+        chunks = decode_split(batch_size, cfg.num_key_value_heads * tp_world, -(-max_length // page), device)
     return MultiLayerPagedKVCache4Bit(
-        batch_size=batch_size, page_size=min(page_size or DEFAULT_PAGE_SIZE, max_length), max_seq_len=max_length,
-        device=model.get_input_embeddings().weight.device, n_layers=cfg.num_hidden_layers,
-        num_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, hadamard_dtype=torch.float16,
-        group_size=cfg.num_attention_heads // cfg.num_key_value_heads)
+        batch_size=batch_size, page_size=page, max_seq_len=max_length, device=device,
+        n_layers=cfg.num_hidden_layers, num_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim,
+        hadamard_dtype=torch.float16, group_size=cfg.num_attention_heads // cfg.num_key_value_heads,
+        decode_chunks=chunks)
 
 
 # ----------------------------------------------------------------------------- graph runner

@@ -232,9 +232,18 @@ class _AttentionStub:
         return out.unsqueeze(1)
 
 
+def decode_split(batch_size, kv_heads, max_pages, device):
+    """Chunks per (request, KV head) of the split-KV decode: about two CTAs per SM, at most one per page."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    per_sm = int(os.environ.get("SIGNROT_B200_DECODE_CTAS_PER_SM", "2"))
+    chunks = max(1, -(-per_sm * sms // (batch_size * kv_heads)))
+    return min(chunks, max(1, max_pages))
+
+
 class MultiLayerPagedKVCache4Bit(_HFCache):
     def __init__(self, batch_size, page_size, max_seq_len, device, n_layers, num_heads, head_dim,
-                 disable_quant=False, hadamard_dtype=torch.float16, group_size=1, lac=False):
+                 disable_quant=False, hadamard_dtype=torch.float16, group_size=1, lac=False, decode_chunks=None):
+        self.decode_chunks = decode_chunks
         if disable_quant:
             raise NotImplementedError("the unquantized fp16 cache (a baseline knob of the reference) is not built")
         if lac:
@@ -274,12 +283,13 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
 
     def _configure_decode_split(self, max_pages):
         """Fixed number of sequence chunks per (request, KV head) so that about two CTAs per SM
-        are in flight; bounded by the page count (a chunk is a page range)."""
-        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        ctas = self.batch_size * self.num_heads
-        per_sm = int(os.environ.get("SIGNROT_B200_DECODE_CTAS_PER_SM", "2"))
-        chunks = max(1, -(-per_sm * sms // ctas))
-        chunks = min(chunks, max(1, max_pages))
+        are in flight; bounded by the page count (a chunk is a page range).  `decode_chunks`
+        pins the number (a tensor-parallel shard uses the split of the unsharded head count, so
+        that its fp32 merge order, and with it every output bit, is that of one GPU)."""
+        if self.decode_chunks is not None:
+            chunks = max(1, min(int(self.decode_chunks), max(1, max_pages)))
+        else:
+            chunks = decode_split(self.batch_size, self.num_heads, max_pages, self.device)
         self._stub.num_chunks = chunks
         if chunks > 1:
             self._stub.tmp = torch.empty((self.batch_size, self.num_heads * self.group_size, chunks,
