@@ -194,9 +194,12 @@ int sr_moe_route(const void *logits, int64_t tokens, int64_t num_experts, int64_
 int sr_moe_gather(const void *q, const void *scale, const void *zero, const void *tok, int64_t rows, int64_t row_bytes,
                   void *q_out, void *scale_out, void *zero_out, void *stream);
 /* out[t] = sum_j rn_h(y[inv[t * top_k + j]] * weights[t, j]) over fp16 rows of `hidden` values, fp32
- * sum, one fp16 rounding: the un-permute and weighted sum of moe.py:231-235. */
-int sr_moe_combine(const void *y, const void *weights, const void *inv, int64_t tokens, int64_t top_k, int64_t hidden,
-                   void *out, void *stream);
+ * sum, one fp16 rounding: the un-permute and weighted sum of moe.py:231-235.  row_range (int32 [2] on
+ * the device, or NULL): only sorted rows lo <= r < hi are added (the rows of an expert-parallel rank's
+ * own experts); out_f32 != 0 writes the fp32 sum unrounded (fp32 [tokens, hidden]) for a sum across
+ * ranks, otherwise fp16. */
+int sr_moe_combine(const void *y, const void *weights, const void *inv, const void *row_range, int64_t tokens,
+                   int64_t top_k, int64_t hidden, int out_f32, void *out, void *stream);
 
 /* ------------------------------------------------------------------ offline weight preparation */
 

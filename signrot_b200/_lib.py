@@ -51,7 +51,7 @@ _SIGNATURES = {
     "sr_rotate_quant": [_P, _I, _I64, _I64, _P, _I64, _F, _P, _P, _I64, _F, _I, _P, _P, _P, _P, _P],
     "sr_moe_route": [_P, _I64, _I64, _I64, _I, _P, _P, _P, _P, _P, _P, _P],
     "sr_moe_gather": [_P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P],
-    "sr_moe_combine": [_P, _P, _P, _I64, _I64, _I64, _P, _P],
+    "sr_moe_combine": [_P, _P, _P, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_rtn_pack": [_P, _I, _I64, _I64, _P, _I, _P, _P, _P],
     "sr_rmsnorm": [_P, _I64, _I64, _F, _I64, _P, _P],
     "sr_add_rmsnorm_quant": [_P, _P, _I64, _I64, _F, _I64, _F, _I, _P, _P, _P, _P, _P, _P],

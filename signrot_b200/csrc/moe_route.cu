@@ -196,26 +196,38 @@ moe_gather_kernel(const uint8_t *__restrict__ q, const __half *__restrict__ scal
     }
 }
 
-// one CTA per token, 8 values per thread and step
+// one CTA per token, 8 values per thread and step.  row_range (optional, two int32 on the device): only sorted rows
+// lo <= r < hi contribute (an expert-parallel rank owns a contiguous range of the sorted rows); OUT32: the fp32 sum
+// is written unrounded, for a sum across ranks.
+template <bool OUT32>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __half *__restrict__ y, const __half *__restrict__ weights, const int32_t *__restrict__ inv,
-                   uint32_t T, uint32_t k, uint32_t hid, __half *__restrict__ out) {
+                   const int32_t *__restrict__ row_range, uint32_t T, uint32_t k, uint32_t hid, void *__restrict__ out) {
     pdl_trigger();
     pdl_wait();
     const uint32_t t = blockIdx.x;
+    const int32_t lo = row_range ? row_range[0] : 0, hi = row_range ? row_range[1] : 0x7fffffff;
     for (uint32_t c = threadIdx.x * 8; c < hid; c += 256 * 8) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (uint32_t j = 0; j < k; ++j) {
+            const int32_t r = inv[(size_t)t * k + j];
+            if (r < lo || r >= hi) continue;
             const float w = __half2float(weights[(size_t)t * k + j]);
             Vec16 v;
-            v.u = __ldg(reinterpret_cast<const uint4 *>(y + (size_t)inv[(size_t)t * k + j] * hid + c));
+            v.u = __ldg(reinterpret_cast<const uint4 *>(y + (size_t)r * hid + c));
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] += __half2float(__float2half_rn(__half2float(v.h[i]) * w));
         }
-        Vec16 o;
+        if (OUT32) {
+            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)t * hid + c);
+            dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        } else {
+            Vec16 o;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o.h[i] = __float2half_rn(acc[i]);
-        *reinterpret_cast<uint4 *>(out + (size_t)t * hid + c) = o.u;
+            for (int i = 0; i < 8; ++i) o.h[i] = __float2half_rn(acc[i]);
+            *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(out) + (size_t)t * hid + c) = o.u;
+        }
     }
 }
 
@@ -267,16 +279,21 @@ int sr_moe_gather(const void *q, const void *scale, const void *zero, const void
     return check_launch("moe_gather");
 }
 
-int sr_moe_combine(const void *y, const void *weights, const void *inv, int64_t tokens, int64_t top_k, int64_t hidden,
-                   void *out, void *stream) {
+int sr_moe_combine(const void *y, const void *weights, const void *inv, const void *row_range, int64_t tokens,
+                   int64_t top_k, int64_t hidden, int out_f32, void *out, void *stream) {
     SR_REQUIRE(tokens >= 0 && top_k >= 1 && hidden >= 0, SR_ERR_INVALID, "moe_combine: bad size");
     if (tokens == 0 || hidden == 0) return SR_OK;
     SR_REQUIRE(y && weights && inv && out, SR_ERR_INVALID, "moe_combine: null pointer");
     SR_REQUIRE(hidden % 8 == 0 && aligned16(y) && aligned16(out), SR_ERR_UNSUPPORTED,
                "moe_combine: hidden must be a multiple of 8 and rows 16-byte aligned");
-    launch_pdl(moe_combine_kernel, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), (const __half *)y,
-               (const __half *)weights, (const int32_t *)inv, (uint32_t)tokens, (uint32_t)top_k, (uint32_t)hidden,
-               (__half *)out);
+    if (out_f32)
+        launch_pdl(moe_combine_kernel<true>, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), (const __half *)y,
+                   (const __half *)weights, (const int32_t *)inv, (const int32_t *)row_range, (uint32_t)tokens,
+                   (uint32_t)top_k, (uint32_t)hidden, out);
+    else
+        launch_pdl(moe_combine_kernel<false>, dim3((unsigned)tokens), dim3(256), 0, as_stream(stream), (const __half *)y,
+                   (const __half *)weights, (const int32_t *)inv, (const int32_t *)row_range, (uint32_t)tokens,
+                   (uint32_t)top_k, (uint32_t)hidden, out);
     return check_launch("moe_combine");
 }
 

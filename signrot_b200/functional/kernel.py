@@ -536,14 +536,17 @@ def moe_gather(packed: PackedQuantizedTensor, tok):
     return PackedQuantizedTensor(q_out, s_out, z_out)
 
 
-def moe_combine(y, weights, inv):
+def moe_combine(y, weights, inv, row_range=None, out_fp32=False):
     """Un-permute and weighted sum of the expert outputs (moe.py:231-235): y fp16 [R, hidden] in
-    sorted row order, weights fp16 [T, k], inv int32 [T * k] -> fp16 [T, hidden]."""
+    sorted row order, weights fp16 [T, k], inv int32 [T * k] -> fp16 [T, hidden].  `row_range`
+    (int32 [2] on the device): only sorted rows lo <= r < hi count; `out_fp32`: the unrounded fp32
+    sum (for a sum across expert-parallel ranks)."""
     y = y.contiguous()
-    dev = require_cuda("moe_combine", y, weights, inv)
+    dev = require_cuda("moe_combine", y, weights, inv, row_range)
     T, k = weights.shape
-    out = torch.empty((T, y.shape[-1]), dtype=torch.float16, device=dev)
-    run(dev, "sr_moe_combine", ptr(y), ptr(weights), ptr(inv), T, k, y.shape[-1], ptr(out))
+    out = torch.empty((T, y.shape[-1]), dtype=torch.float32 if out_fp32 else torch.float16, device=dev)
+    run(dev, "sr_moe_combine", ptr(y), ptr(weights), ptr(inv), ptr(row_range), T, k, y.shape[-1], int(bool(out_fp32)),
+        ptr(out))
     return out
 
 

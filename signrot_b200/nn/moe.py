@@ -35,6 +35,7 @@ class SignRotMoEBlock(torch.nn.Module):
                  asym=False, clip_ratio=1.0, fp32_had=False, use_grouped=True, fused_routing=True):
         super().__init__()
         self.fused_routing = fused_routing
+        self._ep = None                 # (group, first expert, end expert) after shard_experts_
         self.gate = gate
         self.top_k = top_k
         self.norm_topk_prob = norm_topk_prob
@@ -144,15 +145,50 @@ class SignRotMoEBlock(torch.nn.Module):
         weights, _, tok, eid, inv, row_off = kernel.moe_route(router_logits, self.top_k, self.norm_topk_prob)
         q_tok, s_tok, z_tok = self._quantize(x)
         routed = kernel.moe_gather(kernel.PackedQuantizedTensor(q_tok, s_tok, z_tok), tok)
-        gate_h = kernel.grouped_linear(routed, eid, row_off, self.w_gate, self.s_gate, self.wsum_gate)
-        up_h = kernel.grouped_linear(routed, eid, row_off, self.w_up, self.s_up, self.wsum_up)
+        ep = self._ep
+        if ep is None:
+            eid_w, off_w, rng = eid, row_off, None
+        else:
+            # expert parallel: this rank holds experts [e0, e1); the rows are sorted by expert, so its rows are
+            # the contiguous range row_off[e0] .. row_off[e1] and the grouped GEMMs touch nothing else.  Expert
+            # ids index the local weight stacks; the sign table stays global.
+            e0, e1 = ep[1], ep[2]
+            eid_w, off_w, rng = eid - e0, row_off[e0:e1 + 1], row_off[e0:e1 + 1:e1 - e0].contiguous()
+        gate_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_gate, self.s_gate, self.wsum_gate)
+        up_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_up, self.s_up, self.wsum_up)
         inter = kernel.swiglu(gate_h, up_h)
         pk = kernel.rotate_quant(inter, self.had_K, self.K, sign=self.sign_down,
                                  expert_ids=eid if self.sign_down is not None else None,
                                  clip_ratio=self.clip_ratio, asym=self.asym)
-        y = kernel.grouped_linear(pk, eid, row_off, self.w_down, self.s_down, self.wsum_down)
-        out = kernel.moe_combine(y, weights, inv)
+        y = kernel.grouped_linear(pk, eid_w, off_w, self.w_down, self.s_down, self.wsum_down)
+        if ep is None:
+            out = kernel.moe_combine(y, weights, inv)
+        else:
+            import torch.distributed as dist
+            part = kernel.moe_combine(y, weights, inv, row_range=rng, out_fp32=True)
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=ep[0])
+            out = part.to(torch.float16)
         return out.view(bsz, seq, hid), router_logits
+
+    def shard_experts_(self, group=None):
+        """Expert parallelism, in place: this rank keeps a contiguous block of num_experts / world experts
+        (weights, scales, row sums); router, tokens and the sign table stay replicated.  Every rank routes all
+        tokens, computes the rows of its own experts and the weighted partial sums are added across ranks in
+        fp32 (with top-2 a token has at most two non-zero addends, so the result has the bits of one GPU)."""
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.num_experts % world:
+            raise ValueError(f"{self.num_experts} experts do not split {world} ways")
+        per = self.num_experts // world
+        e0, e1 = rank * per, (rank + 1) * per
+        self._ensure_wsum()
+        for name in ("w_gate", "w_up", "w_down", "s_gate", "s_up", "s_down", "wsum_gate", "wsum_up", "wsum_down"):
+            t = getattr(self, name)
+            if t is not None:
+                setattr(self, name, t[e0:e1].contiguous())
+        self._ep = (group, e0, e1)
+        self.fused_routing = True
+        return self
 
     def forward(self, hidden_states: torch.Tensor):
         bsz, seq, hid = hidden_states.shape
@@ -163,6 +199,8 @@ class SignRotMoEBlock(torch.nn.Module):
                 and self.num_experts <= 512 and self.top_k <= 8 and hid % 8 == 0
                 and self.gate.weight.dtype == torch.float16):
             return self._forward_fused_routing(hidden_states)
+        if self._ep is not None:
+            raise RuntimeError("an expert-parallel block runs the fused-routing path only (fp16, grouped)")
 
         router_logits = self.gate(x)
         probs = torch.softmax(router_logits, dim=1, dtype=torch.float)

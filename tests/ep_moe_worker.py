@@ -1,0 +1,57 @@
+"""Worker of the expert-parallel MoE check (one process per GPU, NCCL).  Launched by tests/test_gpu_tp.py, or:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29514 tests/ep_moe_worker.py
+
+Every rank builds the same seeded sparse block, computes the one-GPU output, shards a second copy by experts
+and checks that the expert-parallel block (local grouped GEMMs + fp32 all-reduce of the weighted partial sums)
+reproduces it bit for bit (top-2: at most two addends per token)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from signrot_b200 import nn as snn  # noqa: E402
+
+
+def block(E, hidden, inter, top_k, seed, dev, asym):
+    g = torch.Generator().manual_seed(seed)
+    def w(n, k):
+        return torch.randint(0, 256, (E, n, k // 2), generator=g, dtype=torch.uint8).to(dev)
+    def s(n, k):
+        return (torch.rand((E, n), generator=g) * 0.5 / k + 0.5 / k).half().to(dev)
+    gate = torch.nn.Linear(hidden, E, bias=False).half()
+    gate.weight.data = torch.randn((E, hidden), generator=g).half()
+    sg = (torch.randint(0, 2, (E, inter), generator=g) * 2 - 1).to(torch.int8).to(dev)
+    return snn.SignRotMoEBlock(gate.to(dev), top_k=top_k, norm_topk_prob=True, w_gate=w(inter, hidden),
+                               s_gate=s(inter, hidden), w_up=w(inter, hidden), s_up=s(inter, hidden),
+                               w_down=w(hidden, inter), s_down=s(hidden, inter), sign_down=sg, asym=asym)
+
+
+@torch.no_grad()
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    for (E, hidden, inter, tokens, asym) in [(8, 512, 768, 64, False), (8, 512, 768, 700, False), (4, 256, 1536, 33, True)]:
+        full = block(E, hidden, inter, 2, 11, dev, asym)
+        ep = block(E, hidden, inter, 2, 11, dev, asym).shard_experts_()
+        assert ep.w_gate.shape[0] == E // world
+        x = torch.randn((1, tokens, hidden), generator=torch.Generator().manual_seed(tokens)).half().to(dev)
+        want, logits_a = full(x)
+        got, logits_b = ep(x)
+        assert torch.equal(logits_a, logits_b)
+        assert torch.equal(got, want), f"expert-parallel output differs at {(E, hidden, inter, tokens, asym)} on rank {rank}"
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"ep_moe_worker: OK on {world} ranks", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
