@@ -84,3 +84,60 @@ def test_tp_linears_two_ranks(tmp_path):
     world, port = 2, 29600 + os.getpid() % 300
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_decoder_head_slices_match_row_shards():
+    """The tensor-parallel decoder slices q/k/v by heads and gate/up by MLP width; the row-parallel o_proj and
+    down_proj of the same rank must own exactly the input channels those slices produce."""
+    from signrot_b200.tp import shard_range
+    for heads, kv_heads, d, ffn, world in [(32, 8, 128, 14336, 2), (32, 8, 128, 14336, 4), (32, 8, 128, 14336, 8),
+                                           (8, 4, 128, 3072, 2)]:
+        for rank in range(world):
+            ql = heads // world * d
+            assert shard_range(heads * d, rank, world, 64) == (rank * ql, (rank + 1) * ql)
+            fl = ffn // world
+            assert shard_range(ffn, rank, world, 64) == (rank * fl, (rank + 1) * fl)
+            assert (kv_heads // world) * world == kv_heads
+
+
+def _ep_worker(rank, world, port, out_dir):
+    """Expert parallelism on CPU: routing replicated, each rank adds the weighted outputs of its own experts' rows
+    (a contiguous range of the expert-sorted rows), fp32 all-reduce; equals the unsharded weighted sum."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(5)
+        T, E, k, hid = 37, 8, 2, 64
+        logits = torch.randn((T, E), generator=g).half()
+        probs = torch.softmax(logits.float(), dim=1)
+        pw, sel = torch.topk(probs, k, dim=-1)
+        w = (pw / pw.sum(-1, keepdim=True)).half()
+        flat = sel.reshape(-1)
+        perm = torch.argsort(flat, stable=True)
+        inv = torch.argsort(perm)
+        counts = torch.bincount(flat, minlength=E)
+        row_off = torch.cat([counts.new_zeros(1), counts.cumsum(0)])
+        y = torch.randn((T * k, hid), generator=g).half()            # expert outputs in sorted row order
+        want = (y[inv].view(T, k, hid) * w.unsqueeze(-1)).sum(dim=1)
+        per = E // world
+        lo, hi = int(row_off[rank * per]), int(row_off[(rank + 1) * per])
+        part = torch.zeros((T, hid), dtype=torch.float32)
+        for t in range(T):
+            for j in range(k):
+                r = int(inv[t * k + j])
+                if lo <= r < hi:
+                    part[t] += (y[r].float() * w[t, j].float()).half().float()
+        dist.all_reduce(part, op=dist.ReduceOp.SUM)
+        assert torch.equal(part.half(), want), "expert-parallel sum differs from the unsharded one"
+        covered = [(int(row_off[r * per]), int(row_off[(r + 1) * per])) for r in range(world)]
+        assert covered[0][0] == 0 and covered[-1][1] == T * k and all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+        (Path(out_dir) / f"ep{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_sum_two_ranks(tmp_path):
+    world, port = 2, 29900 + os.getpid() % 90
+    mp.spawn(_ep_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ep{r}").exists() for r in range(world))
