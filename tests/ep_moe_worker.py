@@ -46,6 +46,33 @@ def main():
         got, logits_b = ep(x)
         assert torch.equal(logits_a, logits_b)
         assert torch.equal(got, want), f"expert-parallel output differs at {(E, hidden, inter, tokens, asym)} on rank {rank}"
+    if "--time" in sys.argv:
+        # Mixtral-shaped block (8 experts of 14336 x 4096, top-2), 64 and 4096 tokens: milliseconds per forward,
+        # one GPU against expert-parallel, max over ranks
+        for tokens in (64, 4096):
+            full = block(8, 4096, 14336, 2, 1, dev, False)
+            x = torch.randn((1, tokens, 4096), generator=torch.Generator().manual_seed(1)).half().to(dev)
+            res = []
+            for blk in (full, None):
+                if blk is None:
+                    blk = full.shard_experts_()      # shard the same block in place (saves memory)
+                for _ in range(3):
+                    blk(x)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0.record()
+                for _ in range(10):
+                    blk(x)
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                res.append(t.item())
+            if rank == 0:
+                print(f"ep_moe_worker: timing tokens={tokens} one_gpu_ms={res[0]:.3f} ep{world}_ms={res[1]:.3f}", flush=True)
+            del full, blk
+            torch.cuda.empty_cache()
     dist.barrier()
     torch.cuda.synchronize()
     if rank == 0:
