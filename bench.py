@@ -296,7 +296,12 @@ def run_ours(args, rank, world, local_rank):
         raise RuntimeError("a kernel reported a device-side failure during warm-up")
 
     # ---- timed region: exactly `steps` steps, device time, per-kernel events inside
-    evs = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SHAPES] for _ in range(args.steps)]
+    # per-kernel events on every EV_EVERY-th step of the timed region (an event record between two launches keeps
+    # the second kernel's set-up from overlapping the first one's tail, so instrumenting every step would slow
+    # the thing being measured); SIGNROT_BENCH_EVENTS_EVERY=1 instruments all steps
+    ev_every = max(1, int(os.environ.get("SIGNROT_BENCH_EVENTS_EVERY", "8")))
+    sampled = [i for i in range(args.steps) if i % ev_every == 0]
+    evs = {i: [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SHAPES] for i in sampled}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         torch.distributed.barrier()
@@ -304,7 +309,7 @@ def run_ours(args, rank, world, local_rank):
     with ClockSampler(local_rank) as clk:
         e0.record()
         for i in range(args.steps):
-            step(i, evs[i])
+            step(i, evs.get(i))
         e1.record()
         torch.cuda.synchronize()
     if world > 1:
@@ -317,8 +322,8 @@ def run_ours(args, rank, world, local_rank):
     if _lib.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure during the timed region")
 
-    rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in range(args.steps)) / args.steps for j in range(3)]
-    gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in range(args.steps)) / args.steps for j in range(3)]
+    rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in sampled) / len(sampled) for j in range(3)]
+    gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in sampled) / len(sampled) for j in range(3)]
 
     # ---- the rotation kernels back to back (no GEMM, no launch gap between dependent kernels): one CUDA graph of
     # 16 launches per shape over the rotating input sets, replayed once under CUDA events.  The in-step figures
@@ -404,7 +409,8 @@ def run_ours(args, rank, world, local_rank):
         "data": "synthetic",
         "config": {"workload": "qlinear-8b-m4096", "M": M, "shapes_KN": SHAPES, "activations": "bf16",
                    "output": "fp16", "parallelism": f"rows x{world} (no collective)",
-                   "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB"},
+                   "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB",
+                   "kernel_events": f"per-kernel CUDA events on every {ev_every}th step of the timed region"},
         "roofline": {"kernel": "gemm_tc3_kernel (persistent tcgen05 cta_group::2 kind::i8, 256x256 tile per CTA pair, TMA-staged packed tiles, fused dequant)", "bound": "tensor",
                      "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
                      "frac": round(gemm_ach / int8_peak, 4),
