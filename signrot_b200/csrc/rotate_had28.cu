@@ -107,14 +107,21 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
     if (sign != nullptr && !per_row_sign) neg_static = load_sign(sign);
     // sign of the 32 codes this thread stores at the end (row tid / 16, values 32 * (tid % 16) ..): one 0xF per -1
     uint32_t late_mask[4] = {0, 0, 0, 0};
-    if (LATE && sign != nullptr) {
-        const int8_t *sg = sign + (tid >> 4) * SEG + (tid & 15) * 32;
+    auto load_late = [&](const int8_t *tab) {
+        const int8_t *sg = tab + (tid >> 4) * SEG + (tid & 15) * 32;
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 4; ++i) {
+            late_mask[i] = 0;
 #pragma unroll
             for (int n = 0; n < 8; ++n)
                 if (sg[8 * i + n] < 0) late_mask[i] |= 0xFu << (4 * n);
-    }
+        }
+    };
+    if (LATE && sign != nullptr && !per_row_sign) load_late(sign);
+    // per-row sign tables (MoE): rows arrive sorted by expert, so the table of the previous row is usually still
+    // the right one; it is reloaded only when the expert changes
+    int cur_expert = -1;
+    uint64_t neg_row = 0;
 
     // step-1 A operand: H16 / 8 (rows g, g + 8; columns 2 qd (+1), + 8); step-2 B operand: H8 / 8 with
     // physical k = qd carrying logical l = 2 qd and k = qd + 4 carrying 2 qd + 1
@@ -221,8 +228,15 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
         if (row + gridDim.x < rows) fetch(row + gridDim.x);
 
         // ---- 3. Y = H * Z on the tensor cores, fp16 rounding, (sign), row maximum
-        uint64_t neg = neg_static;
-        if (per_row_sign) neg = load_sign(sign + (size_t)expert_ids[row] * N);
+        if (per_row_sign) {
+            const int e = expert_ids[row];
+            if (e != cur_expert) {
+                cur_expert = e;
+                if (LATE) load_late(sign + (size_t)e * N);
+                else neg_row = load_sign(sign + (size_t)e * N);
+            }
+        }
+        uint64_t neg = per_row_sign ? neg_row : neg_static;
         __half2 y[5][2][2];  // [tile][mt][half: rows g / g+8] = columns (2qd, 2qd+1)
         auto flip = [&](int ti, int mt) {   // sign of the four values of slot pair (ti, mt), from the bit mask
             const uint32_t sb = (uint32_t)(neg >> (ti * 8 + mt * 4)) & 15u;
@@ -327,6 +341,7 @@ rotate_quant_had28_kernel(const InT *__restrict__ x, const __half *__restrict__ 
         // no quotient reaches 7.5 when the scale is a normal fp16 number and nothing was clipped
         const bool safe = LATE && __half2float(s) >= 6.2e-5f;
         if (LATE && !safe) {
+            if (per_row_sign) neg = load_sign(sign + (size_t)cur_expert * N);   // rare: subnormal scale
 #pragma unroll
             for (int ti = 0; ti < 5; ++ti)
 #pragma unroll
@@ -395,7 +410,7 @@ int launch_rotate_had28(const RotateArgs &a, cudaStream_t st) {
         if (sm_count <= 0) sm_count = 148;
     }
     const uint32_t grid = a.rows < (uint32_t)(2 * sm_count) ? a.rows : (uint32_t)(2 * sm_count);
-    const bool late = a.clip == 1.f && a.out == nullptr && a.expert_ids == nullptr && !a.asym;
+    const bool late = a.clip == 1.f && a.out == nullptr && !a.asym;
 #define SR_H28(T, LATE, ASYM)                                                                                  \
     do {                                                                                                   \
         auto kfn = rotate_quant_had28_kernel<T, LATE, ASYM>;                                                   \

@@ -142,17 +142,30 @@ def test_rotate_quant_asym_heads_and_clip():
     assert torch.equal(z2.to(torch.int8), pk.zeros_x)
 
 
-def test_rotate_quant_expert_signs():
+@pytest.mark.parametrize("n,rows,sorted_rows", [(768, 21, False), (14336, 300, True), (14336, 37, False), (4096, 50, True)])
+def test_rotate_quant_expert_signs(n, rows, sorted_rows):
+    """Per-row sign tables (MoE down_proj): the fused kernel against rotation followed by the expert-indexed
+    quantizer, with and without the rotated rows as a second output (the two take different code paths for
+    n = 14336: sign on the packed codes, sign on the values)."""
     g = torch.Generator().manual_seed(2)
-    E, rows, n = 4, 21, 768
+    E = 4
     x = _x(rows, n, 9)
     sign = (torch.randint(0, 2, (E, n), generator=g) * 2 - 1).to(torch.int8)
     eid = torch.randint(0, E, (rows,), generator=g).to(torch.int32)
+    if sorted_rows:
+        eid = eid.sort()[0]
     hadK, K = get_hadK(n)
     pk = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), expert_ids=eid.to(DEV))
-    h = kernel.hadamard(x.to(DEV), hadK, K)
-    q2, s2 = kernel.sym_quant_dynamic_moe(h, sign.to(DEV), eid.to(DEV))
+    pk2, rot = kernel.rotate_quant(x.to(DEV), hadK, K, sign=sign.to(DEV), expert_ids=eid.to(DEV), return_rotated=True)
+    assert torch.equal(pk.quantized_x, pk2.quantized_x) and torch.equal(pk.scales_x, pk2.scales_x)
+    q2, s2 = kernel.sym_quant_dynamic(rot)
     assert torch.equal(q2, pk.quantized_x) and torch.equal(s2, pk.scales_x)
+    if n == 768:   # generic kernel: same rounding points as the separate rotation
+        h = kernel.hadamard(x.to(DEV), hadK, K)
+        q3, s3 = kernel.sym_quant_dynamic_moe(h, sign.to(DEV), eid.to(DEV))
+        assert torch.equal(q3, pk.quantized_x) and torch.equal(s3, pk.scales_x)
+    want = oracle.rotate(x, hadK, K, None, cast_in_to_f16=True, out_dtype=torch.float16) * sign[eid.long()].to(torch.float16)
+    _ulp_close(rot.cpu(), want)
 
 
 def test_rotation_is_orthogonal_at_full_size():
