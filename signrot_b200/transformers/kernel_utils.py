@@ -667,3 +667,40 @@ def shard_decoder_(model: "KernelDecoderModel", group=None):
     model.config = replace(cfg, num_attention_heads=hq // world, num_key_value_heads=hkv // world)
     model.tp_world = world
     return model.fuse_projections_()
+
+
+# ----------------------------------------------------------------------------- sparse blocks
+
+def build_moe_block(mlp):
+    """A sparse MLP whose experts are per-expert `KernelLinear` triples (`mlp.experts[i].gate_proj / up_proj /
+    down_proj`, router `mlp.gate`, `mlp.top_k`, `mlp.norm_topk_prob`) -> one `SignRotMoEBlock` over stacked
+    expert weights: routing on the GPU, grouped int4 GEMMs and the per-expert adjustment signs fused into the
+    down_proj quantizer (fake_quant/kernel_utils.py:295-349).  Returns None, leaving the module as it is, when
+    the experts are not uniformly kernel-enabled."""
+    gates = [e.gate_proj for e in mlp.experts]
+    ups = [e.up_proj for e in mlp.experts]
+    downs = [e.down_proj for e in mlp.experts]
+    wrappers = gates + ups + downs
+    if not all(getattr(w, "use_kernel", False) and isinstance(w, KernelLinear) for w in wrappers):
+        logging.warning("MoE experts are not all kernel-enabled; keeping the per-expert loop")
+        return None
+    quantizer = gates[0].kernel_quantizer
+    assert all(type(w.kernel_quantizer) is type(quantizer) and w.kernel_quantizer.clip_ratio == quantizer.clip_ratio
+               for w in wrappers), "MoE stacking expects one activation quantizer config across all experts"
+    assert all(w.online_full_had for w in downs), "expert down_proj must run the online Hadamard on the kernel path"
+    assert all(w.fp32_had == downs[0].fp32_had for w in downs)
+    asym = isinstance(quantizer, snn.AsymQuantizer)
+    w_gate, s_gate, _ = snn.SignRotMoEBlock.stack_experts([w.kernel_module for w in gates], need_wsum=False)
+    w_up, s_up, _ = snn.SignRotMoEBlock.stack_experts([w.kernel_module for w in ups], need_wsum=False)
+    w_down, s_down, _ = snn.SignRotMoEBlock.stack_experts([w.kernel_module for w in downs], need_wsum=False)
+    sign_down = None
+    if any(w.kernel_hadamard.had_adj_sign is not None for w in downs):
+        inter = w_gate.shape[1]
+        sign_down = torch.stack([
+            w.kernel_hadamard.had_adj_sign.to(w_gate.device) if w.kernel_hadamard.had_adj_sign is not None
+            else torch.ones(inter, dtype=torch.int8, device=w_gate.device)      # never-routed experts: identity
+            for w in downs]).contiguous()
+    return snn.SignRotMoEBlock(mlp.gate, top_k=mlp.top_k, norm_topk_prob=mlp.norm_topk_prob,
+                               w_gate=w_gate, s_gate=s_gate, w_up=w_up, s_up=s_up, w_down=w_down, s_down=s_down,
+                               sign_down=sign_down, asym=asym, clip_ratio=quantizer.clip_ratio,
+                               fp32_had=downs[0].fp32_had)

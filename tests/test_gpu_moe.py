@@ -200,3 +200,45 @@ def test_fused_routing_block_equals_tensor_chain_block(E, hidden, inter, top_k, 
     assert torch.equal(l1, l2)
     # routing weights may differ by one fp16 ulp (softmax summation order); everything else is the same
     assert rel_l2(y1.cpu(), y2.cpu()) <= 1e-3
+
+
+@torch.no_grad()
+def test_build_moe_block_from_per_expert_linears():
+    """Per-expert KernelLinear triples behind a host loop -> stacked SignRotMoEBlock: same output as running
+    each routed token through its experts one by one."""
+    from types import SimpleNamespace
+    from signrot_b200.transformers import kernel_utils as ku
+    E, hid, ffn, k, T = 4, 256, 768, 2, 19
+    g = torch.Generator().manual_seed(21)
+
+    def lin(i, o, **kw):
+        m = ku.KernelLinear(i, o, **kw).to(DEV)
+        m.kernel_module.weight.copy_(torch.randint(0, 256, (o, i // 2), generator=g, dtype=torch.uint8))
+        m.kernel_module.weight_scales = ((torch.rand((o, 1), generator=g) * 0.5 + 0.5) / i).half().to(DEV)
+        return m
+    experts = []
+    for _ in range(E):
+        down = lin(ffn, hid, online_full_had=True, had_adj=True)
+        down.kernel_hadamard.had_adj_sign.copy_((torch.randint(0, 2, (ffn,), generator=g) * 2 - 1).to(torch.int8))
+        experts.append(SimpleNamespace(gate_proj=lin(hid, ffn), up_proj=lin(hid, ffn), down_proj=down))
+    gate = torch.nn.Linear(hid, E, bias=False).half().to(DEV)
+    gate.weight.data = torch.randn((E, hid), generator=g).half().to(DEV)
+    mlp = SimpleNamespace(experts=experts, gate=gate, top_k=k, norm_topk_prob=True)
+    blk = ku.build_moe_block(mlp)
+    assert blk is not None and blk.num_experts == E and blk.sign_down.shape == (E, ffn)
+    x = torch.randn((1, T, hid), generator=g).half().to(DEV)
+    y, logits = blk(x)
+    probs = torch.softmax(logits.float(), dim=1)
+    pw, sel = torch.topk(probs, k, dim=-1)
+    pw = (pw / pw.sum(-1, keepdim=True)).half()
+    want = torch.zeros((T, k, hid), dtype=torch.float16, device=DEV)
+    for t in range(T):
+        for j in range(k):
+            e = experts[int(sel[t, j])]
+            xt = x[0, t:t + 1]
+            inter = kernel.swiglu(e.gate_proj(xt), e.up_proj(xt))
+            want[t, j] = e.down_proj(inter)[0]
+    want = (want * pw.unsqueeze(-1)).sum(dim=1)
+    assert rel_l2(y.view(T, hid).cpu(), want.cpu()) <= 1e-3
+    experts[0].gate_proj.use_kernel = False
+    assert ku.build_moe_block(mlp) is None
