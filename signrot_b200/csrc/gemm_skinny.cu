@@ -19,6 +19,7 @@
 // so the dot product is unchanged; every product carries a factor 256 that the epilogue removes
 // with an exact shift.  The eight partial accumulators of a block meet in shared memory.
 #include <cstdlib>
+#include <cstring>
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -299,6 +300,16 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
 // Warps that share one row block.  Two (four blocks in flight per CTA) pays when there are enough blocks to
 // occupy every warp group of the grid and K is short, so that the per-block reduction and epilogue
 // would otherwise weigh as much as the block's own steps; eight otherwise.
+// SIGNROT_B200_SKINNY_GRID=full: every CTA slot gets a CTA even when the row blocks then deal out unevenly (A/B runs)
+static bool skinny_full_grid() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("SIGNROT_B200_SKINNY_GRID");
+        v = (e && !strcmp(e, "full")) ? 1 : 0;
+    }
+    return v == 1;
+}
+
 static int skinny_kw(int64_t blocks, int64_t K, int sm_count, bool grouped = false) {
     static int forced = -1;
     if (forced < 0) {
@@ -334,7 +345,8 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     // two CTAs per SM; the row blocks are dealt round-robin to the warp groups, so shrink the grid to even the deal out
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
-    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
+    // (grouped launches keep every CTA slot: measured 6 % faster on the MoE decode stack than the even deal)
+    else if (!skinny_full_grid() && !grouped) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
 #define SR_SK_KW(NT, MT, GR, KWV)                                                                              \
     do {                                                                                                       \
@@ -389,7 +401,7 @@ int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int
     const int groups = SK_WARPS / kw;
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
-    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
+    else if (!skinny_full_grid()) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
 #define SR_SKS_KW(NT, KWV)                                                                                     \
     do {                                                                                                       \
