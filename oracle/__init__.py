@@ -27,3 +27,4 @@ from .hadamard import *  # noqa: F401,F403
 from .gemm import *  # noqa: F401,F403
 from .misc import *  # noqa: F401,F403
 from .attention import *  # noqa: F401,F403
+from .moe import *  # noqa: F401,F403

@@ -39,16 +39,22 @@ class PagedCacheRef:
         vq, vp = kv_quant_pack(v_h)
         T = k_h.shape[1]
         start = self.length[layer]
-        for b in range(self.batch):
-            for t in range(T):
-                pos = start + t
-                page = (pos // self.page_size) * self.batch + b
-                e = pos % self.page_size
-                self.data[page, layer, 0, :, e] = kq[b, t]
-                self.data[page, layer, 1, :, e] = vq[b, t]
-                self.param[page, layer, 0, :, e] = kp[b, t]
-                self.param[page, layer, 1, :, e] = vp[b, t]
+        page, slot, head = self._slots(start, T)
+        self.data[page, layer, 0, head, slot] = kq
+        self.data[page, layer, 1, head, slot] = vq
+        self.param[page, layer, 0, head, slot] = kp
+        self.param[page, layer, 1, head, slot] = vp
         self.length[layer] = start + T
+
+    def _slots(self, start, count):
+        """Index tensors (physical page [B, T, 1], slot [1, T, 1], head [1, 1, H]) of positions
+        start .. start + count - 1 of every request."""
+        pos = torch.arange(start, start + count)
+        b = torch.arange(self.batch)
+        page = ((pos // self.page_size)[None, :] * self.batch + b[:, None])[:, :, None]
+        slot = (pos % self.page_size)[None, :, None]
+        head = torch.arange(self.heads)[None, None, :]
+        return page, slot, head
 
     def specs(self, layer):
         n = self.length[layer]
@@ -64,17 +70,10 @@ class PagedCacheRef:
     def dense(self, layer):
         """Dequantized K, V as fp32 [batch, heads, length, 128]."""
         n = self.length[layer]
-        ks, vs = [], []
-        for b in range(self.batch):
-            kb, vb = [], []
-            for pos in range(n):
-                page = (pos // self.page_size) * self.batch + b
-                e = pos % self.page_size
-                kb.append(kv_dequant(self.data[page, layer, 0, :, e], self.param[page, layer, 0, :, e]))
-                vb.append(kv_dequant(self.data[page, layer, 1, :, e], self.param[page, layer, 1, :, e]))
-            ks.append(torch.stack(kb, dim=1))
-            vs.append(torch.stack(vb, dim=1))
-        return torch.stack(ks), torch.stack(vs)
+        page, slot, head = self._slots(0, n)
+        k = kv_dequant(self.data[page, layer, 0, head, slot], self.param[page, layer, 0, head, slot])
+        v = kv_dequant(self.data[page, layer, 1, head, slot], self.param[page, layer, 1, head, slot])
+        return k.permute(0, 2, 1, 3).contiguous(), v.permute(0, 2, 1, 3).contiguous()
 
 
 def decode_attention_ref(q_h: torch.Tensor, k_f: torch.Tensor, v_f: torch.Tensor, hadamard_q: bool = True):

@@ -259,6 +259,8 @@ def decoder_layer_fake_quant(layer: dict, mode: str = "fake", attn_fp32: bool = 
         v.transpose(1, 2).repeat_interleave(Hh // Hk, dim=1).to(adt), is_causal=True)
     attn = attn.transpose(1, 2).reshape(1, T, Hh * D).to(dt)
     x1 = x + run("o", attn)
+    if trace is not None:
+        trace["x1"] = x1
     h2 = norm(x1)
     g, u = run("gate", h2), run("up", h2)
     m = (torch.nn.functional.silu(g) * u).to(dt)

@@ -130,7 +130,121 @@ def main():
         aq.find_params(x)
         d[tag] = npy(aq(x))
     np.savez_compressed(OUT / "act_fake_quant.npz", **d)
+    extra(g)
     print("golden vectors written to", OUT)
+
+
+def _reference_function(path: Path, name: str, namespace: dict):
+    """Compiles ONE function of a reference script without importing the script (its module level
+    imports the CUDA extension and runs on a GPU)."""
+    import ast
+    tree = ast.parse(path.read_text())
+    fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == name)
+    code = compile(ast.Module(body=[fn], type_ignores=[]), str(path), "exec")
+    exec(code, namespace)
+    return namespace[name]
+
+
+def extra(g):
+    """Vectors for the statements that exist only as CUDA kernels in the reference, taken from the
+    pure-torch code the reference itself tests those kernels against."""
+    import math
+    import types
+    import oracle
+    kern = ref_shim.module("signrot.functional.kernel")
+    qn = ref_shim.module("signrot.nn.quantization")
+    kvc = ref_shim.module("signrot.transformers.kv_cache")
+
+    # 8. scale order of the quantizer modules' torch statements (signrot/nn/quantization.py:23-28, 44-48,
+    #    67-76).  Their code decision is a CUDA call; it is answered by the oracle here, so only the scales
+    #    (and the asymmetric zero point) written by the reference's lines are stored.
+    seen = {}
+    def grab_sym(x, scales):
+        seen["scale"] = scales.clone()
+        return oracle.sym_quant(x, scales)
+    def grab_asym(x, scales, zeros):
+        seen["scale"], seen["zero"] = scales.clone(), zeros.clone()
+        return oracle.pack_codes(oracle.asym_quant_codes(x, scales.half(), zeros.half(), 0, 15))
+    kern.sym_quant, kern.asym_quant_f16_ui4 = grab_sym, grab_asym
+    x = torch.randn((7, 256), generator=g).half()
+    x[2] *= 40.0
+    x[5] = x[5].abs() + 0.5
+    d = {"x": npy(x)}
+    for clip in (1.0, 0.9):
+        tag = f"clip{int(clip * 100)}"
+        qn.Quantizer(clip_ratio=clip).forward_reference(x)
+        d[f"quantizer_{tag}"] = npy(seen["scale"])
+        qn.SymQuantizer(clip_ratio=clip).forward_reference(x)
+        d[f"symquantizer_{tag}"] = npy(seen["scale"])
+        qn.AsymQuantizer(clip_ratio=clip).forward_reference(x)
+        d[f"asym_scale_{tag}"], d[f"asym_zero_{tag}"] = npy(seen["scale"]), npy(seen["zero"])
+    np.savez_compressed(OUT / "quantizer_scales.npz", **d)
+
+    # 9. rotary embedding: the HF function the reference checks rope_qk against
+    #    (benchmarks/test_fused_equivalence.py:102-115)
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+    d = {}
+    for tag, (b, t_, hq, hk, cos_b) in {"b4t3": (4, 3, 32, 8, 4), "b2t5_shared": (2, 5, 8, 8, 1)}.items():
+        q = torch.randn((b, t_, hq, 128), generator=g).half()
+        k = torch.randn((b, t_, hk, 128), generator=g).half()
+        cos = torch.randn((cos_b, t_, 128), generator=g).half()
+        sin = torch.randn((cos_b, t_, 128), generator=g).half()
+        qr, kr = apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=2)
+        for name, val in (("q", q), ("k", k), ("cos", cos), ("sin", sin), ("q_out", qr), ("k_out", kr)):
+            d[f"{tag}_{name}"] = npy(val)
+    np.savez_compressed(OUT / "rope.npz", **d)
+
+    # 10. decode attention: the reference's fp32 statement over its own dequantized paged cache
+    #     (benchmarks/test_split_decode.py:22-46 with kv_cache.py:12-68), K rotated as the cache does
+    #     (kv_cache.py:70-73)
+    ref_attn = _reference_function(ref_shim.REF / "benchmarks" / "test_split_decode.py", "reference_attention",
+                                   {"torch": torch, "math": math,
+                                    "unpack_i4_and_asym_dequantize": kvc.unpack_i4_and_asym_dequantize})
+    B, L, Hh, page, T = 2, 2, 4, 16, 37
+    k = torch.randn((B, T, Hh, 128), generator=g).half()
+    v = torch.randn((B, T, Hh, 128), generator=g).half()
+    q = torch.randn((B, Hh, 128), generator=g).half()
+    kq, ks, kz = kvc.asym_quantize_and_pack_i4(kvc.matmul_had_cuda(k, torch.float16))
+    vq, vs, vz = kvc.asym_quantize_and_pack_i4(v)
+    n_pages = (T + page - 1) // page
+    pages = torch.zeros((n_pages * B, L, 2, Hh, page, 64), dtype=torch.uint8)
+    scales = torch.zeros((n_pages * B, L, 2, Hh, page, 2), dtype=torch.float16)
+    for b in range(B):
+        for pos in range(T):
+            pg, slot = (pos // page) * B + b, pos % page
+            pages[pg, 1, 0, :, slot], pages[pg, 1, 1, :, slot] = kq[b, pos], vq[b, pos]
+            scales[pg, 1, 0, :, slot] = torch.cat((ks[b, pos], kz[b, pos]), -1)
+            scales[pg, 1, 1, :, slot] = torch.cat((vs[b, pos], vz[b, pos]), -1)
+    cache = types.SimpleNamespace(page_size=page, pages=pages, scales=scales, batch_size=B)
+    q_rot = kvc.matmul_had_cuda(q, torch.float16)
+    out = ref_attn(cache, q_rot, 1, T)
+    np.savez_compressed(OUT / "attention.npz", k=npy(k), v=npy(v), q=npy(q), out=npy(out), page=np.int64(page))
+
+    # 11. sparse block: the reference's forward (signrot/nn/moe.py:160-236, per-expert loop branch) with its
+    #     CUDA calls answered by the integer oracle; router, stable sort, gathers, un-permute and weighted
+    #     sum are the reference's own lines
+    moe = ref_shim.module("signrot.nn.moe")
+    kern.sym_quant_dynamic = lambda x, clip: (lambda c, s: (oracle.pack_codes(c), s))(*oracle.sym_quant_dynamic(x, clip))
+    kern.matmul_si4_si4 = lambda a, b: oracle.matmul_i4(a, b)
+    kern.sym_dequant = lambda acc, sr, sc: oracle.sym_dequant(acc, sr, sc)
+    kern.swiglu = lambda a, b: oracle.swiglu(a, b)
+    E, hidden, inter, top_k, tokens = 4, 64, 96, 2, 10
+    def w(n, kk):
+        return oracle.pack_i4(torch.randint(-8, 8, (E * n, kk), generator=g, dtype=torch.int32)).view(E, n, kk // 2)
+    def sc(n, kk):
+        return (torch.rand((E, n), generator=g) * 0.5 / kk + 0.5 / kk).half()
+    gate = torch.nn.Linear(hidden, E, bias=False).half()
+    gate.weight.data = torch.randn((E, hidden), generator=g).half()
+    sign = (torch.randint(0, 2, (E, inter), generator=g) * 2 - 1).to(torch.int8)
+    tensors = dict(w_gate=w(inter, hidden), s_gate=sc(inter, hidden), w_up=w(inter, hidden), s_up=sc(inter, hidden),
+                   w_down=w(hidden, inter), s_down=sc(hidden, inter), sign_down=sign)
+    blk = moe.SignRotMoEBlock(gate, top_k=top_k, norm_topk_prob=True, use_grouped=False, **tensors)
+    x = torch.randn((1, tokens, hidden), generator=g).half()
+    with torch.no_grad():
+        y, logits = blk(x)
+    d = {kk: npy(vv) for kk, vv in tensors.items()}
+    d.update(x=npy(x), gate_w=npy(gate.weight.data), y=npy(y), logits=npy(logits), top_k=np.int64(top_k))
+    np.savez_compressed(OUT / "moe_block.npz", **d)
 
 
 if __name__ == "__main__":

@@ -59,6 +59,31 @@ def test_matmul_ui4_and_extremes(which):
     assert int(C.min()) == int(C.max()) == -120 * 4096
 
 
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 14336), (14336, 4096)])
+def test_w4a4_linear_benchmark_shapes(K, N):
+    """The benchmarked launches (M = 4096 token rows, the library's own kernel choice): int32 accumulators and
+    the fused fp16 output against the oracle on a random 256-row subset, and EVERY row through a
+    checksum the integer product must satisfy exactly: sum_m C[m, :] = (sum_m A[m, :]) B^T."""
+    M = 4096
+    g = torch.Generator().manual_seed(K + N)
+    A = torch.randint(0, 256, (M, K // 2), generator=g, dtype=torch.uint8)
+    W = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+    sa = (torch.rand((M, 1), generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand((N, 1), generator=g) * 0.009 + 0.001).half()
+    acc = kernel.matmul_si4_si4(A.to(DEV), W.to(DEV))
+    out = kernel.w4a4_linear(kernel.PackedQuantizedTensor(A.to(DEV), sa.to(DEV)), W.to(DEV), sw.to(DEV))
+    assert _lib.device_status() == 0
+    rows = torch.randperm(M, generator=g)[:256].sort().values
+    want_acc = oracle.matmul_i4(A[rows], W)
+    assert torch.equal(acc[rows.to(DEV)].cpu(), want_acc)
+    assert torch.equal(out[rows.to(DEV)].cpu(), oracle.sym_dequant(want_acc, sa[rows], sw))
+    col_sum = oracle.unpack_i4(A).sum(0, dtype=torch.int64).double()            # |.| <= 8 * 4096
+    want_sum = (col_sum[None, :] @ oracle.unpack_i4(W).double().T).to(torch.int64).view(-1)
+    assert torch.equal(acc.sum(0, dtype=torch.int64).cpu(), want_sum)
+    # the fp16 output of every row is the dequant of the accumulator the same launch family produced
+    assert torch.equal(out, kernel.sym_dequant(acc, sa.to(DEV), sw.to(DEV)))
+
+
 def test_matmul_leading_dims_and_empty():
     a, b = _codes(6, 128, 1), _codes(10, 128, 2)
     A, B = oracle.pack_i4(a).view(2, 3, 64), oracle.pack_i4(b)

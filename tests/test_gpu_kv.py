@@ -67,6 +67,38 @@ def test_fused_append_and_decode(T, page, Hq, Hkv):
         assert (o1.float() - o2.float()).abs().max().item() <= 2e-3
 
 
+def test_decode_attention_benchmark_geometry():
+    """Batch 16, 4096 cached tokens + 1 new, page 256 (17 pages per request), 32 q / 8 kv heads: cache bytes
+    of every slot and the decode output against the oracle (3e-2 vs fp32 attention over the dequantized
+    cache; 2e-3 between the cache object's split-KV schedule and one unsplit pass)."""
+    B, L, Hq, Hkv, page, T = 16, 1, 32, 8, 256, 4096
+    g = torch.Generator().manual_seed(11)
+    k = torch.randn((B, T + 1, Hkv, 128), generator=g).half()
+    v = torch.randn((B, T + 1, Hkv, 128), generator=g).half()
+    q = torch.randn((B, 1, Hq, 128), generator=g).half()
+    ref = oracle.PagedCacheRef(B, L, Hkv, page, 18)
+    ref.append(0, k[:, :T], v[:, :T])
+    ref.append(0, k[:, T:], v[:, T:])
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 64, DEV, L, Hkv, 128, group_size=Hq // Hkv)
+    cache.update(k[:, :T].contiguous().to(DEV), v[:, :T].contiguous().to(DEV), 0)
+    attend = cache.update(k[:, T:].contiguous().to(DEV), v[:, T:].contiguous().to(DEV), 0)
+    o = attend(q.to(DEV)).cpu().view(B, Hq, 128)
+    used = 17 * B
+    assert torch.equal(cache.pages[:used, 0].cpu()[:16 * B], ref.data[:16 * B, 0])          # full pages
+    assert torch.equal(cache.pages[16 * B:used, 0, :, :, :1].cpu(), ref.data[16 * B:used, 0, :, :, :1])
+    assert torch.equal(cache.scales[:used, 0].cpu()[:16 * B], ref.param[:16 * B, 0])
+    kf, vf = ref.dense(0)
+    want = oracle.decode_attention_ref(q.view(B, Hq, 128), kf, vf, hadamard_q=True)
+    err = (o.float() - want).abs().max().item()
+    assert err <= 3e-2, err
+    specs = cache.refresh_specs()
+    qd = q.view(B, Hq, 128).to(DEV).contiguous()
+    o1 = torch.empty_like(qd)
+    kvc.batch_decode_i4(o1, qd, **specs, layer_idx=0, hadamard_q=True)
+    assert (o1.float().cpu() - o.float()).abs().max().item() <= 2e-3
+    assert (o1.float().cpu() - want).abs().max().item() <= 3e-2
+
+
 def test_prequantized_init_append_roundtrip():
     """init_kv_i4 / append_kv_i4 with codes from kv_quant_pack (the reference's unfused chain)."""
     B, L, H, page, T = 2, 1, 4, 16, 37

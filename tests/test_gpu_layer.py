@@ -1,6 +1,7 @@
 """One decoder layer through the package's modules (real int4 kernels) against the oracle's
-integer statement and its fake-quant statement of the same layer (BASELINE config 1 shapes,
-shortened in tokens so the CPU side stays within seconds).  fp16 outputs: rel-L2 <= 1e-3."""
+integer statement and its fake-quant statement of the same layer (Llama-3-8B layer shapes with the
+two massive-outlier channels, shortened in tokens so the CPU side stays within seconds).
+fp16 outputs: rel-L2 <= 1e-3."""
 import pytest
 import torch
 
@@ -80,10 +81,19 @@ def test_decoder_layer_fp16(shape):
                                                   sign=layer["down_sign"].to(DEV))).cpu()
     assert rel_l2(got.view(want.shape), want) <= 1e-3
 
-    # the whole layer: every one-ulp difference upstream of a quantizer (RMSNorm's summation
-    # order, attention) can flip codes downstream, so the end-to-end bound is the quantization
-    # noise floor, not 1e-3; the oracle's own fake-vs-integer gap on this layer is ~8e-3
+    # teacher-forced layer: every quantizer of the GPU layer is fed the oracle's tensor at that point, so
+    # the layer output is the oracle's residual stream plus the GPU's down_proj of the oracle's SwiGLU output
+    forced = (trace["x1"].to(torch.float16) + got.view(want.shape)).to(layer["x"].dtype)
+    err_forced = rel_l2(forced, want_real)
+    assert err_forced <= 1e-3, err_forced
+
+    # free-running layer: a one-ulp difference upstream of a quantizer (RMSNorm's summation order, the
+    # attention product) can move codes downstream, so the end-to-end distance is a quantization-noise
+    # figure, not a rounding figure; the oracle's own fake-vs-integer gap on this layer is ~8e-3
     got = gpu_layer(layer).cpu()
     assert torch.isfinite(got).all()
-    assert rel_l2(got, want_real) <= 1e-2
-    assert rel_l2(got, want_fake) <= 2e-2
+    err_real, err_fake = rel_l2(got, want_real), rel_l2(got, want_fake)
+    print(f"free-running layer rel-L2: {err_real:.3e} vs integer statement, {err_fake:.3e} vs fake-quant "
+          f"(teacher-forced {err_forced:.3e})")
+    assert err_real <= 1e-2, err_real
+    assert err_fake <= 2e-2, err_fake

@@ -44,32 +44,38 @@ def test_grouped_equals_loop(E, hidden, inter, top_k, tokens, asym):
     assert y1.shape == x.shape and torch.isfinite(y1).all()
 
 
-def test_block_against_integer_oracle():
-    E, hidden, inter, top_k = 8, 256, 768, 2
-    blk = _block(E, hidden, inter, top_k, 2)
+def _packed_block(E, hidden, inter, top_k, seed):
+    """Like _block, for big geometries: packed weight bytes drawn directly."""
+    g = torch.Generator().manual_seed(seed)
+    def w(n, k):
+        return torch.randint(0, 256, (E, n, k // 2), generator=g, dtype=torch.uint8)
+    def s(n, k):
+        return (torch.rand((E, n), generator=g) * 0.5 / k + 0.5 / k).half()
+    gate = torch.nn.Linear(hidden, E, bias=False).half()
+    gate.weight.data = torch.randn((E, hidden), generator=g).half()
+    sg = (torch.randint(0, 2, (E, inter), generator=g) * 2 - 1).to(torch.int8)
+    return snn.SignRotMoEBlock(gate.to(DEV), top_k=top_k, norm_topk_prob=True,
+                               w_gate=w(inter, hidden).to(DEV), s_gate=s(inter, hidden).to(DEV),
+                               w_up=w(inter, hidden).to(DEV), s_up=s(inter, hidden).to(DEV),
+                               w_down=w(hidden, inter).to(DEV), s_down=s(hidden, inter).to(DEV), sign_down=sg.to(DEV))
+
+
+@pytest.mark.parametrize("E,hidden,inter,top_k,tokens", [(8, 256, 768, 2, 24), (8, 4096, 14336, 2, 64)],
+                         ids=["small", "mixtral-8x7b-shape"])
+def test_block_against_integer_oracle(E, hidden, inter, top_k, tokens):
+    """The sparse block against the oracle's integer statement of it, expert by expert: quantizer, gate/up
+    GEMMs, SwiGLU, sign-adjusted rotation, quantizer, down GEMM, routing-weighted sum
+    (signrot/nn/moe.py:167-235).  Routing decisions are taken from the block's own logits."""
+    blk = _block(E, hidden, inter, top_k, 2) if hidden <= 512 else _packed_block(E, hidden, inter, top_k, 2)
     g = torch.Generator().manual_seed(4)
-    x = torch.randn((1, 24, hidden), generator=g).half()
+    x = torch.randn((1, tokens, hidden), generator=g).half()
     y, logits = blk(x.to(DEV))
-    # oracle: same routing decisions (taken from the kernel's logits), integer path per expert
-    probs = torch.softmax(logits.float().cpu(), dim=1)
-    pw, sel = torch.topk(probs, top_k, dim=-1)
-    pw = (pw / pw.sum(-1, keepdim=True)).half()
     hadK, K = get_hadK(inter)
-    xf = x.view(-1, hidden)
-    codes, sc = oracle.sym_quant_dynamic(xf)
-    out = torch.zeros((xf.shape[0], top_k, hidden), dtype=torch.float16)
-    for t_ in range(xf.shape[0]):
-        for j in range(top_k):
-            e = int(sel[t_, j])
-            a = oracle.pack_codes(codes[t_:t_ + 1])
-            gh = oracle.w4a4_linear(a, sc[t_:t_ + 1], blk.w_gate[e].cpu(), blk.s_gate[e].cpu())
-            uh = oracle.w4a4_linear(a, sc[t_:t_ + 1], blk.w_up[e].cpu(), blk.s_up[e].cpu())
-            h = oracle.swiglu(gh, uh)
-            hr = oracle.rotate(h, hadK, K, blk.sign_down[e].cpu())
-            c2, s2 = oracle.sym_quant_dynamic(hr)
-            out[t_, j] = oracle.w4a4_linear(oracle.pack_codes(c2), s2, blk.w_down[e].cpu(), blk.s_down[e].cpu())[0]
-    want = (out * pw.unsqueeze(-1)).sum(dim=1)
-    assert rel_l2(y.cpu().view(-1, hidden), want) <= 1e-3
+    cpu = lambda a: a.cpu()
+    want = oracle.moe_block(x.view(-1, hidden), logits.cpu(), top_k, True, cpu(blk.w_gate), cpu(blk.s_gate),
+                            cpu(blk.w_up), cpu(blk.s_up), cpu(blk.w_down), cpu(blk.s_down), cpu(blk.sign_down), hadK, K)
+    err = rel_l2(y.cpu().view(-1, hidden), want)
+    assert err <= 1e-3, err
 
 
 def test_cuda_graph_replay():

@@ -131,3 +131,67 @@ def test_real_vs_fake_small_layer():
     yr = fq.decoder_layer_fake_quant(layer, "real")
     rel = ((yf.float() - yr.float()).norm() / yr.float().norm()).item()
     assert rel <= 1e-3, rel
+
+
+@pytest.mark.parametrize("clip", [1.0, 0.9])
+def test_quantizer_scale_order_golden(clip):
+    """Scales written by the torch statements of the three quantizer modules
+    (signrot/nn/quantization.py:23-28, 44-48, 67-76)."""
+    g = load_golden("quantizer_scales.npz")
+    x = t(g["x"])
+    tag = f"clip{int(clip * 100)}"
+    # Quantizer: rn_h(amax / 7) first, then * clip -- the order of the fused kernel (fused.cu:83-98)
+    _, scale = oracle.sym_quant_dynamic(x, clip)
+    assert torch.equal(scale, t(g[f"quantizer_{tag}"]))
+    # SymQuantizer applies the clip BEFORE the division
+    amax = x.abs().amax(dim=-1).unsqueeze(1) * clip
+    assert torch.equal((amax / 7).to(torch.float16), t(g[f"symquantizer_{tag}"]))
+    if clip == 1.0:
+        assert torch.equal(t(g[f"symquantizer_{tag}"]), scale)
+    # AsymQuantizer's torch statement keeps every step in fp16; the kernel order (fused.cu:156-198) is the same
+    _, a_scale, a_zero = oracle.asym_quant_dynamic(x, clip)
+    assert torch.equal(a_scale, t(g[f"asym_scale_{tag}"]))
+    assert torch.equal(a_zero, t(g[f"asym_zero_{tag}"]))
+
+
+@pytest.mark.parametrize("tag", ["b4t3", "b2t5_shared"])
+def test_rope_golden(tag):
+    """oracle.rope_qk == HF apply_rotary_pos_emb in fp16, bit for bit
+    (benchmarks/test_fused_equivalence.py:102-115)."""
+    g = load_golden("rope.npz")
+    q, k = oracle.rope_qk(t(g[f"{tag}_q"]), t(g[f"{tag}_k"]), t(g[f"{tag}_cos"]), t(g[f"{tag}_sin"]))
+    assert torch.equal(q, t(g[f"{tag}_q_out"]))
+    assert torch.equal(k, t(g[f"{tag}_k_out"]))
+
+
+def test_decode_attention_golden():
+    """PagedCacheRef + decode_attention_ref against the reference's fp32 attention over its own dequantized
+    paged cache (benchmarks/test_split_decode.py:22-46; signrot/transformers/kv_cache.py:12-73)."""
+    g = load_golden("attention.npz")
+    k, v, q = t(g["k"]), t(g["v"]), t(g["q"])
+    B, T, Hh, _ = k.shape
+    ref = oracle.PagedCacheRef(B, 2, Hh, int(g["page"]), 4)
+    ref.append(1, k, v)
+    kf, vf = ref.dense(1)
+    got = oracle.decode_attention_ref(q, kf, vf, hadamard_q=True)
+    want = t(g["out"])
+    # the reference dequantizes in fp16 (q * scale - zero rounded twice), the oracle and the kernels in fp32
+    assert (got - want).abs().max().item() <= 2e-3
+    _, indices, last = ref.specs(1)
+    assert int(last[0]) == T % int(g["page"]) and indices.numel() == B * ((T + int(g["page"]) - 1) // int(g["page"]))
+
+
+def test_moe_block_golden():
+    """oracle.moe_block against the reference's SignRotMoEBlock.forward run on the CPU (router, stable sort,
+    gathers, un-permute and weighted sum are the reference's lines; signrot/nn/moe.py:160-236)."""
+    g = load_golden("moe_block.npz")
+    x = t(g["x"])
+    hidden = x.shape[-1]
+    xf = x.view(-1, hidden)
+    logits = torch.nn.functional.linear(xf, t(g["gate_w"]))
+    assert torch.equal(logits, t(g["logits"]))
+    inter = t(g["w_gate"]).shape[1]
+    hadK, K = sh.get_hadK(inter)
+    got = oracle.moe_block(xf, logits, int(g["top_k"]), True, t(g["w_gate"]), t(g["s_gate"]), t(g["w_up"]), t(g["s_up"]),
+                           t(g["w_down"]), t(g["s_down"]), t(g["sign_down"]), hadK, K)
+    assert torch.equal(got.view(x.shape), t(g["y"]))
