@@ -116,74 +116,97 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- CPU arm
 
-def cpu_fake_quant_step(rows: int, cases, threads: int):
-    """One pass of the oracle's fake-quant statement of the step on `rows` tokens: rotation in
-    bf16 with fp32 butterflies, sign, per-token fake-quant, F.linear on dequantized bf16 weights
-    (fake_quant/quant_utils.py:322-386)."""
-    import oracle
-    from oracle import fake_quant as fq
-    torch.set_num_threads(threads)
-    t0 = time.perf_counter()
-    for c in cases:
-        y = oracle.rotate(c["x"][:rows], c["hadK"], c["K"], c["sign"])
-        y = fq.act_fake_quant(y, 1.0, True)
-        torch.nn.functional.linear(y, c["w_deq"])
-    return time.perf_counter() - t0
+CPU_ROWS = 256   # token rows of the workload one CPU step processes (bounded sample of the 4096)
 
 
-def make_cpu_cases(rows: int):
-    import oracle
-    from oracle import fake_quant as fq
-    from signrot_b200.functional.hadamard import get_hadK
-    cases = []
-    for k, n in SHAPES:
-        c = fq.make_linear_case(rows, k, n, seed=0)
-        hadK, K = get_hadK(k)
-        w = (oracle.unpack_i4(c["w_packed"]).float() * c["w_scale"].float()).to(torch.bfloat16)
-        cases.append({"x": c["x"], "sign": c["sign"], "hadK": hadK, "K": K, "w_deq": w})
-    return cases
+def workload_config(world: int) -> dict:
+    """The `config` object both arms print."""
+    par = "rows x1 (one GPU, no collective)" if world == 1 else \
+        f"tensor-parallel x{world}: (4096,14336) column split, (14336,4096) and (4096,4096) row split with all-gather + int32 all-reduce"
+    return {"workload": "qlinear-8b-m4096", "M": M_TOKENS, "shapes_KN": SHAPES, "activations": "bf16", "output": "fp16",
+            "parallelism": par, "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB"}
 
 
-def cpu_baseline(time_limit_s: float = 12.0, rows: int = 256):
-    threads = os.cpu_count() or 1
-    cases = make_cpu_cases(rows)
-    cpu_fake_quant_step(min(rows, 32), cases, threads)  # warm-up
-    times = []
-    t_start = time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_start < time_limit_s and len(times) < 20):
-        times.append(cpu_fake_quant_step(rows, cases, threads))
-    best = sorted(times)[len(times) // 2]
-    return {"value": round(ops_per_step(rows) / best / 1e12, 4), "unit": "TOP/s", "cores": threads, "kind": "port",
-            "sample": f"{rows} of {M_TOKENS} token rows per linear, {len(times)} passes, median; "
-                      "oracle fake-quant (rotation + sign + fake-quant + bf16 F.linear)"}
+class CpuArm:
+    """The CPU statement of one step (rotation + sign + per-token int4 fake-quant + bf16 F.linear over the
+    three linears) on CPU_ROWS token rows.  With the reference's files at hand (a checkout, or oracle/_ref/
+    placed by build()) it is the reference's own ActQuantWrapper.forward (fake_quant/quant_utils.py:322-386),
+    kind "reference"; otherwise the oracle's restatement of it, kind "port"."""
+
+    def __init__(self, rows: int = CPU_ROWS):
+        import oracle
+        from oracle import fake_quant as fq
+        from oracle import ref_shim
+        from signrot_b200.functional.hadamard import get_hadK
+        self.rows = rows
+        self.threads = os.cpu_count() or 1
+        torch.set_num_threads(self.threads)
+        self.kind = "reference" if ref_shim.available() else "port"
+        self.cases = []
+        for k, n in SHAPES:
+            c = fq.make_linear_case(rows, k, n, seed=0)
+            hadK, K = get_hadK(k)
+            w = (oracle.unpack_i4(c["w_packed"]).float() * c["w_scale"].float()).to(torch.bfloat16)
+            case = {"x": c["x"], "sign": c["sign"], "hadK": hadK, "K": K, "w_deq": w}
+            if self.kind == "reference":
+                qu = ref_shim.module("quant_utils")
+                lin = torch.nn.Linear(k, n, bias=False, dtype=torch.bfloat16)
+                lin.weight.data = w              # RTN weights with the sign already folded
+                wrp = qu.ActQuantWrapper(lin)
+                wrp.quantizer.configure(bits=4, groupsize=-1, sym=True, clip_ratio=1.0)
+                wrp.online_full_had, wrp.had_K, wrp.K = True, hadK, K
+                wrp.had_adj_sign, wrp.had_adj_ready = c["sign"], True
+                case["wrapper"] = wrp
+            self.cases.append(case)
+        self.oracle, self.fq = oracle, fq
+
+    def step(self) -> float:
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            for c in self.cases:
+                if self.kind == "reference":
+                    c["wrapper"](c["x"])
+                else:
+                    y = self.oracle.rotate(c["x"], c["hadK"], c["K"], c["sign"])
+                    torch.nn.functional.linear(self.fq.act_fake_quant(y, 1.0, True), c["w_deq"])
+        return time.perf_counter() - t0
+
+    def run(self, steps: int, warmup: int):
+        """Mean seconds per step over exactly `steps` steps after `warmup` untimed ones."""
+        for _ in range(max(1, warmup)):
+            self.step()
+        return sum(self.step() for _ in range(steps)) / steps
+
+    def describe(self, steps: int) -> str:
+        what = ("the reference's ActQuantWrapper.forward, fake-quant branch (Hadamard through a CPU stand-in for the "
+                "fast_hadamard_transform library)" if self.kind == "reference" else "oracle restatement of the fake-quant forward")
+        return f"{self.rows} of {M_TOKENS} token rows per linear per step, mean of {steps} steps; {what}"
+
+
+def cpu_baseline(steps: int = 20, warmup: int = 3):
+    arm = CpuArm()
+    steps = max(3, min(steps, 40))
+    sec = arm.run(steps, warmup)
+    return {"value": round(ops_per_step(arm.rows) / sec / 1e12, 4), "unit": "TOP/s", "cores": arm.threads,
+            "kind": arm.kind, "sample": arm.describe(steps)}
 
 
 def run_reference_arm(args, rank, world):
-    """The reference's CPU implementation of the path = its Python fake-quant code.  That code
-    cannot travel to the GPU box, so the oracle port (validated against it, tests/golden/) is
-    timed on all host threads; each step is a bounded row sample of the workload."""
+    """The reference's CPU implementation of the path, timed on all host threads; each step is the same
+    bounded row sample of the workload that `cpu_baseline` of the GPU arm uses."""
     if rank != 0:
         return
     steps = max(1, args.steps)
-    # bounded sample: rows per step sized so that K steps take roughly 20 s of CPU time
-    rows = max(32, min(1024, (76000 // steps) // 32 * 32))
-    threads = os.cpu_count() or 1
-    cases = make_cpu_cases(rows)
-    for _ in range(max(1, min(args.warmup, 3))):
-        cpu_fake_quant_step(rows, cases, threads)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_fake_quant_step(rows, cases, threads)
-    dt = time.perf_counter() - t0
-    val = ops_per_step(rows) * steps / dt / 1e12
-    sample = f"{rows} of {M_TOKENS} token rows per linear per step, {steps} steps (bounded sample)"
+    arm = CpuArm()
+    sec = arm.run(steps, min(args.warmup, 5))
+    val = round(ops_per_step(arm.rows) / sec / 1e12, 4)
     print(json.dumps({
-        "impl": "reference", "metric": "w4a4_qlinear_tops", "value": round(val, 4), "unit": "TOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt / steps * 1e3, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 fake-quant (cpu)",
-        "data": "synthetic", "config": {"workload": "qlinear-8b-m4096", "shapes_KN": SHAPES, "M": M_TOKENS},
-        "cpu_baseline": {"value": round(val, 4), "unit": "TOP/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": round(val, 4), "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "w4a4_qlinear_tops", "value": val, "unit": "TOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16 fake-quant (cpu)", "data": "synthetic", "config": workload_config(world),
+        "cpu_baseline": {"value": val, "unit": "TOP/s", "cores": arm.threads, "kind": arm.kind, "sample": arm.describe(steps)},
+        "e2e": {"value": val, "unit": "TOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
@@ -434,7 +457,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clk.summary(),
     }
     if world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline()
+        out["cpu_baseline"] = cpu_baseline(args.steps)
     print(json.dumps(out))
 
 

@@ -1,9 +1,11 @@
 """Imports the reference's own Python on the CPU (test infrastructure only).
 
-Works only where a SignRot checkout is present (its path in $SIGNROT_REFERENCE, else the
-directory `reference` beside this repository's parent); used by tests/golden/make_golden.py to produce the committed golden
-vectors and by CPU tests that compare the oracle with the reference directly (skipped when
-the checkout is absent, e.g. on the GPU box).
+Works only where the reference's files are present: a SignRot checkout (its path in
+$SIGNROT_REFERENCE, else the directory `reference` beside this repository's parent), else the
+handful of its Python files that oracle/build_ref.py placed under oracle/_ref/ (git-ignored; that
+directory travels to a GPU box with the built libraries).  Used by tests/golden/make_golden.py to
+produce the committed golden vectors and by the CPU legs of bench.py to time the reference's own
+fake-quant forward.
 
 `import signrot` itself fails (signrot/__init__.py:5 imports the unbuilt CUDA extension), so
 empty package objects named `signrot`, `signrot.functional`, ... are registered with
@@ -22,7 +24,16 @@ from pathlib import Path
 
 import torch
 
-REF = Path(os.environ.get("SIGNROT_REFERENCE") or Path(__file__).resolve().parents[2] / "reference")
+def _find_reference() -> Path:
+    cands = [os.environ.get("SIGNROT_REFERENCE"), Path(__file__).resolve().parents[2] / "reference",
+             Path(__file__).resolve().parent / "_ref"]
+    for c in cands:
+        if c and (Path(c) / "signrot" / "functional" / "hadamard.py").exists():
+            return Path(c)
+    return Path(cands[1])
+
+
+REF = _find_reference()
 
 
 def available() -> bool:
@@ -37,9 +48,18 @@ def _sylvester(n: int) -> torch.Tensor:
 
 
 def _hadamard_transform(x, scale=1.0):
+    """Stand-in for fast_hadamard_transform.hadamard_transform: fp32 sums, one rounding to the input
+    dtype.  Up to 2048 points a dense Sylvester product; longer rows as H_a (x) H_b (two dense
+    products of sqrt-size factors), which is the same transform with fewer operations."""
     n = x.shape[-1]
-    y = torch.nn.functional.linear(x.float(), _sylvester(n)) * float(scale)
-    return y.to(x.dtype)
+    if n <= 2048:
+        y = torch.nn.functional.linear(x.float(), _sylvester(n)) * float(scale)
+        return y.to(x.dtype)
+    a = 1 << ((n.bit_length() - 1) // 2)
+    b = n // a
+    xf = x.float().reshape(-1, a, b)
+    y = torch.matmul(_sylvester(a), torch.matmul(xf, _sylvester(b))) * float(scale)
+    return y.reshape(x.shape).to(x.dtype)
 
 
 _installed = False
