@@ -47,6 +47,14 @@ int sr_version(void);
  * synchronises with the device; it is meant for tests and health checks. */
 int sr_device_status(int *status, int clear);
 
+/* Health check of the bounded-wait machinery: one thread of a one-CTA kernel waits `budget_cycles`
+ * (1e3 .. 1e7 SM cycles) on a barrier nobody arrives on, gives up, records code 99 in the status word
+ * that sr_device_status reads, and the kernel returns normally.  The status word is per device and
+ * sticky: while it is non-zero the tensor-core GEMM skips its work, so a caller that sees it must read
+ * and clear it (sr_device_status(&s, 1)) before trusting later outputs.  No counterpart in the
+ * reference, whose kernels have no device-side waits. */
+int sr_selftest_bounded_wait(int64_t budget_cycles, void *stream);
+
 /* ------------------------------------------------------------------ int4 GEMM */
 
 /* C[M,N] int32 = A[M,K] * B[N,K]^T, A packed s4 (a_unsigned = 0) or u4 (1), B packed s4.
@@ -94,13 +102,6 @@ int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const vo
 int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
                       const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
                       int64_t num_experts, int64_t N, int64_t K, void *out, void *stream);
-
-/* Pins the GEMM kernel: 0 = choose by shape, 1 = weight-streaming kernel (few rows),
- * 2 = tcgen05 kernel fed by TMA-staged packed tiles, 3 = persistent tcgen05 kernel with
- * register-path unpack, 4 = persistent tcgen05 kernel on CTA pairs (cta_group::2, 256 x 256
- * tiles), 5 = weight-streaming mma.sync kernel for at most 64 rows (larger M falls through to the
- * shape rule).  For tests and tuning; no counterpart in the reference. */
-int sr_set_gemm_kernel(int which);
 
 /* ------------------------------------------------------------------ quantizers */
 
@@ -301,6 +302,17 @@ int sr_batch_decode_i4_merged(void *o, const void *q, void *kv_data, void *kv_pa
                               int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
                               int64_t head_dim, int64_t batch_size, void *tmp, int64_t num_chunks, void *counters,
                               int hadamard_q, void *stream);
+
+/* Bookkeeping of one decode step of a uniform-length batch, done on the device so that it can sit at the
+ * head of a captured decode graph: reads the token count `length` (int32 [1]), writes the position of
+ * the token this step appends (`position`, int64 [1], = count before the step), the page tables of the
+ * sequence including that token (kv_indptr int32 [batch+1], kv_indices int32 [>= batch * pages],
+ * last_page_offset int32 [batch]; page of (request b, logical page j) = j * batch + b) and the new count.
+ * Replaces the host-side refresh the reference's graph runner does between replays
+ * (MultiLayerPagedKVCache4Bit.refresh_specs, signrot/transformers/kv_cache.py:435-487, called from
+ * fake_quant/kernel_utils.py:205-214). */
+int sr_decode_advance(void *length, void *position, void *kv_indptr, void *kv_indices, void *last_page_offset,
+                      int64_t batch_size, int64_t page_size, int64_t max_pages, void *stream);
 
 /* sr_batch_decode_i4 for callers that cannot hand over a workspace.  It has no counterpart in
  * the reference.  Some hosts of this library never get to call cudaMalloc: an inference

@@ -34,7 +34,7 @@ _SIGNATURES = {
     "sr_w4a4_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
     "sr_grouped_linear": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P],
     "sr_matmul_grouped": [_P, _I64, _P, _P, _P, _P, _P, _P, _I, _I64, _P],
-    "sr_set_gemm_kernel": [_I],
+    "sr_selftest_bounded_wait": [_I64, _P],
     "sr_sym_quant_dynamic": [_P, _I64, _I64, _F, _P, _P, _P],
     "sr_asym_quant_dynamic": [_P, _I64, _I64, _F, _P, _P, _P, _P],
     "sr_sym_quant_dynamic_moe": [_P, _P, _P, _I64, _I64, _F, _P, _P, _P],
@@ -64,6 +64,7 @@ _SIGNATURES = {
     "sr_rope_kv_append": [_P] * 8 + [_I64] * 3 + [_P, _P, _I64, _P, _P] + [_I64] * 8 + [_I, _P],
     "sr_batch_decode_i4": [_P] * 7 + [_I64] * 7 + [_P, _I64, _I, _P],
     "sr_batch_decode_i4_merged": [_P] * 7 + [_I64] * 7 + [_P, _I64, _P, _I, _P],
+    "sr_decode_advance": [_P] * 5 + [_I64] * 3 + [_P],
     "sr_batch_decode_i4_static": [_P] * 7 + [_I64] * 7 + [_I64, _I, _P],
 }
 

@@ -71,6 +71,15 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 template <typename T>
 __host__ __device__ __forceinline__ T cdiv(T a, T b) { return (a + b - 1) / b; }
 
+// SM count of the CURRENT device (launch grids are sized by it); the runtime answers from its own cache.
+inline int current_sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n <= 0)
+        return 148;
+    return n;
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
@@ -118,6 +127,41 @@ __device__ __forceinline__ int asym_code(__half x, float rcp, int zero, int lo, 
 // bf16 -> fp16 goes through fp32, the same single rounding torch's .to(float16) does.
 __device__ __forceinline__ __half to_half(__half v) { return v; }
 __device__ __forceinline__ __half to_half(__nv_bfloat16 v) { return __float2half_rn(__bfloat162float(v)); }
+
+// ---------------------------------------------------------------- bounded mbarrier wait
+//
+// No wait in this library spins without a limit.  The poll loop touches nothing but the barrier (any other
+// shared-memory access would compete with operand traffic); the abort flag (shared by the roles of a CTA) and
+// the clock are looked at every 64 polls.  On expiry the waiter raises the abort flag, records `code` in the
+// device status word (first failure wins) and returns false; the caller then leaves its loop and the kernel
+// returns normally, so the context stays usable.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code,
+                                                  long long budget_cycles, int *status_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > budget_cycles) {
+            *abort_flag = code;
+            atomicCAS(status_word, 0, code);
+            return false;
+        }
+    }
+}
 
 union Vec16 {
     uint4 u;

@@ -1,5 +1,5 @@
 // C ABI of the W4A4 GEMMs: argument validation and the choice of kernel by shape (weight-streaming
-// mma.sync kernel for the decode regime, tcgen05 kernels above it, CTA pairs for large M and MoE).
+// mma.sync kernel for the decode regime, the CTA-pair tcgen05 kernel above it and for MoE prefill).
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cstdlib>
@@ -7,25 +7,13 @@
 
 namespace sr {
 
-// 0 = by shape (M <= 32, or M <= 64 and N <= 8192: kernel 5; else kernel 4),
-// 1 = dp4a weight-streaming kernel, 2 = tcgen05 kernel with TMA-staged packed tiles,
-// 3 = persistent tcgen05 kernel with register-path unpack, 4 = persistent CTA-pair (cta_group::2) kernel,
-// 5 = weight-streaming mma.sync kernel of the decode regime (M <= 64).
-// SIGNROT_B200_GEMM=small|tc|tc2|tc3|skinny pins one kernel (used by the parity tests to cover both
-// kernels at every shape); sr_set_gemm_kernel() does the same from code.
-static int g_force = -1;
-static int forced_kernel() {
-    if (g_force < 0) {
-        const char *e = getenv("SIGNROT_B200_GEMM");
-        g_force = 0;
-        if (e && !strcmp(e, "small")) g_force = 1;
-        if (e && !strcmp(e, "tc")) g_force = 2;
-        if (e && !strcmp(e, "tc2")) g_force = 3;
-        if (e && !strcmp(e, "tc3")) g_force = 4;
-        if (e && !strcmp(e, "skinny")) g_force = 5;
-    }
-    return g_force;
-}
+// Kernel choice by shape.  The weight-streaming kernel's mma.sync rate bounds it at about 32 rows; wide outputs go to
+// the tensor-core kernel earlier.
+static bool decode_regime(int64_t M, int64_t N) { return M <= 32 || (M <= 64 && N <= 8192); }
+
+// |a * b| <= 64 for signed codes and <= 120 for unsigned activation codes; the tensor-core kernel carries every product
+// times 256 in its int32 accumulator, so K is bounded by 2^31 / (256 * 64) resp. 2^31 / (256 * 120).
+static int64_t max_k(bool a_unsigned) { return a_unsigned ? 65536 : 131040; }
 
 static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned,
                     const Epilogue &ep, void *stream, const char *who) {
@@ -34,22 +22,13 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     if (M == 0 || N == 0) return SR_OK;
     SR_REQUIRE(K > 0, SR_ERR_INVALID, "%s: K must be positive", who);
     SR_REQUIRE(A && B, SR_ERR_INVALID, "%s: null pointer", who);
-    SR_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K <= 131072, SR_ERR_UNSUPPORTED, "%s: size out of range", who);
+    SR_REQUIRE(M < (1ll << 31) && N < (1ll << 31), SR_ERR_UNSUPPORTED, "%s: size out of range", who);
+    SR_REQUIRE(K <= max_k(a_unsigned != 0), SR_ERR_UNSUPPORTED, "%s: K = %lld exceeds %lld (int32 accumulator range)", who,
+               (long long)K, (long long)max_k(a_unsigned != 0));
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "%s: operands must be 16-byte aligned", who);
-    const int f = forced_kernel();
-    // auto: the mma.sync rate bounds that kernel at about 32 rows; wide outputs go to the tcgen05 kernels earlier
-    if ((f == 5 && M <= 64) || (f == 0 && (M <= 32 || (M <= 64 && N <= 8192))))
-        return launch_gemm_skinny((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
-                                  as_stream(stream));
-    const bool small = f == 1;
-    if (small)
-        return launch_gemm_small((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep,
-                                 as_stream(stream));
-    if (f == 4 || f == 0)
-        return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
-    if (f == 3)
-        return launch_gemm_tc2((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
-    return launch_gemm_tc((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
+    if (decode_regime(M, N))
+        return launch_gemm_skinny((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
+    return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
 }
 
 }  // namespace sr
@@ -57,13 +36,6 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
 using namespace sr;
 
 extern "C" {
-
-int sr_set_gemm_kernel(int which) {
-    SR_REQUIRE(which >= 0 && which <= 5, SR_ERR_INVALID,
-               "set_gemm_kernel: expected 0 (auto), 1 (few rows, dp4a), 2, 3, 4 (tcgen05 kernels) or 5 (few rows, mma)");
-    g_force = which;
-    return SR_OK;
-}
 
 int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned, void *C,
                  void *stream) {
@@ -122,7 +94,8 @@ int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, co
                "grouped_linear: null pointer");
     SR_REQUIRE(a_zero == nullptr || w_sum != nullptr, SR_ERR_INVALID,
                "grouped_linear: asymmetric activations need the int4 row sums of the weights");
-    SR_REQUIRE(K <= 131072, SR_ERR_UNSUPPORTED, "grouped_linear: size out of range");
+    SR_REQUIRE(K <= max_k(a_zero != nullptr), SR_ERR_UNSUPPORTED, "grouped_linear: K = %lld exceeds %lld (int32 accumulator range)",
+               (long long)K, (long long)max_k(a_zero != nullptr));
     Epilogue ep = {};
     ep.mode = 1;
     ep.out = (__half *)out;
@@ -131,10 +104,8 @@ int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, co
     ep.a_zero = (const int8_t *)a_zero;
     ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
     ep.expert_ids = (const int32_t *)expert_ids;
-    // few rows per expert (decode): the weight-streaming kernel; otherwise the CTA-pair tensor-core kernel.
-    // sr_set_gemm_kernel(4 / 5) pins one of them.
-    const int f = forced_kernel();
-    if (f == 5 || (f != 4 && rows <= 16 * num_experts))
+    // few rows per expert (decode): the weight-streaming kernel; otherwise the CTA-pair tensor-core kernel
+    if (rows <= 16 * num_experts)
         return launch_gemm_skinny_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,
                                           (const int32_t *)row_offsets, (int)num_experts, as_stream(stream));
     return launch_gemm_tc3_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,

@@ -137,18 +137,12 @@ __device__ __forceinline__ void store_acc_chunk_warp(const Epilogue &ep, uint32_
     if (!vec) store_acc_chunk(ep, row, col0, v, row_end, N, small);
 }
 
-int launch_gemm_small(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                      const Epilogue &ep, cudaStream_t st);
 int launch_gemm_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                        const Epilogue &ep, cudaStream_t st);
 int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                               const Epilogue &ep, cudaStream_t st);
 int launch_gemm_skinny_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
                                const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st);
-int launch_gemm_tc(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                   const Epilogue &ep, cudaStream_t st);
-int launch_gemm_tc2(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                    const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
                     const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,

@@ -164,13 +164,7 @@ extern "C" int sr_matmul_grouped(const void *problem_sizes, int64_t problem_coun
     if (problem_count == 0) return SR_OK;
     SR_REQUIRE(problem_sizes && ptr_a && ptr_b && ptr_c && lda && ldb && ldc, SR_ERR_INVALID,
                "matmul_grouped: null pointer");
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     auto kfn = signed_a ? gemm_grouped_kernel<false> : gemm_grouped_kernel<true>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul_grouped: cudaFuncSetAttribute: %s", cudaGetErrorString(e));

@@ -300,23 +300,7 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
 // Warps that share one row block.  Two (four blocks in flight per CTA) pays when there are enough blocks to
 // occupy every warp group of the grid and K is short, so that the per-block reduction and epilogue
 // would otherwise weigh as much as the block's own steps; eight otherwise.
-// SIGNROT_B200_SKINNY_GRID=full: every CTA slot gets a CTA even when the row blocks then deal out unevenly (A/B runs)
-static bool skinny_full_grid() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("SIGNROT_B200_SKINNY_GRID");
-        v = (e && !strcmp(e, "full")) ? 1 : 0;
-    }
-    return v == 1;
-}
-
 static int skinny_kw(int64_t blocks, int64_t K, int sm_count, bool grouped = false) {
-    static int forced = -1;
-    if (forced < 0) {
-        const char *e = getenv("SIGNROT_B200_SKINNY_KW");
-        forced = e ? atoi(e) : 0;
-    }
-    if (forced == 2 || forced == 8) return forced;
     // measured: dense launches lose with two (too few blocks for four groups per CTA); the MoE gate/up shape
     // (8 experts x 14336 rows, K = 4096) gains 5 %
     return grouped && K <= 8192 && blocks >= 8ll * sm_count ? 2 : 8;
@@ -326,13 +310,7 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
                          const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "matmul: operands must be 16-byte aligned");
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "matmul: K = %lld must be a multiple of 32", (long long)K);
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const bool grouped = row_off != nullptr;
     // grouped launches: 32 rows per pass (an expert with more rows streams its weights again for the rest)
     const int nt = grouped ? 4 : (M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)));
@@ -346,7 +324,7 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
     // (grouped launches keep every CTA slot: measured 6 % faster on the MoE decode stack than the even deal)
-    else if (!skinny_full_grid() && !grouped) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
+    else if (!grouped) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
 #define SR_SK_KW(NT, MT, GR, KWV)                                                                              \
     do {                                                                                                       \
@@ -388,20 +366,14 @@ int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "w4a4_swiglu: operands must be 16-byte aligned");
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "w4a4_swiglu: K = %lld must be a multiple of 32", (long long)K);
     SR_REQUIRE(ep.mode == 1 && !ep.expert_ids, SR_ERR_INVALID, "w4a4_swiglu: dense dequant epilogue only");
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     const int64_t blocks = cdiv<int64_t>(N, SK_ROWS);
     const int kw = skinny_kw(blocks, K, sm_count);
     const int groups = SK_WARPS / kw;
     int64_t ctas = 2 * (int64_t)sm_count;
     if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
-    else if (!skinny_full_grid()) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
+    else ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
     const unsigned grid = (unsigned)ctas;
 #define SR_SKS_KW(NT, KWV)                                                                                     \
     do {                                                                                                       \

@@ -90,33 +90,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  The poll loop touches nothing but the barrier (every other shared-memory access
-// would compete with the operand traffic); the abort flag and the clock are looked at every 64 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_BUDGET) {
-            *abort_flag = code;
-            atomicCAS(&g_status, 0, code);
-            return false;
-        }
-    }
+    return mbar_wait_bounded(bar, parity, abort_flag, code, WAIT_BUDGET, &g_status);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
     asm volatile(
@@ -518,41 +493,19 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     if (rc) return rc;
     rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)K / 2, BNC);
     if (rc) return rc;
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const int64_t m_tiles = row_off ? cdiv<int64_t>(M, 2 * BMC) + num_experts : cdiv<int64_t>(M, 2 * BMC);
     const int64_t tiles = cdiv<int64_t>(N, BN) * m_tiles;
     int64_t clusters = sm_count / 2;
     if (2 * tiles <= clusters) clusters = 2 * tiles;   // every tile is split into two halves (see the kernel)
     else if (tiles < clusters) clusters = tiles;
-    // SIGNROT_B200_TC3_STAGES="<packed ring>,<int8 ring>,<unpack groups>" is a tuning knob
-    static int sp = 0, su = 0, groups = 0;
-    if (sp == 0) {
-        int a = 5, b = 4, c = 4;
-        const char *env = getenv("SIGNROT_B200_TC3_STAGES");
-        if (env) sscanf(env, "%d,%d,%d", &a, &b, &c);
-        const bool groups_ok = c == 1 || c == 2 || c == 4;
-        // a group may run at most one pass ahead of a ring's barriers: groups <= both ring depths
-        if (a < 2 || a > MAX_STAGES || b < 2 || b > MAX_STAGES || !groups_ok || c > a || c > b ||
-            smem_bytes(a, b) > MAX_SMEM) {
-            a = 5;
-            b = 4;
-            c = 4;
-        }
-        sp = a;
-        su = b;
-        groups = c;
-    }
+    // ring depths: packed (TMA) stages, unpacked int8 stages, unpack warp groups (a group may run at most one
+    // pass ahead of a ring's barriers, so groups <= both depths)
+    constexpr int sp = 5, su = 4, groups = 4;
+    static_assert(groups <= sp && groups <= su, "unpack groups exceed a ring depth");
     void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, const int32_t *, int,
                 Epilogue);
-    if (groups == 1) kfn = a_unsigned ? gemm_tc3_kernel<true, 1> : gemm_tc3_kernel<false, 1>;
-    else if (groups == 2) kfn = a_unsigned ? gemm_tc3_kernel<true, 2> : gemm_tc3_kernel<false, 2>;
-    else kfn = a_unsigned ? gemm_tc3_kernel<true, 4> : gemm_tc3_kernel<false, 4>;
+    kfn = a_unsigned ? gemm_tc3_kernel<true, groups> : gemm_tc3_kernel<false, groups>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     launch_pdl(kfn, dim3((unsigned)(2 * clusters)), dim3(THREADS), smem_bytes(sp, su), st, ma, mb, (uint32_t)M, (uint32_t)N,
@@ -570,6 +523,26 @@ int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, in
     SR_REQUIRE(num_experts >= 1 && num_experts <= tc3::MAX_EXPERTS, SR_ERR_UNSUPPORTED,
                "grouped_linear: at most %d experts", tc3::MAX_EXPERTS);
     return launch_tc3(A, B, rows, N, K, a_unsigned, ep, row_off, num_experts, st);
+}
+
+// One thread waits, with the given cycle budget, on a barrier nobody arrives on: the give-up path of every
+// bounded wait in this file (abort flag, status word, normal return), exercised without any other machinery.
+__global__ void bounded_wait_probe_kernel(long long budget_cycles, int code) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        tc3::mbar_init(tc3::smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_bounded(tc3::smem_u32(&bar), 0, &abort_flag, code, budget_cycles, &tc3::g_status);
+    __syncthreads();
+}
+
+int launch_bounded_wait_probe(long long budget_cycles, cudaStream_t st) {
+    bounded_wait_probe_kernel<<<1, 32, 0, st>>>(budget_cycles, 99);
+    return check_launch("selftest_bounded_wait");
 }
 
 int tc3_device_status(int *out, bool clear) {

@@ -18,6 +18,7 @@
 //    writes the page slot.
 #include "common.cuh"
 #include "kv_cache.cuh"
+#include <atomic>
 #include <cfloat>
 #include <cstdlib>
 #include <cstring>
@@ -608,13 +609,8 @@ static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_par
     __half *op = (__half *)o;
     float *tp = (float *)tmp;
     const uint32_t nc = (uint32_t)num_chunks;
-    // SIGNROT_B200_DECODE=scalar keeps the CUDA-core kernel (A/B runs); default: tensor-core kernel when it applies
-    static int use_tc = -1;
-    if (use_tc < 0) {
-        const char *e = getenv("SIGNROT_B200_DECODE");
-        use_tc = (e && !strcmp(e, "scalar")) ? 0 : 1;
-    }
-    const bool took = use_tc && launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
+    // the tensor-core kernel takes page sizes that are multiples of 16; the CUDA-core kernel the rest
+    const bool took = launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
     if (!took) switch (G) {
         case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
@@ -652,6 +648,45 @@ int sr_batch_decode_i4_merged(void *o, const void *q, void *kv_data, void *kv_pa
                              stream, (int32_t *)counters);
 }
 
+// ------------------------------------------------------------------ decode-step bookkeeping on the device
+//
+// One CTA.  Reads the token count of the (uniform-length) batch, publishes the position of the token
+// this step appends and the page tables of the sequence INCLUDING that token, then stores the new count.
+// Page of (request b, logical page j) = j * batch + b; a request's pages are listed contiguously.
+__global__ void decode_advance_kernel(int32_t *__restrict__ length, int64_t *__restrict__ position,
+                                      int32_t *__restrict__ kv_indptr, int32_t *__restrict__ kv_indices,
+                                      int32_t *__restrict__ last_page_offset, int batch, int page_size, int max_pages) {
+    pdl_trigger();
+    pdl_wait();
+    const int len = *length;
+    __syncthreads();                       // every thread has read the count before thread 0 replaces it
+    const int new_len = min(len + 1, max_pages * page_size);
+    const int pages = (new_len + page_size - 1) / page_size;
+    const int last = new_len - (pages - 1) * page_size;
+    for (int i = threadIdx.x; i <= batch; i += blockDim.x) {
+        kv_indptr[i] = i * pages;
+        if (i < batch) last_page_offset[i] = last;
+    }
+    for (int i = threadIdx.x; i < pages * batch; i += blockDim.x) kv_indices[i] = (i % pages) * batch + i / pages;
+    if (threadIdx.x == 0) {
+        *position = new_len - 1;
+        *length = new_len;
+    }
+}
+
+int sr_decode_advance(void *length, void *position, void *kv_indptr, void *kv_indices, void *last_page_offset,
+                      int64_t batch_size, int64_t page_size, int64_t max_pages, void *stream) {
+    SR_REQUIRE(length && position && kv_indptr && kv_indices && last_page_offset, SR_ERR_INVALID,
+               "decode_advance: null pointer");
+    SR_REQUIRE(batch_size > 0 && page_size > 0 && max_pages > 0 && batch_size * max_pages < (1ll << 30), SR_ERR_INVALID,
+               "decode_advance: bad geometry (batch %lld, page %lld, pages %lld)", (long long)batch_size,
+               (long long)page_size, (long long)max_pages);
+    launch_pdl(decode_advance_kernel, dim3(1), dim3(256), 0, as_stream(stream), (int32_t *)length, (int64_t *)position,
+               (int32_t *)kv_indptr, (int32_t *)kv_indices, (int32_t *)last_page_offset, (int)batch_size,
+               (int)page_size, (int)max_pages);
+    return check_launch("decode_advance");
+}
+
 // ------------------------------------------------------------------ decode without a caller workspace
 //
 // Built-in split-KV workspace for callers that have no way to allocate device memory: a
@@ -663,24 +698,24 @@ static __device__ __align__(256) float g_decode_workspace[SR_DECODE_STATIC_FLOAT
 // In host code `g_decode_workspace` is only a handle for the runtime, not an address a kernel
 // may dereference.  The device address is looked up once per device (with that device current).
 static float *decode_workspace_for_current_device(int *rc) {
-    static float *cached[64] = {nullptr};
+    static std::atomic<float *> cached[64];   // zero-initialised; a racing first call stores the same address
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) {
         *rc = fail(SR_ERR_CUDA, "batch_decode_i4_static: cudaGetDevice: %s", cudaGetErrorString(e));
         return nullptr;
     }
-    if (cached[dev] == nullptr) {
-        float *p = nullptr;
+    float *p = cached[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress((void **)&p, g_decode_workspace);
         if (e != cudaSuccess || p == nullptr) {
             *rc = fail(SR_ERR_CUDA, "batch_decode_i4_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
             return nullptr;
         }
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_release);
     }
     *rc = SR_OK;
-    return cached[dev];
+    return p;
 }
 
 int sr_batch_decode_i4_static(void *o, const void *q, void *kv_data, void *kv_param, const void *kv_indptr,

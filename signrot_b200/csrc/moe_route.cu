@@ -32,8 +32,12 @@ __device__ __forceinline__ void route_token(const __half *__restrict__ logits, u
 #pragma unroll
     for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i) {
         const uint32_t e = lane + 32 * i;
-        p[i] = e < E ? __half2float(logits[(size_t)t * E + e]) : -FLT_MAX;
-        mx = fmaxf(mx, p[i]);
+        float v = e < E ? __half2float(logits[(size_t)t * E + e]) : -FLT_MAX;
+        // non-finite logits (an overflowed router) must still give k valid expert ids: NaN ranks highest, as in
+        // the tensor library's top-k, infinities become the largest finite values
+        v = (v != v) ? FLT_MAX : fminf(fmaxf(v, -FLT_MAX), FLT_MAX);
+        p[i] = v;
+        mx = fmaxf(mx, v);
     }
     mx = warp_max(mx);
     float sum = 0.f;
@@ -68,6 +72,7 @@ __device__ __forceinline__ void route_token(const __half *__restrict__ logits, u
                 bi = oi;
             }
         }
+        bi = min(bi, (int)E - 1);               // always an id a weight stack has
         top_v[j] = bv;
         top_i[j] = bi;
         tot += bv;

@@ -264,13 +264,9 @@ rotate_quant_4096_kernel(const InT *__restrict__ x, const int8_t *__restrict__ s
 }  // namespace
 
 int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
-    // SIGNROT_B200_ROTATE=butterfly keeps the butterfly kernels (A/B runs); default: tensor-core transform first
-    static int use_tc = -1;
-    if (use_tc < 0) {
-        const char *e = getenv("SIGNROT_B200_ROTATE");
-        use_tc = (e && !strcmp(e, "butterfly")) ? 0 : 1;
-    }
-    if (use_tc) {
+    // tensor-core transforms first; the butterfly kernel below takes what they do not: per-row sign tables
+    // (expert ids) at n = 4096
+    {
         int rc = launch_rotate_tc4096(a, st);
         if (rc != SR_ERR_UNSUPPORTED) return rc;
         rc = launch_rotate_heads32(a, st);
@@ -280,13 +276,7 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
                           !a.fp32_mode && (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) &&
                           aligned16(a.x) && aligned4(a.q) && (a.out == nullptr || a.out_dtype == SR_F16);
     if (!shape_ok) return launch_rotate_had28(a, st);  // the other dedicated shape, or SR_ERR_UNSUPPORTED
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const uint32_t ctas_needed = cdiv<uint32_t>(a.rows, ROWS_PER_CTA);
     const uint32_t grid = ctas_needed < (uint32_t)(sm_count * 2) ? ctas_needed : (uint32_t)(sm_count * 2);
 #define SR_RQ(T, ASYM)                                                                                     \

@@ -402,13 +402,7 @@ int launch_rotate_had28(const RotateArgs &a, cudaStream_t st) {
                     a.hadk != nullptr && (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) &&
                     aligned16(a.x) && aligned16(a.q) && (a.out == nullptr || (a.out_dtype == SR_F16 && aligned4(a.out)));
     if (!ok) return SR_ERR_UNSUPPORTED;
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const uint32_t grid = a.rows < (uint32_t)(2 * sm_count) ? a.rows : (uint32_t)(2 * sm_count);
     const bool late = a.clip == 1.f && a.out == nullptr && !a.asym;
 #define SR_H28(T, LATE, ASYM)                                                                                  \

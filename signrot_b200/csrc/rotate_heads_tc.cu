@@ -293,13 +293,7 @@ int launch_rotate_heads32(const RotateArgs &a, cudaStream_t st) {
                           a.expert_ids == nullptr && aligned16(a.x) && aligned16(a.q) &&
                           (a.out == nullptr || (a.out_dtype == SR_F16 && aligned4(a.out)));
     if (!shape_ok) return SR_ERR_UNSUPPORTED;
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = current_sm_count();
     const uint32_t want = cdiv<uint32_t>(a.rows, TC_PAIRS);
     const uint32_t grid = want < (uint32_t)sm_count ? want : (uint32_t)sm_count;
     const float scale4 = a.scale * 4.f;

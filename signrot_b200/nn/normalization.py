@@ -14,10 +14,6 @@ class RMSNorm(torch.nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.dtype == torch.float16:
             return kernel.rmsnorm(x, self.eps, self.mean_dim)
-        return self.forward_reference(x)
-
-    def forward_reference(self, x: torch.Tensor) -> torch.Tensor:
-        dt = x.dtype
-        xf = x.to(torch.float32) if dt == torch.float16 else x
-        var = xf.pow(2).sum(-1, keepdim=True) / self.mean_dim
-        return (xf * torch.rsqrt(var + self.eps)).to(dt)
+        # other dtypes stay in their own precision, as the reference's module does for them
+        inv_rms = torch.rsqrt(x.square().sum(dim=-1, keepdim=True) / self.mean_dim + self.eps)
+        return x * inv_rms

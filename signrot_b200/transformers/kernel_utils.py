@@ -9,7 +9,8 @@ Reference counterparts:
   * `kernel_attention_forward` fake_quant/kernel_utils.py:86-161
   * `kernel_mlp_forward`       fake_quant/kernel_utils.py:352-363
   * `build_paged_cache`        fake_quant/kernel_utils.py:64-83
-  * `GraphedDecoder`, `try_graph_decoder`   fake_quant/kernel_utils.py:164-292
+  * `GraphedDecoder`, `try_graph_decoder`   fake_quant/kernel_utils.py:164-292 (same job, different mechanism:
+                               the per-step bookkeeping is a device node of the graph)
 
 The reference patches these functions onto a Hugging Face model.  Here the same functions drive a
 small self-contained decoder (`KernelDecoderModel`: embedding, N decoder layers, final norm, fp16
@@ -473,103 +474,119 @@ def build_paged_cache(model, batch_size, max_length, page_size=None):
 # ----------------------------------------------------------------------------- graph runner
 
 class GraphedDecoder:
-    """Replays one decode step from a captured CUDA graph.
+    """The decode step as one CUDA graph that needs nothing from the host between replays but the token.
 
-    Everything that changes between tokens lives in fixed buffers refreshed outside the graph:
-    the input token, the cache position (which drives the rotary tables) and the cache's index
-    tensors.  The Python bookkeeping inside the cache's `update` does not run on replay, so the
-    sequence length is advanced here.  Capture writes a throwaway token into the cache and rewinds
-    the length, so the slot is overwritten by the first real step."""
+    The graph's first node is the cache's `advance_on_device` launch: it turns the device-resident token
+    count into the position of the token being appended (which drives the rotary tables) and into the
+    page tables of the sequence that includes it, and increments the count.  The decoder stack follows,
+    reading those tensors.  A replay is therefore `token -> buffer, replay`: no index tensor is rewritten
+    from the host (the reference's runner refreshes position and cache specs from Python before every
+    replay, fake_quant/kernel_utils.py:164-254).  The host keeps its own copy of the length for
+    bookkeeping and re-synchronises the device count only when the two were moved apart (an eager step,
+    a rewind)."""
 
     def __init__(self, model, cache, batch_size):
-        self.model = model
-        self.cache = cache
-        self.inner = getattr(cache, "inner", cache)
-        device = model.get_input_embeddings().weight.device
-        self.input_ids = torch.zeros((batch_size, 1), dtype=torch.long, device=device)
-        self.cache_position = torch.zeros(1, dtype=torch.long, device=device)
+        self.model, self.cache = model, cache
+        self.pool = getattr(cache, "inner", cache)
+        dev = model.get_input_embeddings().weight.device
+        self.token = torch.zeros((batch_size, 1), dtype=torch.long, device=dev)
         self.graph = None
         self.logits = None
+        self._device_length = None          # what the device-resident count holds, as far as the host knows
 
-    def _forward(self):
-        return self.model(self.input_ids, past_key_values=self.cache, use_cache=True,
-                          cache_position=self.cache_position).logits
+    def _sync(self):
+        if self._device_length != self.pool.length:
+            self.pool.sync_device_length()
+            self._device_length = self.pool.length
 
-    def _prepare_step(self):
-        self.cache_position.fill_(self.inner.length)
-        self.inner.length += 1
-        self.inner.refresh_specs()
+    def _body(self):
+        """What gets captured.  The Python side effects of the cache's `update` (host length, first-call
+        flags) run once at capture time and are undone by the caller."""
+        position = self.pool.advance_on_device()
+        return self.model(self.token, past_key_values=self.cache, use_cache=True, cache_position=position).logits
 
-    def capture(self, warmup=3):
-        start_length = self.inner.length
-        self.inner.freeze_specs(True)
+    def capture(self, warmup: int = 2):
+        pool, at = self.pool, self.pool.length
+        if at + 1 > pool.capacity():
+            raise RuntimeError(f"the cache holds {pool.capacity()} tokens per request; no room to capture a step at {at}")
+        pool.freeze_specs(True)             # `update` must not rewrite the tables the device node owns
         try:
-            stream = torch.cuda.Stream()
-            stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(stream):
-                for _ in range(warmup):
-                    self.inner.length = start_length
-                    self._prepare_step()
-                    self._forward()
-            torch.cuda.current_stream().wait_stream(stream)
-            self.inner.length = start_length
-            self._prepare_step()
-            self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self.logits = self._forward()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(warmup):     # first-use work (attribute set-up, lazy buffers) outside the capture
+                    pool.length, self._device_length = at, None
+                    self._sync()
+                    self._body()
+            torch.cuda.current_stream().wait_stream(side)
+            pool.length, self._device_length = at, None
+            self._sync()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = self._body()
+            self.graph = graph
         finally:
-            self.inner.length = start_length
-            self.inner.freeze_specs(False)
+            pool.length = at                # nothing was appended for real: the slot is rewritten by step()
+            pool.freeze_specs(False)
         return self
 
-    def step(self, input_ids):
-        """One decode step; returns the logits buffer (overwritten by the next step)."""
+    def step(self, token):
+        """Appends `token` [B, 1] and returns the logits buffer (overwritten by the next step)."""
         if self.graph is None:
             raise RuntimeError("capture() must run before step()")
-        self.input_ids.copy_(input_ids)
-        self.inner.freeze_specs(True)
-        self._prepare_step()
+        pool = self.pool
+        if pool.length + 1 > pool.capacity():
+            raise RuntimeError(f"the cache is full ({pool.capacity()} tokens per request)")
+        self._sync()
+        self.token.copy_(token)
         self.graph.replay()
-        self.inner.freeze_specs(False)
+        pool.length += 1
+        self._device_length = pool.length
+        pool._spec_page_cnt = None          # the device node rewrote the page list
         return self.logits
 
 
-def _graph_matches_eager(model, cache, decoder, batch_size, probes=2, tol=1e-3):
-    """A captured graph freezes every host-side branch at what the capture inputs selected; check
-    it against the eager step on tokens it has not seen."""
-    inner = decoder.inner
-    device = decoder.input_ids.device
+def replay_matches_eager(model, cache, decoder: GraphedDecoder, probes: int = 2, tol: float = 1e-3) -> bool:
+    """Runs `probes` unseen tokens through the eager step and through a replay from the same cache state and
+    compares the logits.  A capture bakes in every host-side decision taken while it ran (kernel choice,
+    chunk counts, buffer addresses); this is the check that those decisions still hold.  Leaves the cache
+    where it found it.  Also surfaces a device-side bounded-wait failure, which would otherwise turn every
+    later output into garbage without an error."""
+    from .. import _lib
+    pool, at = decoder.pool, decoder.pool.length
     vocab = model.get_input_embeddings().weight.shape[0]
-    start = inner.length
-    try:
-        for _ in range(probes):
-            token = torch.randint(0, vocab, (batch_size, 1), dtype=torch.long).to(device)
-            inner.length = start
-            eager = model(token, past_key_values=cache, use_cache=True).logits.float()
-            inner.length = start
-            graphed = decoder.step(token).float()
-            rel = (graphed - eager).abs().max() / eager.abs().max().clamp(min=1e-6)
-            if not torch.isfinite(rel) or rel.item() > tol:
-                logging.warning(f"CUDA graph output diverges from eager (relative {rel.item():.3e}); "
-                                f"the decode step is not capture-safe")
-                return False
-    finally:
-        inner.length = start
-    return True
+    gen = torch.Generator().manual_seed(at)
+    ok = True
+    for _ in range(probes):
+        token = torch.randint(0, vocab, decoder.token.shape, generator=gen).to(decoder.token.device)
+        pool.length = at
+        want = model(token, past_key_values=cache, use_cache=True).logits.float()
+        pool.length = at
+        got = decoder.step(token).float()
+        worst = ((got - want).abs().max() / want.abs().max().clamp_min(1e-6)).item()
+        if not worst <= tol:                # also catches NaN
+            logging.warning("decode graph replay differs from the eager step by %.3e of the logit range; "
+                            "decoding eagerly", worst)
+            ok = False
+            break
+    pool.length = at
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel gave up a bounded device-side wait; outputs since then are undefined")
+    return ok
 
 
-def try_graph_decoder(model, cache, batch_size, warmup=3, validate=True):
-    """Captures the decode step, or returns None when capture fails or the replay does not
-    reproduce the eager step (the caller then decodes eagerly: same kernels, launched one by one)."""
+def try_graph_decoder(model, cache, batch_size, warmup=2, validate=True):
+    """A captured decoder for `cache`, or None when the step cannot be captured or its replay does not
+    reproduce the eager step (the caller then runs the same kernels launch by launch)."""
     if not torch.cuda.is_available():
         return None
     try:
         decoder = GraphedDecoder(model, cache, batch_size).capture(warmup=warmup)
-    except Exception as exc:
-        logging.warning(f"CUDA graph capture failed, decoding eagerly: {exc}")
+    except Exception as exc:   # capture errors invalidate the stream capture only, not the context
+        logging.warning("decode step could not be captured (%s); decoding eagerly", exc)
         torch.cuda.synchronize()
         return None
-    if validate and not _graph_matches_eager(model, cache, decoder, batch_size):
+    if validate and not replay_matches_eager(model, cache, decoder):
         return None
     return decoder
 
@@ -591,7 +608,12 @@ def generate(model, input_ids, max_new_tokens, page_size=None, use_graph=True):
             logits = model(token, past_key_values=cache).logits
         token = logits[:, -1:].argmax(-1)
         out.append(token)
-    return torch.cat(out, dim=1)
+    tokens = torch.cat(out, dim=1)
+    torch.cuda.synchronize(tokens.device)
+    from .. import _lib
+    if _lib.device_status() != 0:       # per device: the status word lives on the current device
+        raise RuntimeError("a kernel gave up a bounded device-side wait during generation; the tokens are undefined")
+    return tokens
 
 
 # ----------------------------------------------------------------------------- tensor parallelism

@@ -396,6 +396,33 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
         self._set_page_cnt(page_cnt)
         return self._spec_cache
 
+    def device_step_state(self):
+        """Device-resident (token count int32 [1], position int64 [1]) of the decode step, for a captured
+        graph whose first node is `advance_on_device`.  Created on first use; the count is set from the
+        host-side length by `sync_device_length`."""
+        if getattr(self, "_len_dev", None) is None:
+            self._len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._pos_dev = torch.zeros(1, dtype=torch.int64, device=self.device)
+        return self._len_dev, self._pos_dev
+
+    def sync_device_length(self):
+        self.device_step_state()[0].fill_(self.length)
+
+    def advance_on_device(self):
+        """One launch: position of the token about to be appended and the page tables of the sequence that
+        includes it, from the device-resident count, which it then increments (the device twin of
+        `refresh_specs(length + 1)`; capturable).  Returns the position tensor."""
+        length, position = self.device_step_state()
+        _lib.run(self.device, "sr_decode_advance", _lib.ptr(length), _lib.ptr(position), _lib.ptr(self._kv_indptr_buf),
+                 _lib.ptr(self._kv_indices_full), _lib.ptr(self._last_page_offset), self.batch_size, self.page_size,
+                 self.pages.shape[0] // self.batch_size)
+        self._spec_page_cnt = None      # the host-side copy of the page count is stale now
+        return position
+
+    def capacity(self) -> int:
+        """Tokens per request the allocated pages hold."""
+        return (self.pages.shape[0] // self.batch_size) * self.page_size
+
     def freeze_specs(self, frozen=True):
         """While frozen, `update` does not touch the index tensors (graph capture/replay)."""
         self._specs_frozen = frozen

@@ -1,5 +1,6 @@
-"""int4 GEMM kernels (few-rows dp4a kernel and tcgen05 kernel) against the integer oracle:
-int32 accumulators bit-exact, fused dequant epilogue bit-exact."""
+"""int4 GEMM kernels (weight-streaming mma.sync kernel of the decode regime: M <= 32, or M <= 64 with N <= 8192;
+CTA-pair tcgen05 kernel above it) against the integer oracle: int32 accumulators bit-exact, fused dequant
+epilogue bit-exact.  The shapes below reach both kernels."""
 import pytest
 import torch
 
@@ -18,43 +19,38 @@ def _codes(rows, K, seed, lo=-8, hi=8):
 
 
 @pytest.fixture(autouse=True)
-def _auto_kernel():
+def _status_clean():
     yield
-    _lib.call_nostream("sr_set_gemm_kernel", 0)
     assert _lib.device_status() == 0
 
 
 SHAPES = [(1, 4096, 4096), (16, 4096, 4096), (3, 64, 40), (33, 256, 96), (128, 4096, 512), (256, 4096, 4096),
-          (200, 1024, 300), (129, 14336, 264), (512, 2048, 14336), (64, 14336, 256), (16, 14336, 4096)]
+          (200, 1024, 300), (129, 14336, 264), (512, 2048, 14336), (64, 14336, 256), (16, 14336, 4096),
+          (32, 4096, 14336), (33, 4096, 14336), (64, 4096, 8192), (65, 512, 8192), (40, 1024, 9000), (1, 32, 8), (257, 32, 257)]
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
 @pytest.mark.parametrize("M,K,N", SHAPES)
-def test_matmul_si4_bit_exact(which, M, K, N):
-    if which == 1 and M * N * K > 16 * 14336 * 4096 * 4:
-        pytest.skip("few-rows kernel is not meant for this size")
+def test_matmul_si4_bit_exact(M, K, N):
     a, b = _codes(M, K, M + K), _codes(N, K, N + 7)
     A, B = oracle.pack_i4(a), oracle.pack_i4(b)
-    _lib.call_nostream("sr_set_gemm_kernel", which)
     C = kernel.matmul_si4_si4(A.to(DEV), B.to(DEV)).cpu()
     assert _lib.device_status() == 0
     assert torch.equal(C, oracle.matmul_i4(A, B))
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
-def test_matmul_ui4_and_extremes(which):
-    _lib.call_nostream("sr_set_gemm_kernel", which)
-    M, K, N = 130, 1024, 257 + 7
+@pytest.mark.parametrize("M", [130, 24])
+def test_matmul_ui4_and_extremes(M):
+    K, N = 1024, 257 + 7
     a, b = _codes(M, K, 1, 0, 16), _codes(N, K, 2)
     A, B = oracle.pack_codes(a), oracle.pack_i4(b)
     C = kernel.matmul_ui4_si4(A.to(DEV), B.to(DEV)).cpu()
     assert torch.equal(C, oracle.matmul_i4(A, B, a_unsigned=True))
     # worst-case magnitudes: every product 64 (signed) / -120 (unsigned x -8)
-    A = oracle.pack_i4(torch.full((5, 4096), -8, dtype=torch.int32))
+    A = oracle.pack_i4(torch.full((M, 4096), -8, dtype=torch.int32))
     B = oracle.pack_i4(torch.full((40, 4096), -8, dtype=torch.int32))
     C = kernel.matmul_si4_si4(A.to(DEV), B.to(DEV)).cpu()
     assert int(C.min()) == int(C.max()) == 64 * 4096
-    A = oracle.pack_codes(torch.full((5, 4096), 15, dtype=torch.int32))
+    A = oracle.pack_codes(torch.full((M, 4096), 15, dtype=torch.int32))
     C = kernel.matmul_ui4_si4(A.to(DEV), B.to(DEV)).cpu()
     assert int(C.min()) == int(C.max()) == -120 * 4096
 
@@ -84,6 +80,15 @@ def test_w4a4_linear_benchmark_shapes(K, N):
     assert torch.equal(out, kernel.sym_dequant(acc, sa.to(DEV), sw.to(DEV)))
 
 
+def test_k_limit_of_the_int32_accumulator():
+    """Products are carried times 256 by the tensor-core kernel: K is refused where the worst case leaves int32."""
+    A = torch.zeros((1, 131072 // 2), dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="accumulator range"):
+        kernel.matmul_si4_si4(A, A)
+    with pytest.raises(RuntimeError, match="accumulator range"):
+        kernel.matmul_ui4_si4(A[:, : 65568 // 2].contiguous(), A[:, : 65568 // 2].contiguous())
+
+
 def test_matmul_leading_dims_and_empty():
     a, b = _codes(6, 128, 1), _codes(10, 128, 2)
     A, B = oracle.pack_i4(a).view(2, 3, 64), oracle.pack_i4(b)
@@ -94,11 +99,10 @@ def test_matmul_leading_dims_and_empty():
     assert E.shape == (0, 10)
 
 
-@pytest.mark.parametrize("which", [1, 2, 3, 4, 5], ids=["few_rows", "tcgen05", "tcgen05_persistent", "tcgen05_2cta", "few_rows_mma"])
 @pytest.mark.parametrize("M,K,N,asym,bias", [(16, 4096, 4096, False, False), (200, 1024, 264, False, True),
-                                             (130, 2048, 512, True, False), (7, 256, 40, True, True)])
-def test_w4a4_linear_fused_epilogue(which, M, K, N, asym, bias):
-    _lib.call_nostream("sr_set_gemm_kernel", which)
+                                             (130, 2048, 512, True, False), (7, 256, 40, True, True),
+                                             (70, 256, 40, True, True), (16, 1024, 264, False, True), (300, 4096, 4096, True, False)])
+def test_w4a4_linear_fused_epilogue(M, K, N, asym, bias):
     g = torch.Generator().manual_seed(M)
     a = _codes(M, K, 3, 0 if asym else -8, 16 if asym else 8)
     w = _codes(N, K, 4)
@@ -199,3 +203,24 @@ def test_w4a4_swiglu_equals_two_linears_and_swiglu(M, F, K, asym):
     up = kernel.w4a4_linear(packed, w[F:], ws[F:], wsum[F:] if asym else None)
     want = kernel.swiglu(gate, up)
     assert got.shape == (M, F) and torch.equal(got, want)
+
+
+def test_bounded_wait_gives_up_and_the_next_launch_is_clean():
+    """The give-up path of the device-side waits, without provoking anything: a one-thread wait with a budget of
+    1e5 cycles on a barrier nobody arrives on returns, the status word reports its code until it is read and
+    cleared, a GEMM launched while the word is set does no work, and the launch after the clear is correct."""
+    a, b = _codes(300, 512, 1), _codes(264, 512, 2)
+    A, B = oracle.pack_i4(a).to(DEV), oracle.pack_i4(b).to(DEV)
+    want = oracle.matmul_i4(A.cpu(), B.cpu())
+    assert torch.equal(kernel.matmul_si4_si4(A, B).cpu(), want)
+    _lib.call("sr_selftest_bounded_wait", 100000)
+    torch.cuda.synchronize()                       # returns: the kernel ended by itself
+    assert _lib.device_status(clear=False) == 99
+    skipped = kernel.matmul_si4_si4(A, B)          # sticky word: the tensor-core kernel drains without computing
+    torch.cuda.synchronize()
+    del skipped
+    assert _lib.device_status() == 99              # read and clear
+    assert _lib.device_status() == 0
+    assert torch.equal(kernel.matmul_si4_si4(A, B).cpu(), want)
+    with pytest.raises(RuntimeError, match="budget"):
+        _lib.call("sr_selftest_bounded_wait", 10 ** 9)

@@ -71,16 +71,29 @@ def test_dynamic_quant_edge_rows(cols):
 
 
 def test_quantizer_modules_fused_vs_unfused():
-    """nn.Quantizer / AsymQuantizer: fused kernel == forward_reference chain, bit-exact
-    (the criterion of benchmarks/test_fused_equivalence.py:65-74)."""
+    """nn.Quantizer / AsymQuantizer: the fused kernel against the unfused chain (range from the tensor
+    library, then the given-scale quantizer kernels), bit-exact: the criterion and the chain of
+    benchmarks/test_fused_equivalence.py:65-74 and signrot/nn/quantization.py:23-28, 67-76."""
     for rows, cols in [(1, 4096), (8, 11008), (16, 128), (2048, 4096)]:
         x = _x(rows, cols, 11).to(DEV)
         for clip in (1.0, 0.9):
-            a, b = snn.Quantizer(clip_ratio=clip)(x), snn.Quantizer(clip_ratio=clip).forward_reference(x)
-            assert torch.equal(a.quantized_x, b.quantized_x) and torch.equal(a.scales_x, b.scales_x)
-        a, b = snn.AsymQuantizer()(x), snn.AsymQuantizer().forward_reference(x)
-        assert torch.equal(a.quantized_x, b.quantized_x) and torch.equal(a.scales_x, b.scales_x)
-        assert torch.equal(a.zeros_x, b.zeros_x)
+            a = snn.Quantizer(clip_ratio=clip)(x)
+            scales = (x.abs().amax(dim=-1).unsqueeze(1) / 7).to(torch.float16) * clip
+            assert torch.equal(a.scales_x, scales) and torch.equal(a.quantized_x, kernel.sym_quant(x, scales))
+        a = snn.AsymQuantizer()(x)
+        lo, hi = x.amin(dim=-1, keepdim=True), x.amax(dim=-1, keepdim=True)
+        scales = (hi - lo) / 15
+        zeros = (-lo / scales).round()
+        assert torch.equal(a.scales_x, scales) and torch.equal(a.zeros_x, zeros.to(torch.int8))
+        assert torch.equal(a.quantized_x, kernel.asym_quant_f16_ui4(x, scales, zeros))
+    # SymQuantizer applies the clip before the division
+    x = _x(9, 512, 3).to(DEV)
+    b = snn.SymQuantizer(clip_ratio=0.9)(x)
+    want = (x.abs().amax(dim=-1, keepdim=True) * 0.9 / 7).to(torch.float16)
+    assert torch.equal(b.scales_x, want) and torch.equal(b.quantized_x, kernel.sym_quant(x, want))
+    c = snn.SymQuantizer()(x)
+    d = snn.Quantizer()(x)
+    assert torch.equal(c.quantized_x, d.quantized_x) and torch.equal(c.scales_x, d.scales_x)
 
 
 def test_given_scale_quantizers():
