@@ -336,6 +336,36 @@ int sr_batch_decode_i4_static(void *o, const void *q, void *kv_data, void *kv_pa
                               int64_t head_dim, int64_t batch_size, int64_t num_chunks, int hadamard_q,
                               void *stream);
 
+/* ------------------------------------------------------------------ exchanges over peer memory
+ *
+ * Tensor- and expert-parallel groups of up to 8 GPUs on one node.  The reference has no multi-GPU form of
+ * this path (the kernel model must live on one device: fake_quant/kernel_utils.py:365-366), so these entry
+ * points have no counterpart there; they stand where a sharded caller would otherwise put collective-library
+ * calls of a few hundred KB (all-gather of a row-parallel linear's input, all-reduce of its int32 partial
+ * sums, sum of expert-parallel partial outputs).
+ *
+ * Set-up (allocates; not capturable): every rank calls sr_peer_region_bytes, sr_peer_alloc (zeroed device
+ * memory + a 64-byte inter-process handle), sends the handle to its peers (any host channel), and maps their
+ * regions with sr_peer_open.  Tear-down: sr_peer_close on the mapped regions, sr_peer_free on the own one. */
+int sr_peer_region_bytes(int64_t world, int64_t slot_bytes, int64_t *bytes);
+int sr_peer_alloc(int64_t bytes, void **ptr, void *ipc_handle);
+int sr_peer_open(const void *ipc_handle, void **ptr);
+int sr_peer_close(void *ptr);
+int sr_peer_free(void *ptr);
+
+/* One exchange = one kernel on every rank of the group: push the message into every rank's slot with plain
+ * peer stores, raise a flag, wait (bounded; code 60 + rank in sr_device_status if a rank never arrives), then
+ * combine the slots into `out`.  `regions`: host array of `world` device pointers (own region at [rank]).
+ *   mode 0  all-gather of columns: src fp16 [rows, cols] -> out fp16 [rows, world * cols]
+ *   mode 1  integer all-reduce + dequant: src int32 [rows, cols] -> out fp16 [rows, cols] =
+ *           rn_h((float(sum over ranks) * row_scale[m]) * col_scale[n]), the epilogue of sr_w4a4_linear
+ *   mode 2  fp32 all-reduce in rank order: src fp32 [rows, cols] -> out fp16 [rows, cols]
+ * rows * cols * element size must fit `slot_bytes`.  Every rank must issue the same sequence of exchanges;
+ * nothing is allocated or synchronised, the launch is the same every time (capturable). */
+int sr_peer_exchange(int mode, const void *const *regions, int rank, int world, int64_t slot_bytes, const void *src,
+                     int64_t rows, int64_t cols, const void *row_scale, const void *col_scale, void *out,
+                     void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,6 +19,7 @@ int fail(int code, const char *fmt, ...) {
 
 int grouped_device_status(int *out, bool clear);
 int tc3_device_status(int *out, bool clear);
+int peer_device_status(int *out, bool clear);
 int launch_bounded_wait_probe(long long budget_cycles, cudaStream_t st);
 
 }  // namespace sr
@@ -36,7 +37,10 @@ int sr_device_status(int *status, int clear) {
     if (rc) return rc;
     rc = sr::grouped_device_status(&b, clear != 0);
     if (rc) return rc;
-    *status = a ? a : b;
+    int c = 0;
+    rc = sr::peer_device_status(&c, clear != 0);
+    if (rc) return rc;
+    *status = a ? a : (b ? b : c);
     return SR_OK;
 }
 

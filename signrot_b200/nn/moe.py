@@ -50,7 +50,7 @@ class SignRotMoEBlock(torch.nn.Module):
         if had_K is not None:
             had_K = had_K.to(w_gate.device, torch.float32 if fp32_had else torch.float16)
         self.register_buffer("had_K", had_K, persistent=False)
-        self._ep = None                     # (group, first expert, end expert) after shard_experts_
+        self._ep = None                     # (group, first expert, end expert, peer group) after shard_experts_
 
     @staticmethod
     def stack_experts(linears, need_wsum):
@@ -117,13 +117,17 @@ class SignRotMoEBlock(torch.nn.Module):
         else:
             import torch.distributed as dist
             part = kernel.moe_combine(y, weights, inv, row_range=rng, out_fp32=True)
-            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=ep[0])
-            out = part.to(torch.float16)
+            peer = ep[3]
+            if peer is not None and peer.fits(part.shape[0], part.shape[1], 2):
+                out = peer.all_reduce_f32(part)      # one kernel: push, sum in rank order, round
+            else:
+                dist.all_reduce(part, op=dist.ReduceOp.SUM, group=ep[0])
+                out = part.to(torch.float16)
         if dtype != torch.float16:
             out = out.to(dtype)
         return out.view(bsz, seq, hid), router_logits
 
-    def shard_experts_(self, group=None):
+    def shard_experts_(self, group=None, peer=None):
         """Expert parallelism, in place: this rank keeps a contiguous block of num_experts / world experts
         (weights, scales, row sums); router, tokens and the sign table stay replicated.  Every rank routes all
         tokens, computes the rows of its own experts and the weighted partial sums are added across ranks in
@@ -139,5 +143,5 @@ class SignRotMoEBlock(torch.nn.Module):
             t = getattr(self, name)
             if t is not None:
                 setattr(self, name, t[e0:e1].contiguous())
-        self._ep = (group, e0, e1)
+        self._ep = (group, e0, e1, peer)     # peer: signrot_b200.comm.PeerGroup for decode-size sums, or None
         return self

@@ -37,14 +37,22 @@ def shard_range(total: int, rank: int, world: int, align: int = 1):
 
 def all_gather_cat(x: torch.Tensor, sizes, group=None) -> torch.Tensor:
     """Concatenation along the last dimension of every rank's `x` (rank r contributes sizes[r]
-    columns).  Shards of unequal width are padded to the widest one for the collective."""
+    columns).  Equal shards take one collective into one buffer; shards of unequal width are padded to
+    the widest one first."""
     width = max(sizes)
     local = x.contiguous()
     if local.shape[-1] != width:
         local = torch.nn.functional.pad(local, (0, width - local.shape[-1]))
-    parts = [torch.empty_like(local) for _ in sizes]
-    dist.all_gather(parts, local, group=group)
-    return torch.cat([p[..., :w] for p, w in zip(parts, sizes)], dim=-1)
+    world = len(sizes)
+    stacked = torch.empty((world, *local.shape), dtype=local.dtype, device=local.device)
+    if local.is_cuda:
+        dist.all_gather_into_tensor(stacked, local, group=group)
+    else:       # the CPU backend of the plumbing tests has only the list form
+        dist.all_gather(list(stacked.unbind(0)), local, group=group)
+    if min(sizes) == width:
+        # [world, ..., w] -> [..., world * w]
+        return stacked.movedim(0, -2).reshape(*local.shape[:-1], world * width)
+    return torch.cat([stacked[r][..., :w] for r, w in enumerate(sizes)], dim=-1)
 
 
 def _default_ops():
@@ -82,8 +90,9 @@ class RowParallelLinear4bit:
     rank."""
 
     def __init__(self, weight, weight_scales, hadK=None, K_had=1, sign=None, heads=0, clip_ratio=1.0,
-                 group=None, ops=None):
+                 group=None, ops=None, peer=None):
         self.group = group
+        self.peer = peer            # signrot_b200.comm.PeerGroup: one-kernel exchanges for messages that fit its slots
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.ops = ops or _default_ops()
@@ -96,6 +105,10 @@ class RowParallelLinear4bit:
 
     def gather_input(self, x_local):
         sizes = [e - b for b, e in (shard_range(self.k, r, self.world, 64) for r in range(self.world))]
+        peer = self.peer
+        if (peer is not None and min(sizes) == max(sizes) and x_local.dim() == 2 and x_local.dtype == torch.float16
+                and peer.fits(x_local.shape[0], x_local.shape[1], 0)):
+            return peer.all_gather_cols(x_local)
         return all_gather_cat(x_local, sizes, self.group)
 
     def forward(self, x_local):
@@ -104,6 +117,10 @@ class RowParallelLinear4bit:
                                        clip_ratio=self.clip)
         q_slice = packed.quantized_x[..., self.begin // 2:self.end // 2].contiguous()
         acc = self.ops.matmul_si4_si4(q_slice, self.weight)
+        peer = self.peer
+        if self.world > 1 and peer is not None and acc.dim() == 2 and peer.fits(acc.shape[0], acc.shape[1], 1):
+            # push the int32 partials to every peer, sum and dequantize in the same kernel
+            return peer.all_reduce_dequant(acc, packed.scales_x.reshape(-1), self.weight_scales)
         if self.world > 1:
             dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.group)  # int32: exact, order-free
         return self.ops.sym_dequant(acc, packed.scales_x, self.weight_scales)

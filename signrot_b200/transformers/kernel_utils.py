@@ -625,7 +625,7 @@ class TPRowLinear(torch.nn.Module):
     multiplies its K-slice of the codes and the int32 partial sums are all-reduced: integer addition
     is associative, so every TP degree gives the bits of one GPU (`signrot_b200.tp`)."""
 
-    def __init__(self, lin: KernelLinear, group, heads=0):
+    def __init__(self, lin: KernelLinear, group, heads=0, peer=None):
         super().__init__()
         from .. import tp
         had = lin.kernel_hadamard
@@ -636,7 +636,8 @@ class TPRowLinear(torch.nn.Module):
         self.row = tp.RowParallelLinear4bit(
             lin.kernel_module.weight, lin.kernel_module.weight_scales,
             hadK=had.had_rem_dim if full else None, K_had=had.rem_dim if full else 1,
-            sign=had.had_adj_sign if full else None, heads=heads, clip_ratio=lin.kernel_quantizer.clip_ratio, group=group)
+            sign=had.had_adj_sign if full else None, heads=heads, clip_ratio=lin.kernel_quantizer.clip_ratio, group=group,
+            peer=peer)
 
     def forward(self, x_local):
         lead = x_local.shape[:-1]
@@ -646,41 +647,57 @@ class TPRowLinear(torch.nn.Module):
 
 def _slice_linear(lin: KernelLinear, begin, end):
     """Output rows [begin, end) of a projection without an online rotation (column parallelism)."""
-    new = KernelLinear(lin.in_features, end - begin, asym=lin._asym, clip_ratio=lin.kernel_quantizer.clip_ratio)
+    has_bias = lin.kernel_module.bias is not None
+    new = KernelLinear(lin.in_features, end - begin, bias=has_bias, asym=lin._asym, clip_ratio=lin.kernel_quantizer.clip_ratio)
     new = new.to(lin.kernel_module.weight.device)
     new.kernel_module.weight = lin.kernel_module.weight[begin:end].contiguous()
     new.kernel_module.weight_scales = lin.kernel_module.weight_scales[begin:end].contiguous()
+    if has_bias:
+        new.kernel_module.bias = lin.kernel_module.bias[begin:end].contiguous()
     return new
 
 
-def shard_decoder_(model: "KernelDecoderModel", group=None):
-    """Turns a (replicated) dense `KernelDecoderModel` into this rank's tensor-parallel shard, in place:
-    q/k/v and gate/up column-parallel by heads / MLP width (no collective), o_proj and down_proj
-    row-parallel (`TPRowLinear`: one all-gather and one int32 all-reduce each), residual stream,
-    norms, embedding and head replicated, KV cache per rank over its own KV heads.  The reference keeps
-    this path on one device (fake_quant/kernel_utils.py:365-366)."""
+def shard_decoder_(model: "KernelDecoderModel", group=None, peer="auto"):
+    """Turns a (replicated) `KernelDecoderModel` into this rank's shard, in place: q/k/v column-parallel by heads
+    (no collective), o_proj row-parallel (`TPRowLinear`: one gather and one integer reduce), KV cache per rank over
+    its own KV heads; a dense MLP is tensor-parallel the same way (gate/up by width, down_proj row-parallel), a
+    sparse block expert-parallel (`SignRotMoEBlock.shard_experts_`: every rank routes all tokens and computes its
+    own experts, one sum of the partial outputs); residual stream, norms, embedding and head are replicated.
+    `peer`: a `signrot_b200.comm.PeerGroup` for the decode-size exchanges ("auto": one is created on CUDA; None:
+    the collective library only).  The reference keeps this path on one device
+    (fake_quant/kernel_utils.py:365-366)."""
     import torch.distributed as dist
     cfg = model.config
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    if cfg.num_local_experts:
-        raise NotImplementedError("expert-parallel sparse stacks are not built")
     hq, hkv, d, ffn = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
-    if hq % world or hkv % world or (ffn // world) % 64 or ffn % world:
-        raise ValueError(f"{hq} q heads / {hkv} kv heads / MLP width {ffn} do not split {world} ways")
+    sparse = cfg.num_local_experts > 0
+    if hq % world or hkv % world:
+        raise ValueError(f"{hq} q heads / {hkv} kv heads do not split {world} ways")
+    if not sparse and ((ffn // world) % 64 or ffn % world):
+        raise ValueError(f"MLP width {ffn} does not split {world} ways")
+    if sparse and cfg.num_local_experts % world:
+        raise ValueError(f"{cfg.num_local_experts} experts do not split {world} ways")
+    if peer == "auto":
+        peer = None
+        if world > 1 and model.get_input_embeddings().weight.is_cuda:
+            from ..comm import PeerGroup
+            peer = PeerGroup(group)
     ql, kl, fl = hq // world * d, hkv // world * d, ffn // world
     for layer in model.layers:
         at, mlp = layer.self_attn, layer.mlp
-        for name in ("qkv_fused",):
-            if name in at.__dict__:
-                object.__delattr__(at, name)
-        if "gate_up_fused" in mlp.__dict__:
-            object.__delattr__(mlp, "gate_up_fused")
-        o_row = TPRowLinear(at.o_proj, group, heads=hq)
-        down_row = TPRowLinear(mlp.down_proj, group)
+        if "qkv_fused" in at.__dict__:
+            object.__delattr__(at, "qkv_fused")
+        o_row = TPRowLinear(at.o_proj, group, heads=hq, peer=peer)
         at.q_proj = _slice_linear(at.q_proj, rank * ql, (rank + 1) * ql)
         at.k_proj = _slice_linear(at.k_proj, rank * kl, (rank + 1) * kl)
         at.v_proj = _slice_linear(at.v_proj, rank * kl, (rank + 1) * kl)
         at.o_proj = o_row
+        if sparse:
+            mlp.shard_experts_(group, peer=peer)
+            continue
+        if "gate_up_fused" in mlp.__dict__:
+            object.__delattr__(mlp, "gate_up_fused")
+        down_row = TPRowLinear(mlp.down_proj, group, peer=peer)
         mlp.gate_proj = _slice_linear(mlp.gate_proj, rank * fl, (rank + 1) * fl)
         mlp.up_proj = _slice_linear(mlp.up_proj, rank * fl, (rank + 1) * fl)
         mlp.down_proj = down_row
@@ -688,6 +705,7 @@ def shard_decoder_(model: "KernelDecoderModel", group=None):
     from dataclasses import replace
     model.config = replace(cfg, num_attention_heads=hq // world, num_key_value_heads=hkv // world)
     model.tp_world = world
+    model.peer_group = peer
     return model.fuse_projections_()
 
 

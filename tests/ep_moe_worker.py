@@ -37,15 +37,21 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
+    from signrot_b200.comm import PeerGroup
+    peer = PeerGroup()
     for (E, hidden, inter, tokens, asym) in [(8, 512, 768, 64, False), (8, 512, 768, 700, False), (4, 256, 1536, 33, True)]:
         full = block(E, hidden, inter, 2, 11, dev, asym)
         ep = block(E, hidden, inter, 2, 11, dev, asym).shard_experts_()
+        ep_peer = block(E, hidden, inter, 2, 11, dev, asym).shard_experts_(peer=peer)   # sum through peer memory
         assert ep.w_gate.shape[0] == E // world
         x = torch.randn((1, tokens, hidden), generator=torch.Generator().manual_seed(tokens)).half().to(dev)
         want, logits_a = full(x)
         got, logits_b = ep(x)
         assert torch.equal(logits_a, logits_b)
         assert torch.equal(got, want), f"expert-parallel output differs at {(E, hidden, inter, tokens, asym)} on rank {rank}"
+        for it in range(3):
+            got_p, _ = ep_peer(x)
+            assert torch.equal(got_p, want), f"peer-exchange expert-parallel output differs, call {it}, rank {rank}"
     if "--time" in sys.argv:
         # Mixtral-shaped block (8 experts of 14336 x 4096, top-2), 64 and 4096 tokens: milliseconds per forward,
         # one GPU against expert-parallel, max over ranks
@@ -55,7 +61,7 @@ def main():
             res = []
             for blk in (full, None):
                 if blk is None:
-                    blk = full.shard_experts_()      # shard the same block in place (saves memory)
+                    blk = full.shard_experts_(peer=peer)      # shard the same block in place (saves memory)
                 for _ in range(3):
                     blk(x)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
