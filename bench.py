@@ -48,8 +48,9 @@ def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", 0), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -248,91 +249,104 @@ def measure_int8_peak(dev):
     return 2 * n ** 3 / (best * 1e-3) / 1e12
 
 
-def run_ours(args, rank, world, local_rank):
-    import signrot_b200  # noqa: F401  (fails loudly when the library is missing)
-    from signrot_b200 import _lib
-    from signrot_b200.functional import kernel
-    from signrot_b200.functional.hadamard import get_hadK
+class QlinearStep:
+    """One step of the workload on this rank: the three linears, each rotate+quant followed by the W4A4 GEMM.
+    world == 1: straight through the C ABI.  world > 1: tensor-parallel over the group (Megatron split): the
+    (4096, 14336) linear column-parallel (replicated input, N / world output columns per rank), the (14336, 4096)
+    and (4096, 4096) linears row-parallel (K / world input channels per rank: all-gather of the fp16 input shards,
+    full-row rotate+quant on every rank, K-slice GEMM to int32, int32 all-reduce, dequant)."""
 
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    M = M_TOKENS
-    sets = []
-    weights = []
-    for k, n in SHAPES:
-        c = make_linear_case(M, k, n, seed=rank)
-        hadK, K = get_hadK(k)
-        weights.append({"w": c["w_packed"].to(dev), "ws": c["w_scale"].to(dev), "sign": c["sign"].to(dev),
-                        "hadK": hadK.to(dev, torch.float16) if hadK is not None else None, "K": K, "k": k, "n": n,
-                        "x_host": c["x"].pin_memory()})
-    for b in range(NBUF):
-        s = []
-        for w in weights:
-            x = w["x_host"].to(dev)
-            if b:
-                x = x.roll(b, 0).contiguous()
-            s.append({"x": x, "q": torch.empty((M, w["k"] // 2), dtype=torch.uint8, device=dev),
-                      "s": torch.empty((M, 1), dtype=torch.float16, device=dev),
-                      "out": torch.empty((M, w["n"]), dtype=torch.float16, device=dev)})
-        sets.append(s)
-    out_host = [torch.empty((M, w["n"]), dtype=torch.float16).pin_memory() for w in weights]
+    def __init__(self, rank, world, dev):
+        from signrot_b200 import _lib, tp
+        from signrot_b200.functional import kernel
+        from signrot_b200.functional.hadamard import get_hadK
+        self.lib, self._lib, self.kernel = _lib.load(), _lib, kernel
+        self.rank, self.world, self.dev, self.M = rank, world, dev, M_TOKENS
+        self.stream = torch.cuda.current_stream().cuda_stream
+        self.weights, self.sets = [], []
+        M = self.M
+        for k, n in SHAPES:
+            c = make_linear_case(M, k, n, seed=0 if world > 1 else rank)     # the group shares one problem
+            hadK, K = get_hadK(k)
+            w = {"w": c["w_packed"].to(dev), "ws": c["w_scale"].to(dev), "sign": c["sign"].to(dev),
+                 "hadK": hadK.to(dev, torch.float16) if hadK is not None else None, "K": K, "k": k, "n": n,
+                 "scale": kernel.had_scale(k), "x_host": c["x"].pin_memory()}
+            if world > 1:
+                if (k, n) == (4096, 14336):
+                    w["mode"] = "column"
+                    w["tp"] = tp.ColumnParallelLinear4bit(w["w"], w["ws"])
+                else:
+                    w["mode"] = "row"
+                    w["tp"] = tp.RowParallelLinear4bit(w["w"], w["ws"], hadK=w["hadK"], K_had=K, sign=w["sign"])
+                del w["w"]
+            self.weights.append(w)
+        for b in range(NBUF):
+            one = []
+            for w in self.weights:
+                x = w["x_host"].to(dev)
+                if b:
+                    x = x.roll(b, 0).contiguous()
+                if world > 1 and w["mode"] == "row":
+                    x = x[:, w["tp"].begin:w["tp"].end].contiguous()        # this rank's input channels
+                one.append({"x": x, "q": torch.empty((M, w["k"] // 2), dtype=torch.uint8, device=dev),
+                            "s": torch.empty((M, 1), dtype=torch.float16, device=dev),
+                            "out": torch.empty((M, w["n"]), dtype=torch.float16, device=dev) if world == 1 else None})
+            self.sets.append(one)
+        self.launches_per_step = 6 if world == 1 else None
+        self.collective_ms = 0.0
 
-    ptr, lib = _lib.ptr, _lib.load()
-    stream = torch.cuda.current_stream().cuda_stream
-    scale = {w["k"]: kernel.had_scale(w["k"]) for w in weights}
-
-    def launch_rotate(w, b):
-        rc = lib.sr_rotate_quant(ptr(b["x"]), _lib.SR_BF16, M, w["k"], ptr(w["hadK"]), w["K"], scale[w["k"]],
-                                 ptr(w["sign"]), None, 0, 1.0, 0, ptr(b["q"]), ptr(b["s"]), None, None, stream)
+    # ---- one GPU: raw C-ABI launches
+    def rotate(self, w, b, stream=None):
+        ptr = self._lib.ptr
+        rc = self.lib.sr_rotate_quant(ptr(b["x"]), self._lib.SR_BF16, self.M, w["k"], ptr(w["hadK"]), w["K"], w["scale"],
+                                      ptr(w["sign"]), None, 0, 1.0, 0, ptr(b["q"]), ptr(b["s"]), None, None,
+                                      stream or self.stream)
         if rc:
-            raise RuntimeError(lib.sr_last_error().decode())
+            raise RuntimeError(self.lib.sr_last_error().decode())
 
-    def launch_rotate_on(w, b, strm):
-        rc = lib.sr_rotate_quant(ptr(b["x"]), _lib.SR_BF16, M, w["k"], ptr(w["hadK"]), w["K"], scale[w["k"]],
-                                 ptr(w["sign"]), None, 0, 1.0, 0, ptr(b["q"]), ptr(b["s"]), None, None, strm)
+    def gemm(self, w, b):
+        ptr = self._lib.ptr
+        rc = self.lib.sr_w4a4_linear(ptr(b["q"]), ptr(b["s"]), None, ptr(w["w"]), ptr(w["ws"]), None, None, self.M,
+                                     w["n"], w["k"], ptr(b["out"]), self.stream)
         if rc:
-            raise RuntimeError(lib.sr_last_error().decode())
+            raise RuntimeError(self.lib.sr_last_error().decode())
 
-    def launch_gemm(w, b):
-        rc = lib.sr_w4a4_linear(ptr(b["q"]), ptr(b["s"]), None, ptr(w["w"]), ptr(w["ws"]), None, None, M, w["n"],
-                                w["k"], ptr(b["out"]), stream)
-        if rc:
-            raise RuntimeError(lib.sr_last_error().decode())
+    def run(self, i, ev=None):
+        bufs = self.sets[i % NBUF]
+        for j, (w, b) in enumerate(zip(self.weights, bufs)):
+            if self.world == 1:
+                if ev is not None:
+                    ev[j][0].record()
+                self.rotate(w, b)
+                if ev is not None:
+                    ev[j][1].record()
+                self.gemm(w, b)
+                if ev is not None:
+                    ev[j][2].record()
+            elif w["mode"] == "column":
+                packed = self.kernel.rotate_quant(b["x"], w["hadK"], w["K"], sign=w["sign"])
+                b["y"] = w["tp"].forward(packed)                      # [M, N / world], stays sharded
+            else:
+                b["y"] = w["tp"].forward(b["x"])                      # [M, N] on every rank
 
-    def step(i, ev=None):
-        bufs = sets[i % NBUF]
-        for j, (w, b) in enumerate(zip(weights, bufs)):
-            if ev is not None:
-                ev[j][0].record()
-            launch_rotate(w, b)
-            if ev is not None:
-                ev[j][1].record()
-            launch_gemm(w, b)
-            if ev is not None:
-                ev[j][2].record()
+    def h2d_bytes(self):
+        return sum(b["x"].numel() * 2 for b in self.sets[0])
 
-    int8_peak = measure_int8_peak(dev) if rank == 0 else None
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if _lib.device_status() != 0:
-        raise RuntimeError("a kernel reported a device-side failure during warm-up")
+    def d2h_bytes(self):
+        return sum(self.M * w["n"] * 2 // self.world for w in self.weights)
 
-    # ---- timed region: exactly `steps` steps, device time, per-kernel events inside
-    # per-kernel events on every EV_EVERY-th step of the timed region (an event record between two launches keeps
-    # the second kernel's set-up from overlapping the first one's tail, so instrumenting every step would slow
-    # the thing being measured); SIGNROT_BENCH_EVENTS_EVERY=1 instruments all steps
-    ev_every = max(1, int(os.environ.get("SIGNROT_BENCH_EVENTS_EVERY", "8")))
-    sampled = [i for i in range(args.steps) if i % ev_every == 0]
-    evs = {i: [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SHAPES] for i in sampled}
+
+def timed_steps(step, steps, world, dev, local_rank, evs=None):
+    """Exactly `steps` steps between two events, bracketed by a barrier and a device synchronise; the slowest
+    rank's device time.  Returns (ms, clock summary)."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize()
     with ClockSampler(local_rank) as clk:
         e0.record()
-        for i in range(args.steps):
-            step(i, evs.get(i))
+        for i in range(steps):
+            step.run(i, evs.get(i) if evs else None)
         e1.record()
         torch.cuda.synchronize()
     if world > 1:
@@ -342,40 +356,83 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([ms], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = t.item()
+    return ms, clk.summary()
+
+
+def run_ours(args, rank, world, local_rank):
+    import signrot_b200  # noqa: F401  (fails loudly when the library is missing)
+    from signrot_b200 import _lib
+    from signrot_b200.functional import kernel
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    M = M_TOKENS
+    step = QlinearStep(rank, world, dev)
+    weights, sets = step.weights, step.sets
+
+    int8_peak = measure_int8_peak(dev) if rank == 0 else None
+    for i in range(args.warmup):
+        step.run(i)
+    torch.cuda.synchronize()
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during warm-up")
+
+    # ---- timed region: exactly `steps` steps, device time.  On one GPU per-kernel events sit inside it on every
+    # 8th step (an event record between two launches keeps the second kernel's set-up from overlapping the first
+    # one's tail, so instrumenting every step would slow the thing being measured).
+    ev_every = 8
+    sampled = [i for i in range(args.steps) if i % ev_every == 0] if world == 1 else []
+    evs = {i: [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in SHAPES] for i in sampled}
+    ms, clocks = timed_steps(step, args.steps, world, dev, local_rank, evs)
     if _lib.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure during the timed region")
 
-    rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in sampled) / len(sampled) for j in range(3)]
-    gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in sampled) / len(sampled) for j in range(3)]
+    # ---- the same step back to back for a few seconds: what the path sustains under the power cap, with the
+    # SM clock sampled beside it (nothing about the GPU is changed; NVML is only read)
+    sus_steps = max(args.steps, int(3000.0 / max(ms / args.steps, 1e-3)))
+    sus_steps = min(sus_steps, 20000)
+    sus_ms, sus_clocks = timed_steps(step, sus_steps, world, dev, local_rank)
 
-    # ---- the rotation kernels back to back (no GEMM, no launch gap between dependent kernels): one CUDA graph of
-    # 16 launches per shape over the rotating input sets, replayed once under CUDA events.  The in-step figures
-    # above include the gap between a GEMM and the rotation that follows it.
-    rot_only_ms = []
-    try:
-        seen = []
-        for j, w in enumerate(weights):
-            bufs = [sets[b][jj] for b in range(NBUF) for jj, ww in enumerate(weights) if ww["k"] == w["k"]]
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                for i in range(16):
-                    launch_rotate_on(w, bufs[i % len(bufs)], torch.cuda.current_stream().cuda_stream)
-            gr.replay()
-            torch.cuda.synchronize()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g0.record()
-            gr.replay()
-            g1.record()
-            torch.cuda.synchronize()
-            rot_only_ms.append(g0.elapsed_time(g1) / 16)
-    except Exception:
+    rot_ms = gemm_ms = rot_only_ms = None
+    if world == 1:
+        rot_ms = [sum(evs[i][j][0].elapsed_time(evs[i][j][1]) for i in sampled) / len(sampled) for j in range(3)]
+        gemm_ms = [sum(evs[i][j][1].elapsed_time(evs[i][j][2]) for i in sampled) / len(sampled) for j in range(3)]
+        # the rotation kernels back to back (no GEMM, no launch gap between dependent kernels): one CUDA graph of
+        # 16 launches per shape over the rotating input sets, replayed once under CUDA events
         rot_only_ms = []
+        try:
+            for j, w in enumerate(weights):
+                bufs = [sets[b][jj] for b in range(NBUF) for jj, ww in enumerate(weights) if ww["k"] == w["k"]]
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    for i in range(16):
+                        step.rotate(w, bufs[i % len(bufs)], torch.cuda.current_stream().cuda_stream)
+                gr.replay()
+                torch.cuda.synchronize()
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record()
+                gr.replay()
+                g1.record()
+                torch.cuda.synchronize()
+                rot_only_ms.append(g0.elapsed_time(g1) / 16)
+        except Exception:
+            rot_only_ms = []
 
     # ---- end to end through the public API from pinned host memory.  Every step copies its inputs host -> device
     # and its outputs device -> host; the two directions of the link run at the same time (three streams: copy-in,
-    # compute, copy-out, ordered by events, one device buffer per linear), as a serving loop would drive it.
+    # compute, copy-out, ordered by events, one device buffer per linear), as a serving loop would drive it.  With
+    # several ranks every rank copies the input channels it owns and 1 / world of the output rows.
     s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    x_dev = [torch.empty_like(w["x_host"], device=dev) for w in weights]
+    x_host = []
+    for w in weights:
+        xh = w["x_host"]
+        if world > 1 and w["mode"] == "row":
+            xh = xh[:, w["tp"].begin:w["tp"].end].contiguous().pin_memory()
+        x_host.append(xh)
+    x_dev = [torch.empty_like(xh, device=dev) for xh in x_host]
+    rows_out = M // world
+    out_host = [torch.empty((rows_out, w["n"] // (world if world > 1 and w["mode"] == "column" else 1)),
+                            dtype=torch.float16).pin_memory() for w in weights]
     ev_x_ready = [torch.cuda.Event() for _ in weights]
     ev_x_free = [torch.cuda.Event() for _ in weights]
     ev_y_ready = [torch.cuda.Event() for _ in weights]
@@ -386,18 +443,29 @@ def run_ours(args, rank, world, local_rank):
         for j, (w, oh) in enumerate(zip(weights, out_host)):
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_x_free[j])
-                x_dev[j].copy_(w["x_host"], non_blocking=True)
+                x_dev[j].copy_(x_host[j], non_blocking=True)
                 ev_x_ready[j].record(s_in)
             with torch.cuda.stream(s_comp):
                 s_comp.wait_event(ev_x_ready[j])
-                pk = kernel.rotate_quant(x_dev[j], w["hadK"], w["K"], sign=w["sign"])
-                ev_x_free[j].record(s_comp)
-                s_comp.wait_event(ev_y_done[j])      # the previous result of this linear has left the device
-                y = kernel.w4a4_linear(pk, w["w"], w["ws"])
+                if world == 1:
+                    pk = kernel.rotate_quant(x_dev[j], w["hadK"], w["K"], sign=w["sign"])
+                    ev_x_free[j].record(s_comp)
+                    s_comp.wait_event(ev_y_done[j])      # the previous result of this linear has left the device
+                    y = kernel.w4a4_linear(pk, w["w"], w["ws"])
+                elif w["mode"] == "column":
+                    pk = kernel.rotate_quant(x_dev[j], w["hadK"], w["K"], sign=w["sign"])
+                    ev_x_free[j].record(s_comp)
+                    s_comp.wait_event(ev_y_done[j])
+                    y = w["tp"].forward(pk)
+                else:
+                    s_comp.wait_event(ev_y_done[j])
+                    y = w["tp"].forward(x_dev[j])
+                    ev_x_free[j].record(s_comp)
                 ev_y_ready[j].record(s_comp)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_y_ready[j])
-                oh.copy_(y, non_blocking=True)
+                part = y if world == 1 else y[rank * rows_out:(rank + 1) * rows_out]
+                oh.copy_(part, non_blocking=True)
                 ev_y_done[j].record(s_out)
                 y.record_stream(s_out)
             y_keep[j] = y
@@ -415,47 +483,91 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([e2e_s], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_s = t.item()
+    h2d = sum(xh.numel() * 2 for xh in x_host)
+    d2h = sum(oh.numel() * 2 for oh in out_host)
+    del x_dev, y_keep, step, sets
+    torch.cuda.empty_cache()
+
+    # ---- the full-model and sparse-stack configurations at this group size (decode tokens/s)
+    extras = {}
+    if not args.no_models:
+        for key, fn in (("decode_llama3_8b", lambda: run_decode_model("decode_model_llama3_8b", {}, 8, 2048, 128, dev, world,
+                                                                     quiet=True)),
+                        ("decode_mixtral_8x7b_shape", lambda: run_decode_model(
+                            "decode_model_mixtral_8x7b_shape",
+                            {"num_local_experts": 8, "num_experts_per_tok": 2, "vocab_size": 32000}, 64, 64, 64, dev,
+                            world, quiet=True, prefill_probe=4096))):
+            try:
+                extras[key] = fn()
+            except Exception as exc:
+                extras[key] = {"error": str(exc)[:300]}
+            torch.cuda.empty_cache()
 
     if rank != 0:
         return
     pk_ = peaks()
     ops = ops_per_step()
-    value = world * ops * args.steps / (ms * 1e-3) / 1e12
-    gemm_ops = [2 * M * n * k for k, n in SHAPES]
-    gemm_ach = sum(gemm_ops) / (sum(gemm_ms) * 1e-3) / 1e12
-    rot_bytes = [M * k * 2 + M * k // 2 + M * 2 + k for k, _ in SHAPES]
-    rot_ach = sum(rot_bytes) / (sum(rot_ms) * 1e-3) / 1e9
+    # one GPU: `world` is 1.  Several GPUs: the group shares ONE problem (strong scaling), so the job's work is `ops`.
+    value = ops * args.steps / (ms * 1e-3) / 1e12
+    sus_value = ops * sus_steps / (sus_ms * 1e-3) / 1e12
     out = {
         "metric": "w4a4_qlinear_tops", "value": round(value, 2), "unit": "TOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, int8 tensor-core MMA, int32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": "qlinear-8b-m4096", "M": M, "shapes_KN": SHAPES, "activations": "bf16",
-                   "output": "fp16", "parallelism": f"rows x{world} (no collective)",
-                   "l2": f"inputs larger than L2: {NBUF} rotating buffer sets of 368 MB",
-                   "kernel_events": f"per-kernel CUDA events on every {ev_every}th step of the timed region"},
-        "roofline": {"kernel": "gemm_tc3_kernel (persistent tcgen05 cta_group::2 kind::i8, 256x256 tile per CTA pair, TMA-staged packed tiles, fused dequant)", "bound": "tensor",
-                     "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
-                     "frac": round(gemm_ach / int8_peak, 4),
-                     "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",
-                     "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "traffic": 106.75e6, "traffic_note": "dram read+write of one M=4096 K=4096 N=14336 launch under ncu (profiles/gemm_tc3_kernel_m4096_k4096_n14336.md); algorithmic 155 MB, the rest of the fp16 output is still in L2 when the kernel ends",
-                     "per_shape_ms": [round(v, 4) for v in gemm_ms],
-                     "per_shape_tops": [round(o / (t * 1e-3) / 1e12, 1) for o, t in zip(gemm_ops, gemm_ms)]},
-        "rotate_quant": {"kernel": "fused rotate+sign+quant", "bound": "hbm", "achieved": round(rot_ach, 1),
-                         "peak": pk_["hbm_gbs"], "unit": "GB/s", "frac": round(rot_ach / pk_["hbm_gbs"], 4),
-                         "peak_source": pk_["source"], "per_shape_ms": [round(v, 4) for v in rot_ms],
-                         "per_shape_gbs": [round(b / (t * 1e-3) / 1e9, 1) for b, t in zip(rot_bytes, rot_ms)],
-                         "back_to_back": ({"per_shape_ms": [round(v, 4) for v in rot_only_ms],
-                                           "achieved": round(sum(rot_bytes) / (sum(rot_only_ms) * 1e-3) / 1e9, 1),
-                                           "frac": round(sum(rot_bytes) / (sum(rot_only_ms) * 1e-3) / 1e9 / pk_["hbm_gbs"], 4),
-                                           "note": "CUDA-graph replay of 16 launches per shape, inputs rotate over > 126 MB"}
-                                          if len(rot_only_ms) == 3 else None)},
-        "e2e": {"value": round(world * ops * e2e_steps / e2e_s / 1e12, 3), "unit": "TOP/s",
-                "h2d_bytes_per_step": sum(M * k * 2 for k, _ in SHAPES),
-                "d2h_bytes_per_step": sum(M * n * 2 for _, n in SHAPES), "steps": e2e_steps},
-        "gpu_launches": 6 * args.steps,
-        "clocks": clk.summary(),
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None,
+        "dtype": "int4 codes, int8 tensor-core MMA, int32 accumulate", "data": "synthetic",
+        "config": workload_config(world),
+        "sustained": {"tops": round(sus_value, 2), "ms_per_step": round(sus_ms / sus_steps, 4), "steps": sus_steps,
+                      "seconds": round(sus_ms * 1e-3, 2), "sm_mhz_median": sus_clocks.get("sm_mhz"),
+                      "samples": sus_clocks.get("samples"), "reasons": sus_clocks.get("reasons"),
+                      "power_w_max": sus_clocks.get("power_w_max"),
+                      "tops_at_max_clock": (round(sus_value * sus_clocks["sm_max_mhz"] / sus_clocks["sm_mhz"], 2)
+                                            if sus_clocks.get("sm_mhz") and sus_clocks.get("sm_max_mhz") else None),
+                      "note": "the same step back to back; tops_at_max_clock scales by max / median sampled SM clock"},
+        "e2e": {"value": round(ops * e2e_steps / e2e_s / 1e12, 3), "unit": "TOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "note": "bytes per rank" if world > 1 else "host buffers in, host buffers out"},
+        "clocks": clocks,
     }
+    if world == 1:
+        gemm_ops = [2 * M * n * k for k, n in SHAPES]
+        gemm_ach = sum(gemm_ops) / (sum(gemm_ms) * 1e-3) / 1e12
+        rot_bytes = [M * k * 2 + M * k // 2 + M * 2 + k for k, _ in SHAPES]
+        rot_ach = sum(rot_bytes) / (sum(rot_ms) * 1e-3) / 1e9
+        sus_peak = 2 * pk_.get("bf16_tflops_sustained", 0) or None
+        out["gpu_launches"] = 6 * args.steps
+        out["config"]["kernel_events"] = f"per-kernel CUDA events on every {ev_every}th step of the timed region"
+        out["roofline"] = {
+            "kernel": "gemm_tc3_kernel (persistent tcgen05 cta_group::2 kind::i8, 256x256 tile per CTA pair, TMA-staged packed tiles, fused dequant)",
+            "bound": "tensor", "achieved": round(gemm_ach, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
+            "frac": round(gemm_ach / int8_peak, 4),
+            "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",
+            "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "frac_of_bf16_x2": round(gemm_ach / (2 * pk_["bf16_tflops"]), 4),
+            "traffic": None,
+            "traffic_note": "not measured in this run; one ncu capture of the M=4096 K=4096 N=14336 launch read 106.75 MB "
+                            "of DRAM traffic against 155 MB algorithmic (profiles/gemm_tc3_kernel_m4096_k4096_n14336.md: part "
+                            "of the fp16 output is still in L2 when the kernel ends)",
+            "per_shape_ms": [round(v, 4) for v in gemm_ms],
+            "per_shape_tops": [round(o / (t * 1e-3) / 1e12, 1) for o, t in zip(gemm_ops, gemm_ms)]}
+        # in the sustained run the step is GEMM-dominated; its whole-step rate against 2 x the sustained bf16 figure
+        if sus_peak:
+            out["sustained"]["step_frac_of_bf16_sustained_x2"] = round(sus_value / sus_peak, 4)
+        out["rotate_quant"] = {
+            "kernel": "fused rotate+sign+quant", "bound": "hbm", "achieved": round(rot_ach, 1),
+            "peak": pk_["hbm_gbs"], "unit": "GB/s", "frac": round(rot_ach / pk_["hbm_gbs"], 4),
+            "peak_source": pk_["source"], "per_shape_ms": [round(v, 4) for v in rot_ms],
+            "per_shape_gbs": [round(b / (t * 1e-3) / 1e9, 1) for b, t in zip(rot_bytes, rot_ms)],
+            "back_to_back": ({"per_shape_ms": [round(v, 4) for v in rot_only_ms],
+                              "achieved": round(sum(rot_bytes) / (sum(rot_only_ms) * 1e-3) / 1e9, 1),
+                              "frac": round(sum(rot_bytes) / (sum(rot_only_ms) * 1e-3) / 1e9 / pk_["hbm_gbs"], 4),
+                              "note": "CUDA-graph replay of 16 launches per shape, inputs rotate over > 126 MB"}
+                             if rot_only_ms and len(rot_only_ms) == 3 else None)}
+    else:
+        out["gpu_launches"] = 10 * args.steps      # per rank: 3 rotate+quant, 3 GEMM, 2 code-slice copies, 2 dequant
+        out["roofline"] = {"kernel": "gemm_tc3_kernel on the per-rank shards", "bound": "tensor", "achieved": None,
+                           "peak": round(int8_peak, 1), "unit": "TOP/s", "frac": None, "traffic": None,
+                           "note": "per-kernel events are taken on one GPU only; at this size the step is bound by the "
+                                   "int32 all-reduce and the fp16 all-gather of the row-parallel linears"}
+    out.update(extras)
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(args.steps)
     print(json.dumps(out))
@@ -588,9 +700,9 @@ def _time_cuda(fn, iters=30, warmup=5, graph=True):
 
 
 def run_sweep():
-    """Secondary measurements (one JSON line each, not the headline): the fused-op sweep of
-    BASELINE config 2 at M in {1, 16, 256, 4096}, decode attention of config 3, one Mixtral-shaped
-    MoE block of config 5 at 64 and 4096 tokens.  Each timing is the mean of 30 launches after 5
+    """Secondary measurements (one JSON line each, not the headline): the fused-op sweep at M in
+    {1, 16, 256, 4096} over the three Llama-3-8B linear shapes, int4-KV decode attention at batch 16 and
+    context 4096, one Mixtral-shaped MoE block at 64 and 4096 tokens.  Each timing is the mean of 30 launches after 5
     warm-ups, replayed from a CUDA graph; small cases re-use L2-resident buffers, so they measure L2 behaviour."""
     import signrot_b200  # noqa: F401
     from signrot_b200.functional import kernel
@@ -616,7 +728,7 @@ def run_sweep():
                               "gemm_tops": round(2 * m * n * k / t_gemm / 1e9, 1),
                               "gemm_gbs": round(w_bytes / t_gemm / 1e6, 1),
                               "gemm_frac_hbm": round(w_bytes / t_gemm / 1e6 / hbm, 3)}))
-    # config 3: int4-KV GQA decode attention, B=16, ctx 4096, 32 q / 8 kv heads, page 256
+    # int4-KV GQA decode attention, B=16, ctx 4096, 32 q / 8 kv heads, page 256
     from signrot_b200.transformers import kv_cache as kvc
     B, Hq, Hkv, T, page = 16, 32, 8, 4096, 256
     cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 64, dev, 1, Hkv, 128, group_size=Hq // Hkv)
@@ -637,7 +749,7 @@ def run_sweep():
                       "chunks": chunks, "decode_us": round(t_dec * 1e3, 2),
                       "kv_gbs": round(kv_bytes / t_dec / 1e6, 1), "frac_hbm": round(kv_bytes / t_dec / 1e6 / hbm, 3),
                       "prefill_append_quant_us": round(t_fill * 1e3, 1)}))
-    # config 4 (one layer of it): decode step of a Llama-3-8B-shaped decoder layer, batch 16 at context 4096,
+    # one layer of the full model: decode step of a Llama-3-8B-shaped decoder layer, batch 16 at context 4096,
     # int4 weights + int4 paged KV cache, every operator from this package, replayed from one CUDA graph
     decode_layer = build_decode_layer(cache, B, Hq, Hkv, dev)
     hid, ffn, D = 4096, 14336, 128
@@ -651,7 +763,7 @@ def run_sweep():
     except Exception as e:  # the sweep is secondary: report and go on
         print(json.dumps({"case": "decode_step_llama3_8b_layer", "error": str(e)[:200]}))
     cache.freeze_specs(False)
-    # config 5: one Mixtral-8x7B-shaped MoE block (8 experts, top-2, hidden 4096, ffn 14336)
+    # one Mixtral-8x7B-shaped MoE block (8 experts, top-2, hidden 4096, ffn 14336)
     from signrot_b200 import nn as snn
     E, hid, ffn, top_k = 8, 4096, 14336, 2
     gen = torch.Generator().manual_seed(1)
@@ -673,7 +785,7 @@ def run_sweep():
                           "tops": round(2 * 3 * tokens * top_k * ffn * hid / t_moe / 1e9, 1)}))
     del blk, cache
     torch.cuda.empty_cache()
-    # configs 4 and 5 end to end: the whole 32-layer stack through the decode-graph glue
+    # the whole 32-layer stacks (dense and sparse) through the decode-graph glue
     for name, kw, bsz, prompt, steps in (
             ("decode_model_llama3_8b", {}, 8, 2048, 128),
             ("decode_model_mixtral_8x7b_shape", {"num_local_experts": 8, "num_experts_per_tok": 2, "vocab_size": 32000},
@@ -684,62 +796,108 @@ def run_sweep():
             print(json.dumps({"case": name, "error": str(e)[:300]}))
 
 
-def run_decode_model(name, cfg_kwargs, bsz, prompt, steps, dev):
-    """Full decoder stack (BASELINE configs 4 and 5): random-init int4 weights, int4 paged KV cache,
-    prefill of `prompt` tokens per request, then `steps` decode steps replayed from one CUDA graph.
-    Prints one JSON line: decode tokens/s (bsz * steps / device time), prefill tokens/s, and the bytes of
-    weights + cache a decode step must read against the measured HBM figure."""
+def run_decode_model(name, cfg_kwargs, bsz, prompt, steps, dev, world=1, quiet=False, prefill_probe=0):
+    """Full decoder stack (the full-model and sparse-stack configurations): random-init int4 weights, int4 paged KV
+    cache, prefill of `prompt` tokens per request, then `steps` decode steps replayed from one CUDA graph.
+    world > 1: the stack is sharded over the process group first (`shard_decoder_`: attention tensor-parallel by
+    heads, dense MLP tensor-parallel, sparse block expert-parallel; decode-size exchanges over peer memory, prefill
+    through the collective library), timed as the slowest rank.  `prefill_probe`: also time one prefill of that many
+    tokens for one request.  Returns (and prints unless `quiet`) a dict: decode tokens/s (bsz * steps / device time),
+    prefill tokens/s, and the bytes of weights + cache a decode step must read against the measured HBM figure."""
     from signrot_b200.transformers import kernel_utils as ku
     hbm = peaks()["hbm_gbs"]
     cfg = ku.DecoderConfig(**cfg_kwargs)
     with torch.device(dev):
         model = ku.KernelDecoderModel(cfg)
     model = model.to(dev).random_init_(0)
+    if world > 1:
+        ku.shard_decoder_(model)
     gen = torch.Generator().manual_seed(0)
     ids = torch.randint(1000, 8000, (bsz, prompt), generator=gen).to(dev)
     cache = ku.build_paged_cache(model, bsz, prompt + steps + 8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def slowest(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t.item()
+
     with torch.no_grad():
         model(ids, past_key_values=cache, last_token_only=True)      # warm-up prefill (first-use costs)
         cache.reset()
+        if world > 1:
+            torch.distributed.barrier()
         torch.cuda.synchronize()
         e0.record()
         logits = model(ids, past_key_values=cache, last_token_only=True).logits
         e1.record()
         torch.cuda.synchronize()
-        t_prefill = e0.elapsed_time(e1)
+        t_prefill = slowest(e0.elapsed_time(e1))
         tok = logits[:, -1:].argmax(-1)
         dec = ku.try_graph_decoder(model, cache, bsz)
         graphed = dec is not None
         for _ in range(3):                               # warm-up steps (they advance the cache like real ones)
             tok = (dec.step(tok) if graphed else model(tok, past_key_values=cache).logits)[:, -1:].argmax(-1)
+        if world > 1:
+            torch.distributed.barrier()
         torch.cuda.synchronize()
         e0.record()
         for _ in range(steps):
             tok = (dec.step(tok) if graphed else model(tok, past_key_values=cache).logits)[:, -1:].argmax(-1)
         e1.record()
         torch.cuda.synchronize()
-    t_dec = e0.elapsed_time(e1) / steps
+        t_dec = slowest(e0.elapsed_time(e1)) / steps
+        t_probe = None
+        if prefill_probe:
+            del cache, dec
+            torch.cuda.empty_cache()
+            probe_ids = torch.randint(1000, 8000, (1, prefill_probe), generator=gen).to(dev)
+            pc = ku.build_paged_cache(model, 1, prefill_probe + 8)
+            model(probe_ids, past_key_values=pc, last_token_only=True)
+            pc.reset()
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            model(probe_ids, past_key_values=pc, last_token_only=True)
+            e1.record()
+            torch.cuda.synchronize()
+            t_probe = slowest(e0.elapsed_time(e1))
+            del pc
+    from signrot_b200 import _lib
+    if _lib.device_status() != 0:
+        raise RuntimeError("a kernel gave up a bounded device-side wait")
     finite = bool(torch.isfinite(logits).all())
-    hid, ffn, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
-    attn_w = (2 * hid * cfg.num_attention_heads * cfg.head_dim + 2 * hid * cfg.num_key_value_heads * cfg.head_dim) / 2
-    if cfg.num_local_experts:
-        mlp_w = 3 * hid * ffn / 2 * min(cfg.num_local_experts, bsz * cfg.num_experts_per_tok)
+    full = ku.DecoderConfig(**cfg_kwargs)                # byte accounting on the unsharded geometry: the whole job
+    hid, ffn, L = full.hidden_size, full.intermediate_size, full.num_hidden_layers
+    attn_w = (2 * hid * full.num_attention_heads * full.head_dim + 2 * hid * full.num_key_value_heads * full.head_dim) / 2
+    if full.num_local_experts:
+        mlp_w = 3 * hid * ffn / 2 * min(full.num_local_experts, bsz * full.num_experts_per_tok)
     else:
         mlp_w = 3 * hid * ffn / 2
     ctx = prompt + 3 + steps / 2
-    kv = bsz * ctx * cfg.num_key_value_heads * 68 * 2
-    step_bytes = L * (attn_w + mlp_w + kv) + cfg.vocab_size * hid * 2
-    print(json.dumps({"case": name, "batch": bsz, "prefill_tokens": prompt, "decode_steps": steps, "layers": L,
-                      "experts": cfg.num_local_experts, "graph_replay": graphed, "finite": finite,
-                      "decode_ms_per_step": round(t_dec, 3), "decode_tokens_per_s": round(bsz / t_dec * 1e3, 1),
-                      "prefill_ms": round(t_prefill, 1), "prefill_tokens_per_s": round(bsz * prompt / t_prefill * 1e3, 1),
-                      "step_bytes_gb": round(step_bytes / 1e9, 3), "step_gbs": round(step_bytes / t_dec / 1e6, 1),
-                      "frac_hbm": round(step_bytes / t_dec / 1e6 / hbm, 3),
-                      "note": "weights (every expert a step can touch), int4 KV at the mean context and the fp16 lm_head "
-                              "counted once per step; prefill time is the second of two calls, dense prefill attention included"}))
-    del model, cache, dec
+    kv = bsz * ctx * full.num_key_value_heads * 68 * 2
+    step_bytes = L * (attn_w + mlp_w + kv) + full.vocab_size * hid * 2 * world     # the fp16 head is replicated
+    res = {"case": name, "n_gpus": world, "batch": bsz, "prefill_tokens": prompt, "decode_steps": steps, "layers": L,
+           "experts": full.num_local_experts, "graph_replay": graphed, "finite": finite,
+           "parallelism": "one GPU" if world == 1 else (f"attention tensor-parallel x{world}, " + (
+               f"experts x{world}" if full.num_local_experts else f"MLP tensor-parallel x{world}")),
+           "decode_ms_per_step": round(t_dec, 3), "decode_tok_s": round(bsz / t_dec * 1e3, 1),
+           "prefill_ms": round(t_prefill, 1), "prefill_tok_s": round(bsz * prompt / t_prefill * 1e3, 1),
+           "step_bytes_gb": round(step_bytes / 1e9, 3), "step_gbs_per_gpu": round(step_bytes / world / t_dec / 1e6, 1),
+           "frac_hbm": round(step_bytes / world / t_dec / 1e6 / hbm, 3)}
+    if t_probe is not None:
+        res["prefill_probe_tokens"], res["prefill_probe_ms"] = prefill_probe, round(t_probe, 1)
+        res["prefill_probe_tok_s"] = round(prefill_probe / t_probe * 1e3, 1)
+    if not quiet:
+        res["note"] = ("weights (every expert a step can touch), int4 KV at the mean context and the fp16 lm_head counted once "
+                       "per step; prefill time is the second of two calls, dense prefill attention included")
+        print(json.dumps(res))
+    del model
     torch.cuda.empty_cache()
+    return res
 
 
 def main():
@@ -749,8 +907,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-models", action="store_true", help="skip the full-model / sparse-stack decode measurements")
     ap.add_argument("--sweep", action="store_true",
-                    help="secondary measurements of the other BASELINE configurations (JSON lines)")
+                    help="secondary measurements of the other configurations (JSON lines)")
     ap.add_argument("--kernel-case", default=None,
                     help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | decode_layer | "
                          "rotate14336 | decode")
@@ -806,11 +965,15 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local_rank)
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    try:
-        run_ours(args, rank, world, local_rank)
-    finally:
-        if world > 1:
-            torch.distributed.destroy_process_group()
+    run_ours(args, rank, world, local_rank)
+    if world > 1:
+        # Nothing is in flight after the barrier and the synchronise.  The process ends here instead of tearing the
+        # communicator down: with CUDA graphs that captured work of this process group still referenced, the
+        # tear-down of this collective-library version can block forever.
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
