@@ -20,6 +20,7 @@ int fail(int code, const char *fmt, ...) {
 int grouped_device_status(int *out, bool clear);
 int tc3_device_status(int *out, bool clear);
 int peer_device_status(int *out, bool clear);
+int rotate_umma_device_status(int *out, bool clear);
 int launch_bounded_wait_probe(long long budget_cycles, cudaStream_t st);
 
 }  // namespace sr
@@ -40,7 +41,10 @@ int sr_device_status(int *status, int clear) {
     int c = 0;
     rc = sr::peer_device_status(&c, clear != 0);
     if (rc) return rc;
-    *status = a ? a : (b ? b : c);
+    int d = 0;
+    rc = sr::rotate_umma_device_status(&d, clear != 0);
+    if (rc) return rc;
+    *status = a ? a : (b ? b : (c ? c : d));
     return SR_OK;
 }
 

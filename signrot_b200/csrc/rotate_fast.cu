@@ -267,7 +267,9 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
     // tensor-core transforms first; the butterfly kernel below takes what they do not: per-row sign tables
     // (expert ids) at n = 4096
     {
-        int rc = launch_rotate_tc4096(a, st);
+        int rc = launch_rotate_umma4096(a, st);
+        if (rc != SR_ERR_UNSUPPORTED) return rc;
+        rc = launch_rotate_tc4096(a, st);
         if (rc != SR_ERR_UNSUPPORTED) return rc;
         rc = launch_rotate_heads32(a, st);
         if (rc != SR_ERR_UNSUPPORTED) return rc;
