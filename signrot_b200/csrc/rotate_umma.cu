@@ -32,14 +32,15 @@ namespace um {
 
 constexpr int N = 4096, LINES = 128, LW = 32;
 constexpr int SLOT_BYTES = LINES * LW * 2;          // 8192: one row
-constexpr int SLOTS = 12;                            // rows in flight from HBM
-constexpr int NACC = 8, ACC_COLS = 32, TMEM_COLS = 256;
-constexpr int GROUPS = 4;                            // epilogue groups of four warps
+constexpr int BATCH = 4;                             // rows per MMA set: B is four row tiles side by side, N = 128
+constexpr int NBATCH = 3, SLOTS = NBATCH * BATCH;    // row batches in flight from HBM
+constexpr int NACC = 2, ACC_COLS = 32, TMEM_COLS = NACC * BATCH * ACC_COLS;   // two accumulator batches of 128 columns
+constexpr int GROUPS = BATCH;                        // epilogue groups of four warps: group g takes row g of every batch
 constexpr int THREADS = (2 + 4 * GROUPS) * 32;       // 576
 constexpr int A_BYTES = 128 * 128 * 2;               // H128 / 64, two K panels of 128 rows x 128 bytes
 // shared memory: row slots first (a descriptor never reaches past the allocation), then A, barriers, exchange
 constexpr int OFF_SLOTS = 0, OFF_A = SLOTS * SLOT_BYTES, OFF_BARS = OFF_A + A_BYTES;
-constexpr int NUM_BARS = 2 * SLOTS + 2 * NACC + GROUPS;
+constexpr int NUM_BARS = 2 * NBATCH + 2 * NACC + GROUPS;
 constexpr int OFF_EXCH = OFF_BARS + NUM_BARS * 8;
 constexpr int SMEM_BYTES = OFF_EXCH + 2 * GROUPS * 4 * 4 + 1024;   // + slack for the 1024-byte alignment
 constexpr long long WAIT_BUDGET = 1500000000ll;
@@ -121,11 +122,11 @@ rotate_quant_4096_umma_kernel(const __grid_constant__ CUtensorMap map_x, const i
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - raw);
     const uint32_t bars = base + OFF_BARS;
-    auto slot_full = [&](int s) { return bars + 8u * s; };
-    auto slot_empty = [&](int s) { return bars + 8u * (SLOTS + s); };
-    auto acc_full = [&](int a) { return bars + 8u * (2 * SLOTS + a); };
-    auto acc_empty = [&](int a) { return bars + 8u * (2 * SLOTS + NACC + a); };
-    auto amax_bar = [&](int g) { return bars + 8u * (2 * SLOTS + 2 * NACC + g); };   // the four warps of a group meet here
+    auto slot_full = [&](int s) { return bars + 8u * s; };                          // per row batch
+    auto slot_empty = [&](int s) { return bars + 8u * (NBATCH + s); };
+    auto acc_full = [&](int a) { return bars + 8u * (2 * NBATCH + a); };            // per accumulator batch
+    auto acc_empty = [&](int a) { return bars + 8u * (2 * NBATCH + NACC + a); };
+    auto amax_bar = [&](int g) { return bars + 8u * (2 * NBATCH + 2 * NACC + g); }; // the four warps of a group meet here
     float *exch = reinterpret_cast<float *>(base_ptr + OFF_EXCH);        // [parity][group][warp of the group]: its part of amax
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -139,13 +140,13 @@ rotate_quant_4096_umma_kernel(const __grid_constant__ CUtensorMap map_x, const i
     // ---- set-up: barriers, tensor memory, the constant A tile H128 / 64 (K-major, 128-byte swizzle, two K panels)
     if (tid == 0) {
         abort_flag = g_status;
-        for (int s = 0; s < SLOTS; ++s) {
+        for (int s = 0; s < NBATCH; ++s) {
             mbar_init(slot_full(s), 1);
             mbar_init(slot_empty(s), 1);
         }
         for (int a = 0; a < NACC; ++a) {
             mbar_init(acc_full(a), 1);
-            mbar_init(acc_empty(a), 4);
+            mbar_init(acc_empty(a), 4 * GROUPS);       // every epilogue warp, whether or not its group has a row in the batch
         }
         for (int g = 0; g < GROUPS; ++g) mbar_init(amax_bar(g), 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -195,55 +196,68 @@ rotate_quant_4096_umma_kernel(const __grid_constant__ CUtensorMap map_x, const i
     const uint32_t tmem_acc = tmem_base_slot;
     volatile int *ab = &abort_flag;
 
+    const uint32_t batches = (cnt + BATCH - 1) / BATCH;
     if (*ab == 0) {
         if (warp == 0) {
-            // ------------------------------------------------ TMA producer
+            // ------------------------------------------------ TMA producer: one barrier per batch of up to four rows
             if (lane == 0) {
                 pdl_wait();      // x comes from the kernel before this one
-                for (uint32_t i = 0; i < cnt; ++i) {
-                    const int s = (int)(i % SLOTS);
-                    if (!mbar_wait(slot_empty(s), ((i / SLOTS) & 1) ^ 1, ab, 51)) break;
-                    mbar_expect_tx(slot_full(s), SLOT_BYTES);
-                    tma_load_2d(base + OFF_SLOTS + s * SLOT_BYTES, &map_x, 0, (int)((row_begin + i) * LINES), slot_full(s));
+                for (uint32_t b = 0; b < batches; ++b) {
+                    const int s = (int)(b % NBATCH);
+                    const uint32_t n_rows = min((uint32_t)BATCH, cnt - b * BATCH);
+                    if (!mbar_wait(slot_empty(s), ((b / NBATCH) & 1) ^ 1, ab, 51)) break;
+                    mbar_expect_tx(slot_full(s), n_rows * SLOT_BYTES);
+                    for (uint32_t r = 0; r < n_rows; ++r)
+                        tma_load_2d(base + OFF_SLOTS + (s * BATCH + r) * SLOT_BYTES, &map_x, 0,
+                                    (int)((row_begin + b * BATCH + r) * LINES), slot_full(s));
                 }
             }
         } else if (warp == 1) {
-            // ------------------------------------------------ MMA issuer
+            // ------------------------------------------------ MMA issuer: eight instructions per batch
             if (lane == 0) {
                 const uint32_t fmt = BF16 ? 1u : 0u;
-                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(ACC_COLS >> 3) << 17) |
-                                       ((uint32_t)(128 >> 4) << 24);     // D fp32, B N-major, N = 32, M = 128
-                for (uint32_t i = 0; i < cnt; ++i) {
-                    const int s = (int)(i % SLOTS), a = (int)(i % NACC);
-                    if (!mbar_wait(slot_full(s), (i / SLOTS) & 1, ab, 52)) break;
-                    if (!mbar_wait(acc_empty(a), ((i / NACC) & 1) ^ 1, ab, 53)) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t d_tmem = tmem_acc + (uint32_t)(a * ACC_COLS);
-                    const uint32_t a_base = base + OFF_A, b_base = base + OFF_SLOTS + s * SLOT_BYTES;
+                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) |
+                                       ((uint32_t)((BATCH * ACC_COLS) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                // (D fp32, B N-major, N = 128: the four row tiles of a batch are the four 64-byte blocks along N, one
+                // slot apart; M = 128.  A batch with fewer rows multiplies what is left in the unused slots into
+                // accumulator columns nobody reads.)
+                uint64_t da[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)     // K = 16 lines per instruction
-                        mma_f16(d_tmem, desc_a(a_base + (j >> 2) * 16384 + (j & 3) * 32), desc_b(b_base + j * 1024), idesc,
-                                j > 0 ? 1u : 0u);
+                for (int j = 0; j < 8; ++j) da[j] = desc_a(base + OFF_A + (j >> 2) * 16384 + (j & 3) * 32);
+                for (uint32_t b = 0; b < batches; ++b) {
+                    const int s = (int)(b % NBATCH), a = (int)(b % NACC);
+                    if (!mbar_wait(slot_full(s), (b / NBATCH) & 1, ab, 52)) break;
+                    if (!mbar_wait(acc_empty(a), ((b / NACC) & 1) ^ 1, ab, 53)) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d_tmem = tmem_acc + (uint32_t)(a * BATCH * ACC_COLS);
+                    const uint64_t db = desc_b(base + OFF_SLOTS + s * BATCH * SLOT_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)     // K = 16 lines (1024 bytes of every row tile) per instruction
+                        mma_f16(d_tmem, da[j], db + (uint64_t)(j * (1024 >> 4)), idesc, j > 0 ? 1u : 0u);
                     mma_commit(slot_empty(s));
                     mma_commit(acc_full(a));
                 }
             }
         } else {
-            // ------------------------------------------------ epilogue: group g takes rows g, g + 4, ...
+            // ------------------------------------------------ epilogue: group g takes row g of every batch
             const int grp = (warp - 2) >> 2;
             pdl_wait();          // q / q_scale may still be read by the kernel before this one
             uint32_t it = 0;     // rows this group has taken
-            for (uint32_t i = (uint32_t)grp; i < cnt; i += GROUPS, ++it) {
-                const int a = (int)(i % NACC);
+            for (uint32_t b = 0; b < batches; ++b) {
+                const int a = (int)(b % NACC);
+                const uint32_t i = b * BATCH + (uint32_t)grp;
                 const uint32_t row = row_begin + i;
                 // (the decision to go on is taken by the whole warp: the tensor-memory load below is warp-collective)
-                if (!__all_sync(0xffffffffu, mbar_wait(acc_full(a), (i / NACC) & 1, ab, 54))) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_full(a), (b / NACC) & 1, ab, 54))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 float d[32];
-                tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * ACC_COLS), d);
+                if (i < cnt) tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((a * BATCH + grp) * ACC_COLS), d);
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty(a));
+                if (i >= cnt) continue;
+                ++it;
+                const uint32_t itp = (it - 1) & 1;
 
                 // ---- the five stages over l, between this thread's registers
                 u64 v[16];
@@ -251,24 +265,28 @@ rotate_quant_4096_umma_kernel(const __grid_constant__ CUtensorMap map_x, const i
                 for (int p = 0; p < 16; ++p) v[p] = pack2(d[2 * p], d[2 * p + 1]);
                 fwht_pairs<16, 16>(v);
                 // ---- one rounding to fp16, sign, range
-                __half2 hv[16];
-                __half2 hmaxv = __floats2half2_rn(0.f, 0.f);
+                __half2 hv[16], am[16];
 #pragma unroll
                 for (int p = 0; p < 16; ++p) {
                     float lo, hi;
                     unpack2(v[p], lo, hi);
                     hv[p] = bits_h2(h2_bits(__floats2half2_rn(lo, hi)) ^ sgn[p]);
-                    hmaxv = __hmax2(hmaxv, __habs2(hv[p]));
+                    am[p] = __habs2(hv[p]);
                 }
+#pragma unroll
+                for (int w2 = 8; w2 > 0; w2 >>= 1)      // a tree: four dependent steps instead of sixteen
+#pragma unroll
+                    for (int p = 0; p < w2; ++p) am[p] = __hmax2(am[p], am[p + w2]);
+                const __half2 hmaxv = am[0];
                 float vmax = warp_max(fmaxf(__low2float(hmaxv), __high2float(hmaxv)));
                 // the row's maximum over the four warps of the group: parts through shared memory (double-buffered by the
                 // parity of the group's row count), met at a barrier whose wait is bounded like every other wait here
-                float *part = exch + ((it & 1) * GROUPS + grp) * 4;
+                float *part = exch + (itp * GROUPS + grp) * 4;
                 if (lane == 0) {
                     part[quarter] = vmax;
                     mbar_arrive(amax_bar(grp));
                 }
-                if (!__all_sync(0xffffffffu, mbar_wait(amax_bar(grp), it & 1, ab, 55))) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(amax_bar(grp), itp, ab, 55))) break;
                 vmax = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
 
                 __half s = __float2half(vmax / 7.f);
@@ -293,23 +311,28 @@ rotate_quant_4096_umma_kernel(const __grid_constant__ CUtensorMap map_x, const i
                 // ---- codes.  After the fp16 addition of the rounding constant (sum in [1536, 1552)) the low byte of
                 // each half is the code + 8; four pairs are merged into one word of four bytes by byte permutes.
                 uint32_t w[4];
+                auto emit = [&](auto clamp_tag) {
+                    constexpr bool CLAMP = decltype(clamp_tag)::value;
 #pragma unroll
-                for (int part = 0; part < 4; ++part) {
-                    uint32_t bits[4];
+                    for (int part = 0; part < 4; ++part) {
+                        uint32_t bits[4];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 f = __half22float2(hv[part * 4 + k]);
-                        float lo, hi;
-                        unpack2(mul2(pack2(f.x, f.y), rcp2), lo, hi);
-                        __half2 qh = __floats2half2_rn(lo, hi);      // rn_h(x * rcp): the quotient __hdiv returns
-                        if (clamp) qh = __hmin2(__hmax2(qh, lo_c), hi_c);
-                        bits[k] = h2_bits(__hadd2(qh, mg));
+                        for (int k = 0; k < 4; ++k) {
+                            const float2 f = __half22float2(hv[part * 4 + k]);
+                            float lo, hi;
+                            unpack2(mul2(pack2(f.x, f.y), rcp2), lo, hi);
+                            __half2 qh = __floats2half2_rn(lo, hi);      // rn_h(x * rcp): the quotient __hdiv returns
+                            if (CLAMP) qh = __hmin2(__hmax2(qh, lo_c), hi_c);
+                            bits[k] = h2_bits(__hadd2(qh, mg));
+                        }
+                        // x = [l0, l1, h0, h1] of two pairs, then the low values and the high values of all four
+                        const uint32_t x01 = __byte_perm(bits[0], bits[1], 0x6240), x23 = __byte_perm(bits[2], bits[3], 0x6240);
+                        const uint32_t ev = __byte_perm(x01, x23, 0x5410), od = __byte_perm(x01, x23, 0x7632);
+                        w[part] = (ev + (od << 4)) ^ 0x88888888u;       // offset-8 codes -> two's complement nibbles
                     }
-                    // x = [l0, l1, h0, h1] of two pairs, then the low values and the high values of all four
-                    const uint32_t x01 = __byte_perm(bits[0], bits[1], 0x6240), x23 = __byte_perm(bits[2], bits[3], 0x6240);
-                    const uint32_t ev = __byte_perm(x01, x23, 0x5410), od = __byte_perm(x01, x23, 0x7632);
-                    w[part] = (ev + (od << 4)) ^ 0x88888888u;       // offset-8 codes -> two's complement nibbles
-                }
+                };
+                if (clamp) emit(std::true_type{});
+                else emit(std::false_type{});
                 *reinterpret_cast<uint4 *>(q + (size_t)row * (N / 2) + 16 * line) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
