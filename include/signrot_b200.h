@@ -63,6 +63,12 @@ int sr_selftest_bounded_wait(int64_t budget_cycles, void *stream);
 int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned, void *C,
                  void *stream);
 
+/* The same product with A taken from a wider code matrix: row m of A starts lda_bytes after row m - 1
+ * (lda_bytes >= K / 2, a multiple of 16; A itself 16-byte aligned).  A tensor-parallel rank multiplies its K-slice
+ * of the full-row codes this way without copying it out (the reference has no sharded form of this path). */
+int sr_matmul_i4_ld(const void *A, int64_t lda_bytes, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned,
+                    void *C, void *stream);
+
 /* out[M,N] fp16 = dequant(A * W^T): the whole of Linear4bit.forward for a packed input
  * (signrot/nn/linear.py:36-50): GEMM, optional asymmetric correction
  * acc -= a_zero[m] * w_sum[n] (a_zero int8 [M], w_sum int32 [N]; both NULL for symmetric

@@ -30,6 +30,7 @@ _F = ctypes.c_float
 _SIGNATURES = {
     "sr_device_status": [ctypes.POINTER(ctypes.c_int), _I],
     "sr_matmul_i4": [_P, _P, _I64, _I64, _I64, _I, _P, _P],
+    "sr_matmul_i4_ld": [_P, _I64, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_w4a4_linear": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
     "sr_w4a4_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
     "sr_grouped_linear": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _P],

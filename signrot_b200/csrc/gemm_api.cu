@@ -47,6 +47,20 @@ int sr_matmul_i4(const void *A, const void *B, int64_t M, int64_t N, int64_t K, 
     return run_gemm(A, B, M, N, K, a_unsigned, ep, stream, "matmul");
 }
 
+int sr_matmul_i4_ld(const void *A, int64_t lda_bytes, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned,
+                    void *C, void *stream) {
+    SR_REQUIRE(M == 0 || N == 0 || C != nullptr, SR_ERR_INVALID, "matmul: null output");
+    SR_REQUIRE(lda_bytes >= K / 2 && lda_bytes % 16 == 0 && lda_bytes < (1ll << 31), SR_ERR_INVALID,
+               "matmul: row stride of %lld bytes for rows of %lld packed bytes (must cover a row and be a multiple of 16)",
+               (long long)lda_bytes, (long long)(K / 2));
+    Epilogue ep = {};
+    ep.mode = 0;
+    ep.c = (int32_t *)C;
+    ep.ldc = N;
+    ep.lda = (uint32_t)lda_bytes;
+    return run_gemm(A, B, M, N, K, a_unsigned, ep, stream, "matmul");
+}
+
 int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
                    const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream) {
     SR_REQUIRE(M == 0 || N == 0 || (out && a_scale && w_scale), SR_ERR_INVALID, "w4a4_linear: null pointer");

@@ -24,6 +24,7 @@ struct Epilogue {
     const int32_t *w_sum;    // [N] or [E, N], required when a_zero is set
     const __half *bias;      // [N] or null
     const int32_t *expert_ids;  // [M] or null
+    uint32_t lda;            // bytes between rows of A; 0 = K / 2 (dense).  A may be a column range of a wider code matrix
 
     __device__ __forceinline__ __half dequant(uint32_t row, uint32_t col, int acc, uint32_t N) const {
         const size_t e = expert_ids ? (size_t)expert_ids[row] * N : 0;

@@ -191,10 +191,11 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
     // activation fragments of the step after the current one (they come from L1/L2, one step ahead is enough)
     auto load_x = [&](const SkItem &it, uint32_t step, uint4 (&x)[NT]) {
         const bool k_ok = step * SK_STEP + 16 * q + 16 <= kp;
-        const uint8_t *xs = A + ((size_t)it.x_row0 + g) * kp + 16 * q + (size_t)step * SK_STEP;
+        const uint32_t lda = ep.lda ? ep.lda : kp;
+        const uint8_t *xs = A + ((size_t)it.x_row0 + g) * lda + 16 * q + (size_t)step * SK_STEP;
 #pragma unroll
         for (int t = 0; t < NT; ++t)
-            x[t] = k_ok && it.x_row0 + g + 8 * t < it.x_end ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * kp))
+            x[t] = k_ok && it.x_row0 + g + 8 * t < it.x_end ? __ldg(reinterpret_cast<const uint4 *>(xs + (size_t)(8 * t) * lda))
                                                            : make_uint4(0, 0, 0, 0);
     };
     uint32_t item = first_item;

@@ -462,11 +462,12 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-static int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+static int make_map(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+                    uint64_t stride_bytes = 0) {
     EncodeTiledFn fn = encode_fn();
     SR_REQUIRE(fn != nullptr, SR_ERR_CUDA, "matmul: cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {row_bytes, rows};
-    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint64_t strides[1] = {stride_bytes ? stride_bytes : row_bytes};
     const cuuint32_t box[2] = {(cuuint32_t)PK_ROW, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
@@ -489,7 +490,8 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     const int64_t b_rows = row_off ? N * (int64_t)num_experts : N;
     SR_REQUIRE(M < (1ll << 31) && b_rows < (1ll << 31), SR_ERR_UNSUPPORTED, "matmul: size out of range");
     CUtensorMap ma, mb;
-    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K / 2, BMC);
+    SR_REQUIRE(ep.lda % 16 == 0, SR_ERR_INVALID, "matmul: the row stride of A must be a multiple of 16 bytes");
+    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K / 2, BMC, ep.lda);
     if (rc) return rc;
     rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)K / 2, BNC);
     if (rc) return rc;

@@ -2,22 +2,25 @@
 //
 // The reference keeps this path on one device (fake_quant/kernel_utils.py:365-366); a sharded decode step
 // adds, per row-parallel linear, an all-gather of a few hundred KB (the online rotation and the per-token
-// scale span the whole row) and an all-reduce of the int32 partial sums.  At those sizes a collective
-// library call costs its latency several times over, so both are ONE kernel here:
+// scale span the whole row) and an all-reduce of the int32 partial sums.  At those sizes the cost is latency,
+// not bandwidth, so both are ONE kernel here and the protocol spends exactly one trip across the fabric:
 //
-//   push     every rank stores its message into slot [rank] of every peer's exchange buffer with plain
-//            16-byte peer stores (no multicast loads, no copy engine), then raises its flag on every peer;
-//   wait     until the flags of all ranks carry this exchange's number (bounded: on expiry the kernel
-//            records a status code and carries on, so the context stays usable);
-//   combine  from the local slots into the caller's output: concatenation (all-gather), integer sum +
-//            dequant epilogue (row-parallel W4A4 linear: integer addition is order-free, so every group size
-//            gives the bits of one GPU), or fp32 sum in rank order (expert-parallel partial outputs).
+//   push     every thread stores its 16-byte pieces of this rank's message into slot [rank] of every rank's
+//            exchange buffer as flagged lines: two 16-byte peer stores per piece, each {data, n, data, n} with n
+//            the number of this exchange.  An aligned 8-byte half of such a store becomes visible as a whole, so a
+//            reader that sees n beside a word has that word: no fence, no separate flag, no second trip;
+//   combine  every thread polls the lines it needs in the LOCAL slots until they carry n (bounded: on expiry the
+//            kernel records a status code and carries on, so the context stays usable) and writes the caller's
+//            output: concatenation (all-gather), integer sum + dequant epilogue (row-parallel W4A4 linear:
+//            integer addition is order-free, so every group size gives the bits of one GPU), or fp32 sum in rank
+//            order (expert-parallel partial outputs).
+// Plain peer stores and local loads only: no multicast loads, no copy engine.
 //
 // Exchange buffers are double-buffered by the parity of a device-resident exchange counter, so the kernel is
 // the same launch every time (capturable in a CUDA graph) and a fast rank that is already pushing exchange
-// e + 1 cannot overwrite slots a slow rank is still combining for exchange e (a rank can never be two
-// exchanges ahead: finishing e + 1 needs every peer's push of e + 1, which a peer issues after its own
-// exchange e has ended).  Every rank must issue the same sequence of exchanges.
+// n + 1 cannot overwrite lines a slow rank is still combining for exchange n (a rank can never be two
+// exchanges ahead: finishing n + 1 needs every peer's lines of n + 1, which a peer stores after its own
+// exchange n has ended).  Every rank must issue the same sequence of exchanges.
 #include "common.cuh"
 #include <cstring>
 
@@ -27,7 +30,7 @@ namespace {
 
 constexpr int PC_MAX_RANKS = 8;
 constexpr int PC_THREADS = 256;
-constexpr int PC_MAX_CTAS = 64;                 // all CTAs of an exchange spin together: they must be co-resident
+constexpr int PC_MAX_CTAS = 128;                // a thread waits only for lines, never for another CTA of its own GPU
 constexpr long long PC_WAIT_BUDGET = 3000000000ll;   // about 1.5 s of SM cycles
 
 __device__ int g_peer_status;
@@ -35,33 +38,48 @@ __device__ int g_peer_status;
 // Control block at the start of every rank's region.
 struct PeerCtrl {
     uint32_t epoch;                 // exchanges this rank has completed
-    uint32_t pushed;                // CTAs of the running exchange that have stored their part
     uint32_t done;                  // CTAs of the running exchange that have finished
-    uint32_t pad;
-    uint32_t flags[PC_MAX_RANKS];   // flags[r]: number of the latest exchange rank r has pushed to this rank
 };
 constexpr size_t PC_CTRL_BYTES = 256;
 
 struct PeerArgs {
     uint8_t *region[PC_MAX_RANKS];  // region of every rank, mapped into this process (own region at [rank])
     int rank, world;
-    unsigned long long slot_bytes;
+    unsigned long long slot_bytes;  // bytes of one slot: twice the largest message (every word travels with a flag)
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t *p) {
     uint32_t v;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ uint4 ld_cg16(const void *p) { return __ldcg(reinterpret_cast<const uint4 *>(p)); }
+__device__ __forceinline__ void st_line(void *p, uint32_t d0, uint32_t d1, uint32_t n) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(n), "r"(d1), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// The four data words of piece i of a slot (two flagged lines), once both lines carry exchange number n.
+__device__ __forceinline__ uint4 wait_piece(const uint8_t *slot, unsigned long long i, uint32_t n, long long t0, int who) {
+    const uint8_t *p = slot + i * 32;
+    uint4 a = ld_line(p), b = ld_line(p + 16);
+    int spins = 0;
+    while (a.y != n || a.w != n || b.y != n || b.w != n) {
+        if (++spins == 64) {
+            spins = 0;
+            if (*reinterpret_cast<volatile int *>(&g_peer_status) != 0) break;      // some wait has already given up
+            if (clock64() - t0 > PC_WAIT_BUDGET) {
+                atomicCAS(&g_peer_status, 0, 60 + who);                              // code 60 + rank that never arrived
+                break;
+            }
+        }
+        a = ld_line(p);
+        b = ld_line(p + 16);
+    }
+    return make_uint4(a.x, a.z, b.x, b.z);
+}
 
 enum { PC_GATHER = 0, PC_REDUCE_I32_DEQUANT = 1, PC_REDUCE_F32 = 2 };
 
@@ -82,65 +100,48 @@ peer_exchange_kernel(PeerArgs a, const uint4 *__restrict__ src, unsigned long lo
     __shared__ uint32_t s_epoch;
     if (tid == 0) s_epoch = ld_relaxed_gpu(&me->epoch) + 1;   // rewritten only after every CTA has read it
     __syncthreads();
-    const uint32_t e = s_epoch;
-    const unsigned long long parity_off = PC_CTRL_BYTES + (unsigned long long)(e & 1) * a.world * a.slot_bytes;
+    const uint32_t n = s_epoch;
+    const unsigned long long parity_off = PC_CTRL_BYTES + (unsigned long long)(n & 1) * a.world * a.slot_bytes;
     const unsigned long long stride = (unsigned long long)gridDim.x * PC_THREADS;
+    const unsigned long long first = (unsigned long long)blockIdx.x * PC_THREADS + tid;
 
-    // ---- push: this rank's message into slot [rank] of every rank's buffer (its own included)
+    // ---- push: this rank's message into slot [rank] of every rank's buffer (its own included), as flagged lines
     {
         const unsigned long long my_slot = parity_off + (unsigned long long)a.rank * a.slot_bytes;
-        for (unsigned long long i = (unsigned long long)blockIdx.x * PC_THREADS + tid; i < pieces; i += stride) {
+        for (unsigned long long i = first; i < pieces; i += stride) {
             const uint4 v = src[i];
 #pragma unroll
             for (int r = 0; r < PC_MAX_RANKS; ++r)
-                if (r < a.world) reinterpret_cast<uint4 *>(a.region[r] + my_slot)[i] = v;
+                if (r < a.world) {
+                    uint8_t *dst = a.region[r] + my_slot + i * 32;
+                    st_line(dst, v.x, v.y, n);
+                    st_line(dst + 16, v.z, v.w, n);
+                }
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-        const uint32_t arrived = atomicAdd(&me->pushed, 1u);
-        if (arrived == gridDim.x - 1) {          // the last CTA to finish its stores raises the flags
-            me->pushed = 0;
-            __threadfence_system();
-            for (int r = 0; r < a.world; ++r)
-                st_release_sys(&reinterpret_cast<PeerCtrl *>(a.region[r])->flags[a.rank], e);
-        }
-    }
-    // ---- wait (bounded) for every rank's push of exchange e
-    // (a rank that has already given up once does not wait again: the status word is sticky until the host clears it)
-    if (tid < a.world && *reinterpret_cast<volatile int *>(&g_peer_status) == 0) {
-        const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(&me->flags[tid]) - e) < 0) {
-            if (clock64() - t0 > PC_WAIT_BUDGET) {
-                atomicCAS(&g_peer_status, 0, 60 + tid);      // code 60 + rank that never arrived
-                break;
-            }
-        }
-    }
-    __syncthreads();
 
-    // ---- combine from the local slots
+    // ---- combine from the local slots, waiting line by line
     const uint8_t *mine = a.region[a.rank] + parity_off;
+    const long long t0 = clock64();
     if (MODE == PC_GATHER) {
         // slot r holds rank r's [rows, cols] fp16 shard; out is [rows, world * cols]
         const unsigned long long per_row = (unsigned long long)c.cols / 8;          // 16-byte pieces per shard row
         const unsigned long long total = (unsigned long long)a.world * pieces;
         uint4 *out = reinterpret_cast<uint4 *>(c.out);
-        for (unsigned long long i = (unsigned long long)blockIdx.x * PC_THREADS + tid; i < total; i += stride) {
+        for (unsigned long long i = first; i < total; i += stride) {
             const unsigned long long r = i / pieces, j = i % pieces;
             const unsigned long long row = j / per_row, col = j % per_row;
-            out[(row * a.world + r) * per_row + col] = ld_cg16(mine + r * a.slot_bytes + j * 16);
+            out[(row * a.world + r) * per_row + col] = wait_piece(mine + r * a.slot_bytes, j, n, t0, (int)r);
         }
     } else if (MODE == PC_REDUCE_I32_DEQUANT) {
         const unsigned long long per_row = (unsigned long long)c.cols / 4;          // pieces of four int32 per row
         uint2 *out = reinterpret_cast<uint2 *>(c.out);
-        for (unsigned long long i = (unsigned long long)blockIdx.x * PC_THREADS + tid; i < pieces; i += stride) {
+        for (unsigned long long i = first; i < pieces; i += stride) {
             int4 acc = make_int4(0, 0, 0, 0);
 #pragma unroll
             for (int r = 0; r < PC_MAX_RANKS; ++r)
                 if (r < a.world) {
-                    const uint4 v = ld_cg16(mine + (unsigned long long)r * a.slot_bytes + i * 16);
+                    const uint4 v = wait_piece(mine + (unsigned long long)r * a.slot_bytes, i, n, t0, r);
                     acc.x += (int)v.x;
                     acc.y += (int)v.y;
                     acc.z += (int)v.z;
@@ -160,12 +161,12 @@ peer_exchange_kernel(PeerArgs a, const uint4 *__restrict__ src, unsigned long lo
         }
     } else {
         uint2 *out = reinterpret_cast<uint2 *>(c.out);
-        for (unsigned long long i = (unsigned long long)blockIdx.x * PC_THREADS + tid; i < pieces; i += stride) {
+        for (unsigned long long i = first; i < pieces; i += stride) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int r = 0; r < PC_MAX_RANKS; ++r)
                 if (r < a.world) {                                 // rank order: the same sum on every rank
-                    const uint4 v = ld_cg16(mine + (unsigned long long)r * a.slot_bytes + i * 16);
+                    const uint4 v = wait_piece(mine + (unsigned long long)r * a.slot_bytes, i, n, t0, r);
                     acc.x += __uint_as_float(v.x);
                     acc.y += __uint_as_float(v.y);
                     acc.z += __uint_as_float(v.z);
@@ -186,7 +187,7 @@ peer_exchange_kernel(PeerArgs a, const uint4 *__restrict__ src, unsigned long lo
         if (finished == gridDim.x - 1) {
             me->done = 0;
             __threadfence();
-            atomicExch(&me->epoch, e);
+            atomicExch(&me->epoch, n);
         }
     }
 }
@@ -215,7 +216,7 @@ int sr_peer_region_bytes(int64_t world, int64_t slot_bytes, int64_t *bytes) {
     SR_REQUIRE(bytes && world >= 1 && world <= PC_MAX_RANKS && slot_bytes > 0 && slot_bytes % 16 == 0, SR_ERR_INVALID,
                "peer_region_bytes: world %lld (1..%d), slot %lld bytes (a positive multiple of 16)", (long long)world,
                PC_MAX_RANKS, (long long)slot_bytes);
-    *bytes = (int64_t)PC_CTRL_BYTES + 2 * world * slot_bytes;
+    *bytes = (int64_t)PC_CTRL_BYTES + 2 * world * (2 * slot_bytes);      // two parities; every data word travels with a flag
     return SR_OK;
 }
 
@@ -287,7 +288,7 @@ int sr_peer_exchange(int mode, const void *const *regions, int rank, int world, 
     }
     a.rank = rank;
     a.world = world;
-    a.slot_bytes = (unsigned long long)slot_bytes;
+    a.slot_bytes = 2ull * (unsigned long long)slot_bytes;
     CombineArgs c = {rows, cols, (const __half *)row_scale, (const __half *)col_scale, out};
     const unsigned long long pieces = (unsigned long long)bytes / 16;
     unsigned long long ctas = cdiv<unsigned long long>(pieces, PC_THREADS);

@@ -96,6 +96,20 @@ def _matmul(name, A, B, a_unsigned):
     return C.view(*a_lead, *b_lead)
 
 
+def matmul_si4_cols(A, begin, end, B):
+    """`matmul_si4_si4(A[:, begin:end], B)` on packed columns [begin, end) of a 2-D code matrix without copying the
+    slice out (the K-slice product of a row-parallel linear).  begin and the row width must be multiples of 16 bytes."""
+    dev = require_cuda("matmul", A, B)
+    _check_dtype("matmul", A, torch.uint8)
+    _check_dtype("matmul", B, torch.uint8)
+    if A.dim() != 2 or B.dim() != 2 or B.shape[1] != end - begin or begin % 16 or A.shape[1] % 16 or (end - begin) % 32:
+        raise RuntimeError(f"matmul: bad column range [{begin}, {end}) of a {tuple(A.shape)} code matrix")
+    M, N = A.shape[0], B.shape[0]
+    C = torch.empty((M, N), dtype=torch.int32, device=dev)
+    run(dev, "sr_matmul_i4_ld", A.data_ptr() + begin, A.shape[1], ptr(B), M, N, 2 * (end - begin), 0, ptr(C))
+    return C
+
+
 def matmul_si4_si4(A, B):
     """int32 `unpack_i4(A) @ unpack_i4(B).T` (kernel.py:67-73)."""
     return _matmul("matmul", A, B, False)

@@ -115,8 +115,11 @@ class RowParallelLinear4bit:
         x = self.gather_input(x_local) if self.world > 1 else x_local
         packed = self.ops.rotate_quant(x, self.hadK, self.K_had, sign=self.sign, heads=self.heads,
                                        clip_ratio=self.clip)
-        q_slice = packed.quantized_x[..., self.begin // 2:self.end // 2].contiguous()
-        acc = self.ops.matmul_si4_si4(q_slice, self.weight)
+        codes = packed.quantized_x
+        if hasattr(self.ops, "matmul_si4_cols") and codes.dim() == 2 and (self.begin // 2) % 16 == 0 and codes.shape[1] % 16 == 0:
+            acc = self.ops.matmul_si4_cols(codes, self.begin // 2, self.end // 2, self.weight)   # no copy of the slice
+        else:
+            acc = self.ops.matmul_si4_si4(codes[..., self.begin // 2:self.end // 2].contiguous(), self.weight)
         peer = self.peer
         if self.world > 1 and peer is not None and acc.dim() == 2 and peer.fits(acc.shape[0], acc.shape[1], 1):
             # push the int32 partials to every peer, sum and dequantize in the same kernel

@@ -224,3 +224,17 @@ def test_bounded_wait_gives_up_and_the_next_launch_is_clean():
     assert torch.equal(kernel.matmul_si4_si4(A, B).cpu(), want)
     with pytest.raises(RuntimeError, match="budget"):
         _lib.call("sr_selftest_bounded_wait", 10 ** 9)
+
+
+@pytest.mark.parametrize("M,N", [(8, 4096), (40, 512), (300, 264)])
+def test_matmul_on_a_column_range_of_the_codes(M, N):
+    """The K-slice product of a row-parallel linear: columns [begin, end) of a wider code matrix, read in place
+    (weight-streaming kernel for few rows, tensor-core kernel otherwise) == the product on a copy of the slice."""
+    K_full, begin, end = 4096, 1024, 3072           # values; packed bytes are half of these
+    a, b = _codes(M, K_full, M), _codes(N, end - begin, N + 1)
+    A, B = oracle.pack_i4(a).to(DEV), oracle.pack_i4(b).to(DEV)
+    got = kernel.matmul_si4_cols(A, begin // 2, end // 2, B)
+    assert _lib.device_status() == 0
+    assert torch.equal(got.cpu(), oracle.matmul_i4(A[:, begin // 2:end // 2].cpu(), B.cpu()))
+    with pytest.raises(RuntimeError, match="column range"):
+        kernel.matmul_si4_cols(A, 8, 8 + (end - begin) // 2, B)
