@@ -21,6 +21,7 @@ int grouped_device_status(int *out, bool clear);
 int tc3_device_status(int *out, bool clear);
 int peer_device_status(int *out, bool clear);
 int rotate_umma_device_status(int *out, bool clear);
+int rotate_had28_umma_device_status(int *out, bool clear);
 int launch_bounded_wait_probe(long long budget_cycles, cudaStream_t st);
 
 }  // namespace sr
@@ -44,7 +45,10 @@ int sr_device_status(int *status, int clear) {
     int d = 0;
     rc = sr::rotate_umma_device_status(&d, clear != 0);
     if (rc) return rc;
-    *status = a ? a : (b ? b : (c ? c : d));
+    int e = 0;
+    rc = sr::rotate_had28_umma_device_status(&e, clear != 0);
+    if (rc) return rc;
+    *status = a ? a : (b ? b : (c ? c : (d ? d : e)));
     return SR_OK;
 }
 

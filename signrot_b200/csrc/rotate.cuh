@@ -29,6 +29,7 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st);
 int launch_rotate_had28(const RotateArgs &a, cudaStream_t st);
 int launch_rotate_tc4096(const RotateArgs &a, cudaStream_t st);   // tensor-core transform (mma.sync), rows of 4096
 int launch_rotate_umma4096(const RotateArgs &a, cudaStream_t st); // tcgen05 + TMA, rows of 4096, symmetric codes
+int launch_rotate_had28_umma(const RotateArgs &a, cudaStream_t st); // tcgen05 + TMA, rows of 14336, symmetric codes
 int launch_rotate_heads32(const RotateArgs &a, cudaStream_t st);  // head-wise H32 (x) I128 on the tensor cores
 
 // ---- packed fp32 arithmetic on register pairs (add.f32x2 / sub.f32x2 / mul.f32x2, sm_100)

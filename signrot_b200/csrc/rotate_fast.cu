@@ -277,7 +277,10 @@ int launch_rotate_fast(const RotateArgs &a, cudaStream_t st) {
     const bool shape_ok = a.n == 4096 && a.K == 1 && a.stride == 1 && a.S == 4096 && a.q != nullptr &&
                           !a.fp32_mode && (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) &&
                           aligned16(a.x) && aligned4(a.q) && (a.out == nullptr || a.out_dtype == SR_F16);
-    if (!shape_ok) return launch_rotate_had28(a, st);  // the other dedicated shape, or SR_ERR_UNSUPPORTED
+    if (!shape_ok) {   // the other dedicated shape, or SR_ERR_UNSUPPORTED
+        const int rc = launch_rotate_had28_umma(a, st);
+        return rc != SR_ERR_UNSUPPORTED ? rc : launch_rotate_had28(a, st);
+    }
     const int sm_count = current_sm_count();
     const uint32_t ctas_needed = cdiv<uint32_t>(a.rows, ROWS_PER_CTA);
     const uint32_t grid = ctas_needed < (uint32_t)(sm_count * 2) ? ctas_needed : (uint32_t)(sm_count * 2);
