@@ -93,6 +93,13 @@ int sr_w4a4_swiglu(const void *A, const void *a_scale, const void *a_zero, const
  * these arrays live in device memory and are never read on the host.  max_k > 0 promises
  * k_p <= max_k for every problem (lets more CTAs share an SM); 0 = unknown.  A problem with
  * k % 32 != 0 or k beyond the promise is skipped and recorded in the device status word.
+ * Two kernels stand behind the call and the choice is made on the device, from the arrays: the layout
+ * the reference's MoE block builds (signrot/nn/moe.py:96-111: rows sorted by problem in one activation
+ * matrix, stacked weights, one output matrix; equal n, k and leading dimensions; at most 512 problems)
+ * with more than 16 rows per problem on average runs on the tensor cores (tcgen05, tensor maps written
+ * on the device); any other set of problems, and decode-sized calls, on a CUDA-core kernel.  The
+ * integers are the same either way.  Calls from more than 16 streams at once, or two graphs captured on
+ * one stream and replayed at the same time, would share the small device-side plan: do not do that.
  * Replaces signrot._CUDA.matmul_grouped (bindings.cpp:49-91, gemm_grouped.cu:19-120). */
 int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const void *ptr_a, const void *ptr_b,
                       const void *ptr_c, const void *lda, const void *ldb, const void *ldc, int signed_a,
@@ -359,9 +366,11 @@ int sr_peer_open(const void *ipc_handle, void **ptr);
 int sr_peer_close(void *ptr);
 int sr_peer_free(void *ptr);
 
-/* One exchange = one kernel on every rank of the group: push the message into every rank's slot with plain
- * peer stores, raise a flag, wait (bounded; code 60 + rank in sr_device_status if a rank never arrives), then
- * combine the slots into `out`.  `regions`: host array of `world` device pointers (own region at [rank]).
+/* One exchange = one kernel on every rank of the group: write the message into every rank's slot with plain
+ * 16-byte peer stores in which every other word is the exchange's sequence number (each line carries its own
+ * "arrived" mark, so there is no separate flag and no fence: one trip across the fabric), poll the own slots
+ * until every line shows the number (bounded; code 60 + rank in sr_device_status if a rank never arrives),
+ * then combine the slots into `out`.  A region holds two sets of slots, used by alternate exchanges.  `regions`: host array of `world` device pointers (own region at [rank]).
  *   mode 0  all-gather of columns: src fp16 [rows, cols] -> out fp16 [rows, world * cols]
  *   mode 1  integer all-reduce + dequant: src int32 [rows, cols] -> out fp16 [rows, cols] =
  *           rn_h((float(sum over ranks) * row_scale[m]) * col_scale[n]), the epilogue of sr_w4a4_linear

@@ -148,5 +148,8 @@ int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, in
                     const Epilogue &ep, cudaStream_t st);
 int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
                             const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st);
+int launch_gemm_tc3_ptr_array(const int32_t *sizes, int64_t P, const int64_t *ptr_a, const int64_t *ptr_b,
+                              const int64_t *ptr_c, const int64_t *lda, const int64_t *ldb, const int64_t *ldc,
+                              bool a_unsigned, int64_t k_limit, const int32_t **use_tc_flag, cudaStream_t st);
 
 }  // namespace sr

@@ -6,7 +6,11 @@
 // (signrot/kernels/bindings.cpp:49-91): nothing is read on the host, so per-expert row
 // counts that change every step do not break CUDA-graph replay.
 //
-// Persistent CTAs walk a tile list that each CTA derives from the problem sizes on the
+// Two kernels share the work and the device decides which one has it (see sr_matmul_grouped
+// below): prefill-sized calls in the MoE block's layout run on the CTA-pair tcgen05 kernel of
+// gemm_tc3.cu, everything else on the CUDA-core kernel in this file.
+//
+// Its persistent CTAs walk a tile list that each CTA derives from the problem sizes on the
 // device: problem p contributes ceil(m_p/8) x ceil(n_p/32) tiles.  A tile unpacks its
 // (at most 8) activation rows to int8 in shared memory once and streams 32 weight rows
 // through dp4a (nibble n stored as byte 16n, factor 256 removed by an exact shift).  MoE
@@ -41,9 +45,11 @@ __global__ void __launch_bounds__(256)
 gemm_grouped_kernel(uint32_t smem_bytes, const int32_t *__restrict__ sizes, uint32_t P, const int64_t *__restrict__ ptr_a,
                     const int64_t *__restrict__ ptr_b, const int64_t *__restrict__ ptr_c,
                     const int64_t *__restrict__ lda, const int64_t *__restrict__ ldb,
-                    const int64_t *__restrict__ ldc) {
+                    const int64_t *__restrict__ ldc, const int32_t *__restrict__ done_elsewhere) {
     extern __shared__ __align__(16) uint8_t a_s8[];  // [G_MT][k]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // the tensor-core kernel launched just before took the problems (its planning kernel says so)
+    if (done_elsewhere != nullptr && *done_elsewhere != 0) return;
 
     uint32_t p = 0;
     uint64_t tile_base = 0;  // first tile id of problem p
@@ -91,6 +97,7 @@ gemm_grouped_kernel(uint32_t smem_bytes, const int32_t *__restrict__ sizes, uint
         __syncthreads();
 
         const uint32_t n_end = min(n, n0 + G_NT);
+        const int m_valid = (int)min((uint32_t)G_MT, m - m0);   // rows of the tile that exist (uniform over the CTA)
         for (uint32_t nr = n0 + warp * 2; nr < n_end; nr += 16) {
             int acc[2][G_MT];
 #pragma unroll
@@ -110,6 +117,7 @@ gemm_grouped_kernel(uint32_t smem_bytes, const int32_t *__restrict__ sizes, uint
                 }
 #pragma unroll
                 for (int mm = 0; mm < G_MT; ++mm) {
+                    if (mm >= m_valid) break;
                     const uint4 *ap = reinterpret_cast<const uint4 *>(a_s8 + (size_t)mm * k + (size_t)c * 32);
                     const uint4 ae = ap[0], ao = ap[1];
 #pragma unroll
@@ -165,6 +173,16 @@ extern "C" int sr_matmul_grouped(const void *problem_sizes, int64_t problem_coun
     SR_REQUIRE(problem_sizes && ptr_a && ptr_b && ptr_c && lda && ldb && ldc, SR_ERR_INVALID,
                "matmul_grouped: null pointer");
     const int sm_count = current_sm_count();
+    // Prefill-sized calls in the layout the MoE block builds go to the tensor cores; which kernel has the
+    // work is decided on the device (nothing here may read a size), so both are launched and one returns at once.
+    const int32_t *on_tensor_cores = nullptr;
+    if (problem_count <= 512) {
+        const int rc = launch_gemm_tc3_ptr_array((const int32_t *)problem_sizes, problem_count, (const int64_t *)ptr_a,
+                                                 (const int64_t *)ptr_b, (const int64_t *)ptr_c, (const int64_t *)lda,
+                                                 (const int64_t *)ldb, (const int64_t *)ldc, signed_a == 0,
+                                                 signed_a ? 131040 : 65536, &on_tensor_cores, as_stream(stream));
+        if (rc) return rc;
+    }
     auto kfn = signed_a ? gemm_grouped_kernel<false> : gemm_grouped_kernel<true>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul_grouped: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -180,6 +198,6 @@ extern "C" int sr_matmul_grouped(const void *problem_sizes, int64_t problem_coun
     kfn<<<sm_count * ctas_per_sm, 256, smem, as_stream(stream)>>>((uint32_t)smem, (const int32_t *)problem_sizes, (uint32_t)problem_count,
                                                      (const int64_t *)ptr_a, (const int64_t *)ptr_b,
                                                      (const int64_t *)ptr_c, (const int64_t *)lda,
-                                                     (const int64_t *)ldb, (const int64_t *)ldc);
+                                                     (const int64_t *)ldb, (const int64_t *)ldc, on_tensor_cores);
     return check_launch("matmul_grouped");
 }

@@ -180,6 +180,93 @@ def test_grouped_matches_dense():
         assert _lib.device_status() == 0
 
 
+def _grouped_case(ms, n, k, signed, seed=0, ldc=None, order=None):
+    """Device arrays of one matmul_grouped call in the layout signrot/nn/moe.py:96-111 builds (rows sorted by
+    problem, stacked weights, one output matrix); `order` permutes the problem list, which keeps every problem
+    valid but is no longer that layout."""
+    P = len(ms)
+    ldc = ldc or n
+    a_all = _codes(sum(ms), k, 1 + seed, -8 if signed else 0, 8 if signed else 16)
+    A = oracle.pack_codes(a_all).to(DEV)
+    Bs = [oracle.pack_i4(_codes(n, k, 10 + seed + i)) for i in range(P)]
+    B = torch.stack(Bs).to(DEV)
+    C = torch.full((sum(ms), ldc), -777, dtype=torch.int32, device=DEV)
+    off = torch.tensor([sum(ms[:i]) for i in range(P)], dtype=torch.int64)
+    idx = torch.tensor(order if order is not None else list(range(P)))
+    ps = torch.tensor([[m, n, k] for m in ms], dtype=torch.int32)[idx].to(DEV)
+    ptr_a = (A.data_ptr() + off * (k // 2))[idx].to(DEV)
+    ptr_b = (B.data_ptr() + torch.arange(P, dtype=torch.int64) * B.stride(0))[idx].to(DEV)
+    ptr_c = (C.data_ptr() + off * (ldc * 4))[idx].to(DEV)
+    ld_ab = torch.full((P,), k, dtype=torch.int64, device=DEV)
+    ld_c = torch.full((P,), ldc, dtype=torch.int64, device=DEV)
+    return dict(a_all=a_all, A=A, Bs=Bs, B=B, C=C, ps=ps, ptr_a=ptr_a, ptr_b=ptr_b, ptr_c=ptr_c, ld_ab=ld_ab,
+                ld_c=ld_c, ms=ms, n=n, signed=signed)
+
+
+def _check_grouped(c):
+    got = c["C"].cpu()
+    row = 0
+    for i, m in enumerate(c["ms"]):
+        want = oracle.matmul_i4(oracle.pack_codes(c["a_all"][row:row + m]), c["Bs"][i], a_unsigned=not c["signed"])
+        assert torch.equal(got[row:row + m, :c["n"]], want), f"problem {i}"
+        row += m
+    assert bool((got[:, c["n"]:] == -777).all())          # padding columns of a wide output stay untouched
+
+
+@pytest.mark.parametrize("signed", [True, False])
+def test_grouped_prefill_size_on_both_kernels(signed):
+    """The pointer-array entry at prefill size.  The expert-sorted layout goes to the tensor cores, the same problems
+    listed in another order (a layout the planning kernel does not recognise) go to the CUDA-core kernel, and so does a
+    decode-sized call; all give the oracle's integers.  Sizes: 8 experts, uneven rows incl. an empty expert, n not a
+    multiple of the tile, an output matrix wider than n."""
+    ms = [700, 0, 129, 256, 1, 333, 64, 517]
+    for kwargs in (dict(), dict(order=[3, 0, 7, 1, 2, 6, 5, 4]), dict(ldc=328)):
+        c = _grouped_case(ms, 320, 1024, signed, seed=3, **kwargs)
+        kernel.matmul_grouped(c["ps"], c["ptr_a"], c["ptr_b"], c["ptr_c"], c["ld_ab"], c["ld_ab"], c["ld_c"],
+                              signed_a=signed)
+        _check_grouped(c)
+    c = _grouped_case([3, 0, 2, 1], 320, 1024, signed, seed=4)
+    kernel.matmul_grouped(c["ps"], c["ptr_a"], c["ptr_b"], c["ptr_c"], c["ld_ab"], c["ld_ab"], c["ld_c"], signed_a=signed)
+    _check_grouped(c)
+    assert _lib.device_status() == 0
+
+
+def test_grouped_graph_replay_switches_kernels_with_the_sizes():
+    """Nothing of a matmul_grouped call is read on the host (signrot/kernels/bindings.cpp:49-91), so a captured call
+    follows the device arrays: replayed with prefill-sized row counts it runs on the tensor cores, with a few rows per
+    expert on the CUDA cores, and back, from one capture."""
+    big = _grouped_case([300, 40, 0, 260], 256, 512, True, seed=5)
+    small_ms = [2, 1, 0, 3]
+    ps, ptr_a, ptr_c = big["ps"].clone(), big["ptr_a"].clone(), big["ptr_c"].clone()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        kernel.matmul_grouped(ps, ptr_a, big["ptr_b"], ptr_c, big["ld_ab"], big["ld_ab"], big["ld_c"])  # warm-up
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            kernel.matmul_grouped(ps, ptr_a, big["ptr_b"], ptr_c, big["ld_ab"], big["ld_ab"], big["ld_c"])
+    off_small = torch.tensor([sum(small_ms[:i]) for i in range(4)], dtype=torch.int64)
+    for ms in (big["ms"], small_ms, big["ms"]):
+        if ms is small_ms:
+            ps.copy_(torch.tensor([[m, 256, 512] for m in ms], dtype=torch.int32))
+            ptr_a.copy_(big["A"].data_ptr() + off_small * 256)
+            ptr_c.copy_(big["C"].data_ptr() + off_small * 256 * 4)
+        else:
+            ps.copy_(big["ps"]); ptr_a.copy_(big["ptr_a"]); ptr_c.copy_(big["ptr_c"])
+        big["C"].fill_(-777)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = big["C"].cpu()
+        row = 0
+        for i, m in enumerate(ms):
+            want = oracle.matmul_i4(oracle.pack_codes(big["a_all"][row:row + m]), big["Bs"][i])
+            assert torch.equal(got[row:row + m], want)
+            row += m
+        assert bool((got[row:] == -777).all())
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize("M", [1, 8, 13, 16, 32, 40])
 @pytest.mark.parametrize("F,K", [(1536, 512), (14336, 4096), (104, 256)])
 @pytest.mark.parametrize("asym", [False, True])
