@@ -318,7 +318,7 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     // two m-tiles per warp step when there are enough row blocks to keep every SM busy and the sums fit
     const int mt = (nt <= 4 && (N >= 8192 || (N >= 4096 && nt >= 2))) ? 2 : 1;   // measured crossover
     const int64_t blocks = cdiv<int64_t>(N, SK_ROWS * mt) * (grouped ? num_experts : 1);
-    // warps per row block: SIGNROT_B200_SKINNY_KW = 2 | 8 pins it (A/B runs); see skinny_kw()
+    // warps per row block: see skinny_kw()
     const int kw = skinny_kw(blocks, K, sm_count, grouped);
     const int groups = SK_WARPS / kw;
     // two CTAs per SM; the row blocks are dealt round-robin to the warp groups, so shrink the grid to even the deal out
