@@ -39,6 +39,14 @@ extern "C" {
 #define SR_BF16 1
 #define SR_F32 2
 
+/* Read-only operands and early loads.  Kernels of the decode step are launched with programmatic
+ * stream serialization: they may start while the kernel before them on the stream is finishing, and
+ * they fetch their constant operands -- weights (B / W), weight scales and sums, the hadK table and
+ * the sign tables -- BEFORE they wait for that kernel.  Those buffers must therefore not be written
+ * by work enqueued earlier on the same stream without a synchronisation in between (a weight that
+ * was just packed, a table that was just cast).  Activations, codes, scales of activations, caches
+ * and workspaces carry no such restriction.  SIGNROT_B200_PDL=0 removes the early start. */
+
 const char *sr_last_error(void);
 int sr_version(void);
 

@@ -46,7 +46,7 @@ def default_quantization_config(cfg) -> dict:
         "k_bits": 4, "k_asym": True, "k_groupsize": cfg.head_dim, "k_clip_ratio": 1.0,
         "v_bits": 4, "v_asym": True, "v_groupsize": cfg.head_dim, "v_clip_ratio": 1.0,
         "format": "packed_int4",
-        "rotate": True, "rotate_mode": "hadamard", "fp32_had": False,
+        "rotate": True, "rotate_mode": "hadamard", "fp32_had": bool(getattr(cfg, "fp32_had", False)),
         "adj_layers": ["down_proj"] if cfg.had_adj else [],
         "int8_down_proj": False,
     }
@@ -201,7 +201,27 @@ def load_packed_checkpoint(load_path: str, device="cuda", fuse_edges=True):
         raise RuntimeError("only packed symmetric int4 checkpoints are supported")
     if qcfg.get("a_bits", 4) != 4:
         raise RuntimeError("the kernels quantize activations to 4 bits")
+    # Settings the model would otherwise run differently from what the checkpoint was calibrated for
+    # (the keys of realquant_utils.py:33-49): the online rotations are Hadamard, the cache is 4-bit asymmetric
+    # per head vector, down_proj takes 4-bit activations.
+    if qcfg.get("rotate_mode", "hadamard") != "hadamard":
+        raise RuntimeError(f"rotate_mode {qcfg['rotate_mode']!r} is not supported: the online rotations are Hadamard")
+    for which in ("k", "v"):
+        if qcfg.get(f"{which}_bits", 4) != 4 or not qcfg.get(f"{which}_asym", True):
+            raise RuntimeError(f"the KV cache stores asymmetric 4-bit codes; the checkpoint asks for "
+                               f"{which}_bits={qcfg.get(f'{which}_bits')}, {which}_asym={qcfg.get(f'{which}_asym')}")
+    if qcfg.get("int8_down_proj", False):
+        raise RuntimeError("int8_down_proj checkpoints are not supported")
     heads = config["num_attention_heads"]
+    with Safetensors(load_path, "cpu") as st:
+        all_keys = set(st.keys())
+    bias_keys = {k for k in all_keys if k.endswith(".bias")}
+    qkv_bias = {f"model.layers.{i}.self_attn.{n}.bias" for i in range(config["num_hidden_layers"])
+                for n in ("q_proj", "k_proj", "v_proj")}
+    if bias_keys - qkv_bias:
+        raise RuntimeError(f"bias on a projection that has no bias slot: {sorted(bias_keys - qkv_bias)[0]}")
+    if bias_keys and bias_keys != qkv_bias:
+        raise RuntimeError("q/k/v biases must be present for every layer or for none")
     cfg = ku.DecoderConfig(
         hidden_size=config["hidden_size"], intermediate_size=config["intermediate_size"],
         num_hidden_layers=config["num_hidden_layers"], num_attention_heads=heads,
@@ -209,7 +229,8 @@ def load_packed_checkpoint(load_path: str, device="cuda", fuse_edges=True):
         head_dim=config.get("head_dim") or config["hidden_size"] // heads, vocab_size=config["vocab_size"],
         rms_norm_eps=config.get("rms_norm_eps", 1e-5), rope_theta=config.get("rope_theta", 10000.0),
         a_asym=bool(qcfg.get("a_asym", False)), a_clip_ratio=float(qcfg.get("a_clip_ratio", 1.0)),
-        had_adj="down_proj" in (qcfg.get("adj_layers") or []), fuse_edges=fuse_edges)
+        had_adj="down_proj" in (qcfg.get("adj_layers") or []), fp32_had=bool(qcfg.get("fp32_had", False)),
+        attention_bias=bool(bias_keys), fuse_edges=fuse_edges)
     with torch.device(device):
         model = ku.KernelDecoderModel(cfg)
     model = model.to(device)
@@ -228,6 +249,8 @@ def load_packed_checkpoint(load_path: str, device="cuda", fuse_edges=True):
                     raise RuntimeError(f"{key}.weight: expected packed uint8 {tuple(mod.weight.shape)}, got {w.dtype} {tuple(w.shape)}")
                 mod.weight.copy_(w)
                 mod.weight_scales = st.get_tensor(f"quantizer.{key}.scale").to(torch.float16).reshape(-1, 1).contiguous()
+                if key + ".bias" in keys:
+                    mod.bias.copy_(st.get_tensor(key + ".bias").to(torch.float16))
                 sign_key = key + ".had_adj_sign"
                 had = lin.kernel_hadamard
                 if sign_key in keys:

@@ -592,6 +592,27 @@ def had_scale(n: int) -> float:
     return float(1.0 / torch.tensor(n).sqrt())
 
 
+_HADK_CACHE = {}
+
+
+def _hadk_as(hadK, device, dtype):
+    """`hadK` on `device` in `dtype`.  A table that already is there is passed through; any other is converted once
+    and the copy kept: the rotation kernels are launched with programmatic dependent launch and read the table
+    before they wait for the kernel in front of them, so it must not be the output of a cast enqueued just before."""
+    if hadK.device == device and hadK.dtype == dtype and hadK.is_contiguous():
+        return hadK
+    key = (hadK.data_ptr(), hadK._version, tuple(hadK.shape), hadK.dtype, str(device), dtype)
+    hit = _HADK_CACHE.get(key)
+    if hit is None:
+        if len(_HADK_CACHE) > 64:
+            _HADK_CACHE.clear()
+        hit = hadK.to(device=device, dtype=dtype).contiguous()
+        if hit.is_cuda and not torch.cuda.is_current_stream_capturing():
+            torch.cuda.current_stream(hit.device).synchronize()     # once per table: the copy is complete before any use
+        _HADK_CACHE[key] = hit
+    return hit
+
+
 def hadamard(x, hadK=None, K=1, sign=None, fp32_mode=False, out_dtype=None, scale=None):
     """`matmul_hadU_cuda(x, hadK, K)` (signrot/functional/hadamard.py:78-87), optionally
     followed by the +-1 `sign` multiply and the cast of `OnlineHadamard.forward`
@@ -604,7 +625,7 @@ def hadamard(x, hadK=None, K=1, sign=None, fp32_mode=False, out_dtype=None, scal
     out_dtype = out_dtype or x.dtype
     if K > 1:
         want = torch.float32 if (fp32_mode or x.dtype == torch.float32) else torch.float16
-        hadK = hadK.to(device=x.device, dtype=want).contiguous()
+        hadK = _hadk_as(hadK, x.device, want)
     else:
         hadK = None
     dev = require_cuda("hadamard", x2, hadK, sign)
@@ -641,7 +662,7 @@ def rotate_quant(x, hadK=None, K=1, sign=None, expert_ids=None, heads=0, clip_ra
     n = x.shape[-1]
     x2, lead = _rows(x)
     if K > 1:
-        hadK = hadK.to(device=x.device, dtype=torch.float16).contiguous()
+        hadK = _hadk_as(hadK, x.device, torch.float16)
     else:
         hadK = None
     dev = require_cuda("rotate_quant", x2, hadK, sign, expert_ids)

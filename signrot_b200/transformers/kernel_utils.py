@@ -282,6 +282,8 @@ class DecoderConfig:
     a_asym: bool = False
     a_clip_ratio: float = 1.0
     had_adj: bool = True              # SignRot sign vector on down_proj's rotation
+    fp32_had: bool = False            # online rotations in fp32, one rounding after the transform (OnlineHadamard force_fp32)
+    attention_bias: bool = False      # q/k/v projections carry a bias (Qwen-style checkpoints)
     fuse_edges: bool = True           # fused launches across the path's edges (same bits as the separate ones)
 
 
@@ -292,10 +294,11 @@ class KernelAttention(torch.nn.Module):
         kw = dict(asym=cfg.a_asym, clip_ratio=cfg.a_clip_ratio)
         self.head_dim = cfg.head_dim
         self.layer_idx = layer_idx
-        self.q_proj = KernelLinear(cfg.hidden_size, q_out, **kw)
-        self.k_proj = KernelLinear(cfg.hidden_size, kv_out, **kw)
-        self.v_proj = KernelLinear(cfg.hidden_size, kv_out, **kw)
-        self.o_proj = KernelLinear(q_out, cfg.hidden_size, online_partial_had=True, had_dim=cfg.head_dim, **kw)
+        self.q_proj = KernelLinear(cfg.hidden_size, q_out, bias=cfg.attention_bias, **kw)
+        self.k_proj = KernelLinear(cfg.hidden_size, kv_out, bias=cfg.attention_bias, **kw)
+        self.v_proj = KernelLinear(cfg.hidden_size, kv_out, bias=cfg.attention_bias, **kw)
+        self.o_proj = KernelLinear(q_out, cfg.hidden_size, online_partial_had=True, had_dim=cfg.head_dim,
+                                   fp32_had=cfg.fp32_had, **kw)
 
     forward = kernel_attention_forward
 
@@ -307,7 +310,7 @@ class KernelMLP(torch.nn.Module):
         self.gate_proj = KernelLinear(cfg.hidden_size, cfg.intermediate_size, **kw)
         self.up_proj = KernelLinear(cfg.hidden_size, cfg.intermediate_size, **kw)
         self.down_proj = KernelLinear(cfg.intermediate_size, cfg.hidden_size, online_full_had=True,
-                                      had_adj=cfg.had_adj, **kw)
+                                      had_adj=cfg.had_adj, fp32_had=cfg.fp32_had, **kw)
 
     forward = kernel_mlp_forward
 

@@ -73,6 +73,55 @@ def test_loader_rejects_other_formats(tmp_path):
         ck.load_packed_checkpoint(str(tmp_path), device="cpu")
 
 
+def _edit_qcfg(tmp_path, **changes):
+    path = os.path.join(tmp_path, "config.json")
+    cfg = json.load(open(path))
+    cfg["quantization_config"].update(changes)
+    json.dump(cfg, open(path, "w"))
+
+
+@pytest.mark.parametrize("changes", [dict(rotate_mode="random"), dict(k_bits=16), dict(v_bits=8), dict(k_asym=False),
+                                     dict(v_asym=False), dict(int8_down_proj=True), dict(a_bits=8)])
+def test_loader_rejects_settings_the_kernels_do_not_run(tmp_path, changes):
+    """Every key of the reference's quantization_config (realquant_utils.py:33-49) that would change the arithmetic is
+    either honoured or refused; none is ignored."""
+    ck.save_packed_checkpoint(tiny_model(), str(tmp_path))
+    _edit_qcfg(tmp_path, **changes)
+    with pytest.raises(RuntimeError):
+        ck.load_packed_checkpoint(str(tmp_path), device="cpu")
+
+
+def test_bias_and_fp32_rotation_survive_the_round_trip(tmp_path):
+    cfg = ku.DecoderConfig(hidden_size=256, intermediate_size=768, num_hidden_layers=2, num_attention_heads=2,
+                           num_key_value_heads=1, head_dim=128, vocab_size=96, attention_bias=True, fp32_had=True)
+    model = ku.KernelDecoderModel(cfg).random_init_(3)
+    g = torch.Generator().manual_seed(0)
+    for layer in model.layers:
+        for name in ("q_proj", "k_proj", "v_proj"):
+            mod = getattr(layer.self_attn, name).kernel_module
+            mod.bias.copy_(torch.randn(mod.bias.shape, generator=g).half())
+    ck.save_packed_checkpoint(model, str(tmp_path))
+    _, qcfg = ck.read_config(str(tmp_path))
+    assert qcfg["fp32_had"] is True
+    back = ck.load_packed_checkpoint(str(tmp_path), device="cpu", fuse_edges=False)
+    assert back.config.attention_bias and back.config.fp32_had
+    assert back.layers[1].mlp.down_proj.fp32_had and back.layers[0].self_attn.o_proj.fp32_had
+    for a, b in zip(model.layers, back.layers):
+        for name in ("q_proj", "k_proj", "v_proj"):
+            assert torch.equal(getattr(a.self_attn, name).kernel_module.bias, getattr(b.self_attn, name).kernel_module.bias)
+
+
+def test_loader_refuses_a_bias_without_a_slot(tmp_path):
+    """A bias on a projection the decoder has no bias for (o_proj here) is an error, not a silently dropped tensor."""
+    model = tiny_model()
+    sd = ck.packed_state_dict(model)
+    sd["model.layers.0.self_attn.o_proj.bias"] = torch.zeros(256, dtype=torch.float16)
+    ck.save_quantized_weights_with_safetensors(sd, ck.model_config_dict(model.config),
+                                               ck.default_quantization_config(model.config), str(tmp_path))
+    with pytest.raises(RuntimeError, match="bias"):
+        ck.load_packed_checkpoint(str(tmp_path), device="cpu")
+
+
 @pytest.mark.skipif(not ref_shim.available(), reason="no SignRot checkout on this machine")
 def test_reference_loader_reads_our_checkpoint(tmp_path):
     """The reference's `load_quantized_weights_with_safetensors` (realquant_utils.py:266-339) on a
