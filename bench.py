@@ -10,15 +10,22 @@ sign-adjusted online Hadamard rotation + per-token int4 quantization (one fused 
 bf16 activations) followed by the W4A4 GEMM with fused dequant epilogue (fp16 output).
 Inputs are seeded synthetic tensors (activations ~N(0,1) with 0.1 % of channels x100, uniform
 int4 weight codes, fp16 scales).  Metric: TOP/s = 2*M*N*K summed over the three linears /
-device time.  With N > 1 every rank runs the same step on its own token rows (the path is
-row-parallel: no data-path collective); the timed region is bracketed by a barrier and a
-device synchronise and the slowest rank's time is used.
+device time.  With N > 1 the group shares ONE problem and runs it tensor-parallel (Megatron
+split: the (4096, 14336) linear by output columns, the other two by input channels with an
+all-gather of the input shards and an int32 all-reduce of the partial sums): strong scaling;
+the timed region is bracketed by a barrier and a device synchronise and the slowest rank's
+time is used.  `rows_data_parallel` gives the same three linears with the token rows dealt
+to the ranks instead (no collective), `decode_llama3_8b` / `decode_mixtral_8x7b_shape` the
+full-model and sparse-stack decode at tensor / expert parallelism N.
 
 The JSON line also carries: `roofline` (the tcgen05 GEMM against the int8 tensor peak,
-measured here with torch._int_mm), `rotate_quant` (the fused kernel against the HBM copy
-peak), `e2e` (the same step through the public API from pinned host buffers, copies timed),
-`cpu_baseline` (the CPU oracle's fake-quant statement of the same step on a bounded row
-sample), `clocks` (NVML samples taken during the timed region) and `gpu_launches`.
+measured here with torch._int_mm), `rotate_quant` (the fused kernels against the HBM copy
+peak: per-launch events, the marginal cost inside the step, and back to back), `sustained`
+(the step repeated for seconds, with the sampled SM clock), `e2e` (the same step through
+the public API from pinned host buffers, copies timed), `cpu_baseline` (the reference's own
+CPU fake-quant forward of the same step on a bounded row sample, or the oracle's restatement
+of it when the reference's files are absent), `clocks` (NVML samples taken during the timed
+region) and `gpu_launches`.
 """
 from __future__ import annotations
 
@@ -498,6 +505,17 @@ def run_ours(args, rank, world, local_rank):
     del x_dev, y_keep, step, sets
     torch.cuda.empty_cache()
 
+    # ---- several GPUs: the same three linears with the token rows dealt to the ranks instead (every rank its own
+    # 4096 rows, no collective on the path), for comparison with the tensor-parallel step above
+    dp_ms = None
+    if world > 1:
+        dp_step = QlinearStep(rank, 1, dev)
+        for i in range(args.warmup):
+            dp_step.run(i)
+        dp_ms, _ = timed_steps(dp_step, args.steps, world, dev, local_rank)
+        del dp_step
+        torch.cuda.empty_cache()
+
     # ---- the full-model and sparse-stack configurations at this group size (decode tokens/s)
     extras = {}
     if not args.no_models:
@@ -581,6 +599,11 @@ def run_ours(args, rank, world, local_rank):
                               "note": "CUDA-graph replay of 16 launches per shape, inputs rotate over > 126 MB"}
                              if rot_only_ms and len(rot_only_ms) == 3 else None)}
     else:
+        out["rows_data_parallel"] = {
+            "value": round(world * ops * args.steps / (dp_ms * 1e-3) / 1e12, 2), "unit": "TOP/s",
+            "ms_per_step": round(dp_ms / args.steps, 4), "scaling": "weak",
+            "note": "every rank runs the one-GPU step on its own 4096 token rows (rows are independent: no collective); "
+                    "the headline value above is the tensor-parallel step on ONE shared problem"}
         out["gpu_launches"] = 10 * args.steps      # per rank: 3 rotate+quant, 3 GEMM, 2 code-slice copies, 2 dequant
         out["roofline"] = {"kernel": "gemm_tc3_kernel on the per-rank shards", "bound": "tensor", "achieved": None,
                            "peak": round(int8_peak, 1), "unit": "TOP/s", "frac": None, "traffic": None,
