@@ -20,6 +20,7 @@
 // with an exact shift.  The eight partial accumulators of a block meet in shared memory.
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -215,7 +216,12 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
             for (int t = 0; t < NT; ++t)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[m][t][i] = 0;
-        if (has_steps) {
+        // token blocks of 8 that exist in this pass (uniform over the CTA): the step loop is instantiated for every count,
+        // so the missing ones cost no nibble expansion and no MMA (a grouped launch sizes its passes for 8 * NT rows,
+        // most experts of a decode batch have fewer)
+        const int tb = (int)min((uint32_t)NT, (cur.x_end - cur.x_row0 + 7u) >> 3);
+        auto run_steps = [&](auto tb_tag) {
+            constexpr int TB = decltype(tb_tag)::value;
 #pragma unroll 1
             for (uint32_t s = kw; s < steps; s += KW) {
                 uint4 x[NT];
@@ -229,9 +235,9 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                 for (int r = 0; r < 2 * MT; ++r) w[r] = ring[slot * (STAGE / 16) + r * 32];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    uint32_t be[NT], bo[NT];
+                    uint32_t be[TB], bo[TB];
 #pragma unroll
-                    for (int t = 0; t < NT; ++t) {
+                    for (int t = 0; t < TB; ++t) {
                         const uint32_t px = word(x[t], j);
                         be[t] = (px << 4) & 0xF0F0F0F0u;
                         bo[t] = px & 0xF0F0F0F0u;
@@ -245,12 +251,18 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                         a[2] = pl & 0xF0F0F0F0u;          // row g,     odd nibbles
                         a[3] = ph & 0xF0F0F0F0u;          // row g + 8, odd nibbles
 #pragma unroll
-                        for (int t = 0; t < NT; ++t) mma_s8<A_UNSIGNED>(acc[m][t], a, be[t], bo[t]);
+                        for (int t = 0; t < TB; ++t) mma_s8<A_UNSIGNED>(acc[m][t], a, be[t], bo[t]);
                     }
                 }
                 issue(slot);   // after the math that consumed the slot
                 slot = slot + 1 == DEPTH ? 0 : slot + 1;
             }
+        };
+        if (has_steps) {
+            if (NT == 1 || NT > 4 || tb >= NT) run_steps(std::integral_constant<int, NT>{});
+            else if (tb <= 1) run_steps(std::integral_constant<int, 1>{});
+            else if (tb == 2) run_steps(std::integral_constant<int, (NT >= 2 ? 2 : NT)>{});
+            else run_steps(std::integral_constant<int, (NT >= 3 ? 3 : NT)>{});
         }
         if (RED_BUFS == 1) group_sync();   // the previous block's sums have been read
         int *rb = red + (size_t)parity * KW * MT * NT * 128;
@@ -266,6 +278,7 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
         if (SWIGLU) {
             for (int idx = gtid; idx < NT * 128; idx += KW * 32) {
                 const int l = idx & 31, i = (idx >> 5) & 3, t = idx >> 7;
+                if (t >= tb) continue;
                 int sg = 0, su = 0;
 #pragma unroll
                 for (int w = 0; w < KW; ++w) {
@@ -284,6 +297,7 @@ gemm_skinny_kernel(const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
         } else
         for (int idx = gtid; idx < MT * NT * 128; idx += KW * 32) {
             const int l = idx & 31, i = (idx >> 5) & 3, t = (idx >> 7) % NT, m = idx / (NT * 128);
+            if (t >= tb) continue;
             int sum = 0;
 #pragma unroll
             for (int w = 0; w < KW; ++w) sum += rb[(((w * MT + m) * NT + t) * 4 + i) * 32 + l];
