@@ -119,10 +119,14 @@ int sr_matmul_grouped(const void *problem_sizes, int64_t problem_count, const vo
  * reference runs as matmul_grouped followed by sym_dequant_moe (signrot/nn/moe.py:114-162,
  * signrot/kernels/moe.cu:190-233): out[r, n] = rn_h((float(acc) * a_scale[r]) * w_scale[e, n]) with
  * e = expert_ids[r] (int32 [rows]); asymmetric activations pass a_zero int8 [rows] and w_sum int32
- * [num_experts, N].  Runs on the tcgen05 CTA-pair kernel; at most 512 experts. */
+ * [num_experts, N].  At most 512 experts.  Few rows per expert (16 or fewer on average) run on the
+ * weight-streaming kernel, more on the tcgen05 CTA-pair kernel.  `rows` is the size of A and out;
+ * `expected_rows` (0 = rows) is how many of them the offsets are expected to cover, for a caller whose
+ * offsets describe a part of A only (an expert-parallel rank passes its own experts' slice of the
+ * offsets and rows * local experts / all experts): only the choice of kernel depends on it. */
 int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
                       const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
-                      int64_t num_experts, int64_t N, int64_t K, void *out, void *stream);
+                      int64_t num_experts, int64_t N, int64_t K, int64_t expected_rows, void *out, void *stream);
 
 /* ------------------------------------------------------------------ quantizers */
 

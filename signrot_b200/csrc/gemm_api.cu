@@ -99,7 +99,7 @@ int sr_w4a4_swiglu(const void *A, const void *a_scale, const void *a_zero, const
 
 int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, const void *expert_ids,
                       const void *row_offsets, const void *W, const void *w_scale, const void *w_sum, int64_t rows,
-                      int64_t num_experts, int64_t N, int64_t K, void *out, void *stream) {
+                      int64_t num_experts, int64_t N, int64_t K, int64_t expected_rows, void *out, void *stream) {
     SR_REQUIRE(rows >= 0 && N >= 0 && K >= 0 && num_experts >= 1, SR_ERR_INVALID, "grouped_linear: bad size");
     if (rows == 0 || N == 0) return SR_OK;
     SR_REQUIRE(K > 0 && K % 32 == 0, SR_ERR_INVALID, "grouped_linear: K = %lld must be a positive multiple of 32",
@@ -119,7 +119,8 @@ int sr_grouped_linear(const void *A, const void *a_scale, const void *a_zero, co
     ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
     ep.expert_ids = (const int32_t *)expert_ids;
     // few rows per expert (decode): the weight-streaming kernel; otherwise the CTA-pair tensor-core kernel
-    if (rows <= 16 * num_experts)
+    const int64_t covered = expected_rows > 0 && expected_rows < rows ? expected_rows : rows;
+    if (covered <= 16 * num_experts)
         return launch_gemm_skinny_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,
                                           (const int32_t *)row_offsets, (int)num_experts, as_stream(stream));
     return launch_gemm_tc3_grouped((const uint8_t *)A, (const uint8_t *)W, rows, N, K, a_zero != nullptr, ep,

@@ -405,7 +405,8 @@ def matmul_colrow_i8_i32(a_col, b_row) -> torch.Tensor:
 
 # ---------------------------------------------------------------------------- fused operators
 
-def grouped_linear(packed: PackedQuantizedTensor, expert_ids, row_offsets, weight, weight_scales, weight_sum=None):
+def grouped_linear(packed: PackedQuantizedTensor, expert_ids, row_offsets, weight, weight_scales, weight_sum=None,
+                   expected_rows=0):
     """fp16 `dequant(packed[r] @ weight[e_r].T)` for expert-sorted rows in ONE launch: the grouped
     GEMM plus expert-indexed dequant of the sparse MoE block (signrot/nn/moe.py:114-162,
     functional/kernel.py:83-110 + 146-159).  `packed` rows sorted by expert, `expert_ids` int32
@@ -439,7 +440,7 @@ def grouped_linear(packed: PackedQuantizedTensor, expert_ids, row_offsets, weigh
         _check_dtype("grouped_linear", weight_sum, torch.int32)
     out = torch.empty((rows, N), dtype=torch.float16, device=dev)
     run(dev, "sr_grouped_linear", ptr(qx), ptr(sx), ptr(zx), ptr(expert_ids), ptr(row_offsets), ptr(weight),
-        ptr(weight_scales), ptr(weight_sum) if zx is not None else None, rows, E, N, K, ptr(out))
+        ptr(weight_scales), ptr(weight_sum) if zx is not None else None, rows, E, N, K, int(expected_rows), ptr(out))
     return out
 
 

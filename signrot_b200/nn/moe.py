@@ -85,6 +85,7 @@ class SignRotMoEBlock(torch.nn.Module):
             per_token = kernel.PackedQuantizedTensor(*kernel.sym_quant_dynamic(x16, self.clip_ratio))
         routed = kernel.moe_gather(per_token, tok)      # a token's experts, and gate/up, read the same codes
         ep = self._ep
+        covered = 0                             # rows the offsets passed below cover: all of them
         if ep is None:
             eid_w, off_w, rng = eid, row_off, None
         else:
@@ -93,8 +94,10 @@ class SignRotMoEBlock(torch.nn.Module):
             # ids index the local weight stacks; the sign table stays global.
             e0, e1 = ep[1], ep[2]
             eid_w, off_w, rng = eid - e0, row_off[e0:e1 + 1], row_off[e0:e1 + 1:e1 - e0].contiguous()
-        gate_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_gate, self.s_gate, self.wsum_gate)
-        up_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_up, self.s_up, self.wsum_up)
+            # about this share of the routed rows (the counts live on the device): picks the decode or the prefill kernel
+            covered = max(1, routed.quantized_x.shape[0] * (e1 - e0) // self.num_experts)
+        gate_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_gate, self.s_gate, self.wsum_gate, covered)
+        up_h = kernel.grouped_linear(routed, eid_w, off_w, self.w_up, self.s_up, self.wsum_up, covered)
         inter = kernel.swiglu(gate_h, up_h)
         sign_ids = eid if self.sign_down is not None else None
         if self.fp32_had:
@@ -111,7 +114,7 @@ class SignRotMoEBlock(torch.nn.Module):
         else:
             pk = kernel.rotate_quant(inter, self.had_K, self.K, sign=self.sign_down, expert_ids=sign_ids,
                                      clip_ratio=self.clip_ratio, asym=self.asym)
-        y = kernel.grouped_linear(pk, eid_w, off_w, self.w_down, self.s_down, self.wsum_down)
+        y = kernel.grouped_linear(pk, eid_w, off_w, self.w_down, self.s_down, self.wsum_down, covered)
         if ep is None:
             out = kernel.moe_combine(y, weights, inv)
         else:
