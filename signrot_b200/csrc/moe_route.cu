@@ -23,14 +23,16 @@ constexpr int RT_THREADS = 1024;
 constexpr int RT_MAX_EXPERTS = 512;
 constexpr int RT_MAX_TOPK = 8;
 
-// softmax + top-k of one token by one warp; lane l owns experts l, l + 32, ...
-__device__ __forceinline__ void route_token(const __half *__restrict__ logits, uint32_t t, uint32_t E, uint32_t k,
-                                            int renorm, __half *__restrict__ weights, int32_t *__restrict__ chosen,
-                                            int lane) {
-    float p[RT_MAX_EXPERTS / 32];
+// softmax + top-k of one token by one warp; lane l owns experts l, l + 32, ... (EPL of them).  Result j of the top-k
+// lives in lane j until the end, so nothing is indexed at run time.  `stage`: shared-memory copy of the chosen ids, or null.
+template <int EPL>
+__device__ __forceinline__ void route_token_n(const __half *__restrict__ logits, uint32_t t, uint32_t E, uint32_t k,
+                                              int renorm, __half *__restrict__ weights, int32_t *__restrict__ chosen,
+                                              uint16_t *stage, int lane) {
+    float p[EPL];
     float mx = -FLT_MAX;
 #pragma unroll
-    for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i) {
+    for (int i = 0; i < EPL; ++i) {
         const uint32_t e = lane + 32 * i;
         float v = e < E ? __half2float(logits[(size_t)t * E + e]) : -FLT_MAX;
         // non-finite logits (an overflowed router) must still give k valid expert ids: NaN ranks highest, as in
@@ -42,23 +44,22 @@ __device__ __forceinline__ void route_token(const __half *__restrict__ logits, u
     mx = warp_max(mx);
     float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i) {
+    for (int i = 0; i < EPL; ++i) {
         const uint32_t e = lane + 32 * i;
         p[i] = e < E ? expf(p[i] - mx) : 0.f;
         sum += p[i];
     }
     sum = warp_sum(sum);
 #pragma unroll
-    for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i) p[i] = (lane + 32 * i) < E ? p[i] / sum : -1.f;
-    float top_v[RT_MAX_TOPK];
-    int top_i[RT_MAX_TOPK];
-    float tot = 0.f;
+    for (int i = 0; i < EPL; ++i) p[i] = (lane + 32 * i) < E ? p[i] / sum : -1.f;
+    float my_v = 0.f, tot = 0.f;
+    int my_i = 0;
     for (uint32_t j = 0; j < k; ++j) {
         // this lane's best, then the warp's best; equal values: the lower expert index wins
         float bv = -1.f;
         int bi = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i)
+        for (int i = 0; i < EPL; ++i)
             if (p[i] > bv) {
                 bv = p[i];
                 bi = lane + 32 * i;
@@ -73,19 +74,29 @@ __device__ __forceinline__ void route_token(const __half *__restrict__ logits, u
             }
         }
         bi = min(bi, (int)E - 1);               // always an id a weight stack has
-        top_v[j] = bv;
-        top_i[j] = bi;
+        if (lane == (int)j) {
+            my_v = bv;
+            my_i = bi;
+        }
         tot += bv;
 #pragma unroll
-        for (int i = 0; i < RT_MAX_EXPERTS / 32; ++i)
+        for (int i = 0; i < EPL; ++i)
             if (lane + 32 * i == bi) p[i] = -1.f;   // taken
     }
-    if (lane == 0)
-        for (uint32_t j = 0; j < k; ++j) {
-            const float w = renorm ? top_v[j] / tot : top_v[j];
-            weights[(size_t)t * k + j] = __float2half_rn(w);
-            chosen[(size_t)t * k + j] = top_i[j];
-        }
+    if ((uint32_t)lane < k) {
+        const float w = renorm ? my_v / tot : my_v;
+        weights[(size_t)t * k + lane] = __float2half_rn(w);
+        chosen[(size_t)t * k + lane] = my_i;
+        if (stage != nullptr) stage[(size_t)t * k + lane] = (uint16_t)my_i;
+    }
+}
+
+__device__ __forceinline__ void route_token(const __half *__restrict__ logits, uint32_t t, uint32_t E, uint32_t k,
+                                            int renorm, __half *__restrict__ weights, int32_t *__restrict__ chosen,
+                                            uint16_t *stage, int lane) {
+    if (E <= 32) route_token_n<1>(logits, t, E, k, renorm, weights, chosen, stage, lane);
+    else if (E <= 128) route_token_n<4>(logits, t, E, k, renorm, weights, chosen, stage, lane);
+    else route_token_n<RT_MAX_EXPERTS / 32>(logits, t, E, k, renorm, weights, chosen, stage, lane);
 }
 
 // many tokens: the per-token part on a grid of its own (8 tokens per CTA)
@@ -95,7 +106,7 @@ moe_topk_kernel(const __half *__restrict__ logits, uint32_t T, uint32_t E, uint3
     pdl_trigger();
     pdl_wait();
     const uint32_t t = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (t < T) route_token(logits, t, E, k, renorm, weights, chosen, threadIdx.x & 31);
+    if (t < T) route_token(logits, t, E, k, renorm, weights, chosen, nullptr, threadIdx.x & 31);
 }
 
 __global__ void __launch_bounds__(RT_THREADS)
@@ -112,10 +123,11 @@ moe_route_kernel(const __half *__restrict__ logits, uint32_t T, uint32_t E, uint
     const uint32_t R = T * k;
 
     if (do_topk)
-        for (uint32_t t = warp; t < T; t += WARPS) route_token(logits, t, E, k, renorm, weights, chosen, lane);
+        for (uint32_t t = warp; t < T; t += WARPS)
+            route_token(logits, t, E, k, renorm, weights, chosen, staged ? chosen_sh : nullptr, lane);
     for (uint32_t e = tid; e < E; e += RT_THREADS) counts[e] = 0;
     __syncthreads();   // also orders the global writes of `chosen` before the reads below (one CTA)
-    if (staged) {
+    if (staged && !do_topk) {     // the ids come from the top-k kernel: stage them (with do_topk they already are)
         for (uint32_t r = tid; r < R; r += RT_THREADS) chosen_sh[r] = (uint16_t)chosen[r];
         __syncthreads();
     }
