@@ -610,7 +610,8 @@ static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_par
     float *tp = (float *)tmp;
     const uint32_t nc = (uint32_t)num_chunks;
     // the tensor-core kernel takes page sizes that are multiples of 16; the CUDA-core kernel the rest
-    const bool took = launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
+    // 0: not this kernel's geometry; 1: split-KV states left in tmp; 2: output complete
+    const int took = launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
     if (!took) switch (G) {
         case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
@@ -619,7 +620,7 @@ static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_par
     }
     rc = check_launch("batch_decode_i4");
     if (rc) return rc;
-    if (num_chunks > 1 && !(took && counters)) {   // the tensor-core kernel merges by itself when it has counters
+    if (num_chunks > 1 && took != 2) {   // the tensor-core kernel merges by itself inside a cluster, or when it has counters
         dim3 mgrid((unsigned)batch_size, (unsigned)num_qo_heads);
         launch_pdl(decode_merge_kernel, mgrid, dim3(128), 0, st, (const float *)tp, op, nc);
         rc = check_launch("batch_decode_i4 (merge)");

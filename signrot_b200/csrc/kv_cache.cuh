@@ -32,8 +32,9 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // Tensor-core decode kernel (kv_decode_tc.cu): same arguments and workspace format as decode_kernel.
-// Returns false when the geometry is not one it handles (page_size % 16 != 0).
-bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
+// Returns 0 when the geometry is not one it handles (page_size % 16 != 0), 1 when the split-KV states are left in tmp
+// for decode_merge_kernel, 2 when the output is complete (one chunk, merged in the cluster, or merged through counters).
+int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
                       int had_q, float had_scale, cudaStream_t st, int32_t *counters = nullptr);
 
 }  // namespace sr

@@ -57,7 +57,7 @@ __device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
 template <int G>
 __global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
-                 uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters) {
+                 uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters, int cluster_merge) {
     pdl_trigger();   // launched with programmatic serialization (launch_pdl); everything read here is produced upstream
     pdl_wait();
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
@@ -71,6 +71,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     __shared__ float sh_q[G][132];
     __shared__ float sh_o[DT_WARPS][G][148];
     __shared__ float sh_md[DT_WARPS][G][2];
+    __shared__ float cl_part[G][HD + 4];      // cluster merge: this chunk's state per head (o[128], m, d), read by the other CTAs
 
     // ---- q (optionally Hadamard-rotated, kv_cache.py:157-158), one warp per q head
     const float sm_scale = 1.44269504088896340736f * 0.08838834764831845f;  // log2(e) / sqrt(128)
@@ -340,6 +341,12 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         const uint32_t hq = hk * G + gg;
         if (num_chunks == 1) {
             o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+        } else if (cluster_merge) {
+            cl_part[gg][tid] = oo;
+            if (tid == 0) {
+                cl_part[gg][HD] = mm;
+                cl_part[gg][HD + 1] = dd;
+            }
         } else {
             float *dst = tmp + (((size_t)b * hq_total + hq) * num_chunks + chunk) * (HD + 4);
             dst[tid] = oo;
@@ -348,6 +355,41 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
                 dst[HD + 1] = dd;
             }
         }
+    }
+    // ---- merge across chunks inside the cluster: the CTAs of one (request, KV head) are one cluster along z, every chunk's
+    // state stays in its CTA's shared memory and head gg is finalised by the CTA of rank gg % chunks, which reads the
+    // chunks' states in chunk order through distributed shared memory: the arithmetic and the order of
+    // decode_merge_kernel, without its launch and without the round trip of the partial states through memory.
+    if (cluster_merge && num_chunks > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t mine = (uint32_t)__cvta_generic_to_shared(&cl_part[0][0]);
+        auto peer_ld = [&](uint32_t c, uint32_t idx) {
+            float v;
+            asm volatile(
+                "{\n\t.reg .b32 remaddr;\n\t"
+                "mapa.shared::cluster.u32 remaddr, %1, %2;\n\t"
+                "ld.shared::cluster.f32 %0, [remaddr];\n\t}"
+                : "=f"(v)
+                : "r"(mine + idx * 4u), "r"(c)
+                : "memory");
+            return v;
+        };
+        for (int gg = 0; gg < G; ++gg) {
+            if ((uint32_t)gg % num_chunks != chunk) continue;
+            const uint32_t hq = hk * G + gg, at = (uint32_t)gg * (HD + 4);
+            float mm = -5e4f;
+            for (uint32_t c = 0; c < num_chunks; ++c) mm = fmaxf(mm, peer_ld(c, at + HD));
+            float dd = 0.f, oo = 0.f;
+            for (uint32_t c = 0; c < num_chunks; ++c) {
+                const float sc = ex2(peer_ld(c, at + HD) - mm);
+                dd += peer_ld(c, at + HD + 1) * sc;
+                oo += peer_ld(c, at + tid) * sc;
+            }
+            o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
+        }
+        // no CTA leaves while another one may still read its state
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        return;
     }
     // ---- merge across chunks by whichever CTA of this (request, KV head) finishes last: the arithmetic and the
     // chunk order of decode_merge_kernel, without its launch.  counters[b * kv_heads + hk] starts at zero and is
@@ -384,25 +426,57 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
 
 }  // namespace
 
-bool launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
-                      int had_q, float had_scale, cudaStream_t st, int32_t *counters) {
-    if (kv.page_size % DT_BLOCK != 0) return false;
+// Returns 0 when the kernel does not take the geometry, 1 when it ran and the split-KV states still have to be merged
+// (decode_merge_kernel), 2 when nothing is left to do (one chunk, or merged inside the kernel).
+int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
+                     int had_q, float had_scale, cudaStream_t st, int32_t *counters) {
+    if (kv.page_size % DT_BLOCK != 0) return 0;
+    // up to eight chunks (the portable cluster size): the chunks of a (request, KV head) form a cluster and merge in it
+    bool cluster = counters == nullptr && num_chunks >= 2 && num_chunks <= 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DT_WARPS * 32);
+    cfg.dynamicSmemBytes = DT_RING_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = num_chunks;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
 #define SR_DT(GG)                                                                                              \
     do {                                                                                                       \
         auto kfn = decode_tc_kernel<GG>;                                                                       \
         if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
-            return false;                                                                                      \
-        launch_pdl(kfn, grid, dim3(DT_WARPS * 32), (size_t)DT_RING_BYTES, st, q, kv, o, tmp, num_chunks, had_q, had_scale, counters); \
+            return 0;                                                                                          \
+        if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, cluster ? 1 : 0) != cudaSuccess) { \
+            if (!cluster) return 0;                                                                            \
+            (void)cudaGetLastError();        /* a cluster of this size does not fit: plain launch, separate merge */ \
+            cluster = false;                                                                                   \
+            cfg.numAttrs = na - 1;                                                                             \
+            if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, 0) != cudaSuccess) \
+                return 0;                                                                                      \
+        }                                                                                                      \
     } while (0)
     switch (G) {
         case 1: SR_DT(1); break;
         case 2: SR_DT(2); break;
         case 4: SR_DT(4); break;
         case 8: SR_DT(8); break;
-        default: return false;
+        default: return 0;
     }
 #undef SR_DT
-    return true;
+    return (num_chunks == 1 || cluster || counters != nullptr) ? 2 : 1;
 }
 
 }  // namespace sr

@@ -60,7 +60,7 @@ def test_fused_append_and_decode(T, page, Hq, Hkv):
     qd = q.view(B, Hq, 128).to(DEV).contiguous()
     o1 = torch.empty_like(qd)
     kvc.batch_decode_i4(o1, qd, **specs, layer_idx=layer, hadamard_q=True)
-    for chunks in (2, 3, 7):
+    for chunks in (2, 3, 7, 12):     # up to 8: merged inside a cluster; more: the separate merge launch
         tmp = torch.empty((B, Hq, chunks, 132), dtype=torch.float32, device=DEV)
         o2 = torch.empty_like(qd)
         kvc.batch_decode_i4(o2, qd, **specs, layer_idx=layer, tmp=tmp, num_chunks=chunks, hadamard_q=True)
@@ -203,10 +203,12 @@ def test_rope_kv_append_equals_rope_then_append(T, start, fused_input):
             assert torch.equal(pa[pg, :, :, e], pb[pg, :, :, e]) and torch.equal(sa[pg, :, :, e], sb[pg, :, :, e])
 
 
-@pytest.mark.parametrize("T,page,Hq,Hkv,chunks", [(513, 128, 32, 8, 3), (1000, 16, 8, 2, 7), (300, 32, 4, 4, 2)])
+@pytest.mark.parametrize("T,page,Hq,Hkv,chunks", [(513, 128, 32, 8, 3), (1000, 16, 8, 2, 7), (300, 32, 4, 4, 2),
+                                                  (1000, 16, 8, 2, 12), (2100, 256, 32, 8, 5)])
 def test_in_kernel_merge_equals_merge_pass(T, page, Hq, Hkv, chunks):
-    """Split-KV merge by the last CTA of each (request, KV head) against the separate merge launch:
-    same bits, and the arrival counters are back at zero after every call."""
+    """Three ways to merge the split-KV states give the same bits: inside the cluster that the chunks of a
+    (request, KV head) form (the default up to 8 chunks), the separate merge launch (more chunks), and the last CTA
+    behind arrival counters, which are back at zero after every call."""
     B, L = 3, 1
     k, v, ref, pages = _fill(B, L, Hkv, page, T, T + 1)
     cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, L, Hkv, 128, group_size=Hq // Hkv)
