@@ -335,8 +335,11 @@ static int launch_skinny(const uint8_t *A, const uint8_t *B, int64_t M, int64_t 
     // warps per row block: see skinny_kw()
     const int kw = skinny_kw(blocks, K, sm_count, grouped);
     const int groups = SK_WARPS / kw;
-    // two CTAs per SM; the row blocks are dealt round-robin to the warp groups, so shrink the grid to even the deal out
-    int64_t ctas = 2 * (int64_t)sm_count;
+    // two CTAs per SM, three when shared memory allows (one token block, one m-tile: 73 KB per CTA): a few more slots
+    // turn "two blocks one after the other" into "one block each" for the 300 .. 440 block shapes (a fused q/k/v).
+    // The row blocks are dealt round-robin to the warp groups, so shrink the grid to even the deal out.
+    const int per_sm = !grouped && skinny_smem(nt, mt) * 3 + 3 * 1024 <= 227 * 1024 ? 3 : 2;
+    int64_t ctas = per_sm * (int64_t)sm_count;
     if (blocks < ctas * groups) ctas = cdiv<int64_t>(blocks, groups);
     // (grouped launches keep every CTA slot: measured 6 % faster on the MoE decode stack than the even deal)
     else if (!grouped) ctas = cdiv<int64_t>(blocks, cdiv<int64_t>(blocks, ctas * groups) * groups);
