@@ -306,6 +306,20 @@ int sr_rope_kv_append(void *kv_data, void *kv_param, const void *kv_indptr, cons
                       void *q_out, void *k_out, int64_t batch_size, int64_t new_tokens, int64_t num_layers,
                       int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size,
                       int64_t head_dim, int hadamard_k, void *stream);
+/* Decode step of one layer's attention in ONE launch: sr_rope_kv_append for one new token per request followed by
+ * sr_batch_decode_i4, with the bits of the two separate calls.  q, k, v: the projections BEFORE the rotary embedding
+ * (fp16, base + request * stride + head * 128, strides in elements: column ranges of one fused q/k/v output are
+ * fine); cos, sin fp16 [cos_seqs (1 or batch), 1, 128].  The page tables already describe the sequence INCLUDING the
+ * new token.  Every CTA rotates the q heads it needs; the CTA that owns the last page of a (request, KV head) rotates,
+ * quantizes and stores the new K and V before it reads that page.  Needs a page size that is a multiple of 16
+ * (SR_ERR_UNSUPPORTED otherwise).  o, tmp, num_chunks, hadamard_q as for sr_batch_decode_i4; hadamard_k as for
+ * sr_rope_kv_append.  No counterpart in the reference, which runs rope_qk, kv_quant_pack, append_kv_i4 and
+ * batch_decode_i4 one after the other (fake_quant/kernel_utils.py:118-158). */
+int sr_rope_decode_i4(void *o, const void *q, const void *k, const void *v, int64_t q_stride, int64_t k_stride,
+                      int64_t v_stride, const void *cos, const void *sin, int64_t cos_seqs, void *kv_data, void *kv_param,
+                      const void *kv_indptr, const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                      int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                      int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, int hadamard_k, void *stream);
 /* o, q fp16 [batch, num_qo_heads, 128]; one new token per request attends to its cached
  * sequence.  num_qo_heads is a multiple (1, 2, 4, 8) of num_kv_heads: q head h reads KV head
  * h / (num_qo_heads / num_kv_heads).  tmp fp32 [batch, num_qo_heads, num_chunks, 132] is the

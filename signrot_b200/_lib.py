@@ -64,6 +64,7 @@ _SIGNATURES = {
     "sr_kv_append_quant": [_P] * 7 + [_I64] * 7 + [_I, _P],
     "sr_rope_kv_append": [_P] * 8 + [_I64] * 3 + [_P, _P, _I64, _P, _P] + [_I64] * 8 + [_I, _P],
     "sr_batch_decode_i4": [_P] * 7 + [_I64] * 7 + [_P, _I64, _I, _P],
+    "sr_rope_decode_i4": [_P] * 4 + [_I64] * 3 + [_P, _P, _I64] + [_P] * 5 + [_I64] * 7 + [_P, _I64, _I, _I, _P],
     "sr_batch_decode_i4_merged": [_P] * 7 + [_I64] * 7 + [_P, _I64, _P, _I, _P],
     "sr_peer_region_bytes": [_I64, _I64, ctypes.POINTER(ctypes.c_int64)],
     "sr_peer_alloc": [_I64, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p],

@@ -65,15 +65,6 @@ kv_scatter_kernel(PagedKV kv, const uint8_t *__restrict__ k, const uint8_t *__re
 
 // ------------------------------------------------------------------ fused Hadamard + quantise + append
 
-__device__ __forceinline__ void kv_params_dev(float vmin, float vmax, __half &scale, __half &zero) {
-    // signrot/kernels/fused.cu:236-247
-    const __half hmin = __float2half(vmin), hmax = __float2half(vmax);
-    __half diff = __float2half(__half2float(hmax) - __half2float(hmin));
-    diff = __float2half(fmaxf(__half2float(diff), 1e-5f));
-    scale = __float2half(__half2float(diff) / 15.f);
-    zero = __hneg(hmin);
-}
-
 // A warp takes KV_VPW consecutive (token, head, k|v) vectors of 128 at a time (lane holds 4 consecutive values
 // of each; the loads and the shuffle butterflies of the KV_VPW vectors are independent, which is what hides
 // their latency).  k, v: [B, T, heads, 128] fp16.  K goes through H_128 / sqrt(128) (fp32 butterflies,
@@ -195,66 +186,13 @@ rope_kv_append_kernel(PagedKV kv, const __half *__restrict__ q, const __half *__
         __half h[4];
         *reinterpret_cast<uint2 *>(h) = raw;
         if (type < 2) {
-            const uint32_t p0 = __shfl_xor_sync(0xffffffffu, raw.x, 16), p1 = __shfl_xor_sync(0xffffffffu, raw.y, 16);
-            __half pb[4];
-            *reinterpret_cast<uint2 *>(pb) = make_uint2(p0, p1);
-            const size_t ct = (cos_seqs == 1 ? token % T : token) * HD + lane * 4;
-            __half c[4], sn[4];
-            *reinterpret_cast<uint2 *>(c) = __ldg(reinterpret_cast<const uint2 *>(cosv + ct));
-            *reinterpret_cast<uint2 *>(sn) = __ldg(reinterpret_cast<const uint2 *>(sinv + ct));
-            const bool first_half = lane < 16;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __half p = __float2half(__half2float(h[j]) * __half2float(c[j]));
-                const float bf = first_half ? -__half2float(pb[j]) : __half2float(pb[j]);
-                const __half r = __float2half(bf * __half2float(sn[j]));
-                h[j] = __float2half(__half2float(p) + __half2float(r));
-            }
+            rope_vec(h, raw, cosv, sinv, (size_t)(cos_seqs == 1 ? token % T : token) * HD + lane * 4, lane);
             __half *dst = type == 0 ? q_out + ((size_t)token * hq + head) * HD : (k_out ? k_out + ((size_t)token * kv.heads + head) * HD : nullptr);
             if (dst) *reinterpret_cast<uint2 *>(dst + lane * 4) = *reinterpret_cast<const uint2 *>(h);
             if (type == 0) continue;
         }
-        float a[4] = {__half2float(h[0]), __half2float(h[1]), __half2float(h[2]), __half2float(h[3])};
-        if (type == 1 && had_k) {
-            const float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
-            a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
-#pragma unroll
-            for (int m = 1; m < 32; m <<= 1) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float o = __shfl_xor_sync(0xffffffffu, a[j], m);
-                    a[j] = (lane & m) ? (o - a[j]) : (a[j] + o);
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) a[j] = __half2float(__float2half_rn(a[j] * had_scale));
-        }
-        float vmax = fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
-        float vmin = fminf(fminf(a[0], a[1]), fminf(a[2], a[3]));
-        vmax = warp_max(vmax);
-        vmin = warp_min(vmin);
-        __half scale, zero;
-        kv_params_dev(vmin, vmax, scale, zero);
-        const float fs = __half2float(scale), fz = __half2float(zero);
-        uint32_t code = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const __half shifted = __float2half(a[j] + fz);
-            const __half scaled = __float2half(__half2float(shifted) / fs);
-            code |= (uint32_t)clampi((int)nearbyintf(__half2float(scaled)), 0, 15) << (4 * j);
-        }
         const uint32_t t = token % T, b = token / T;
-        const uint32_t pos = kv.seq_len(b) - T + t;
-        const uint32_t page = (uint32_t)kv.indices[kv.indptr[b] + pos / kv.page_size];
-        const uint32_t entry = pos % kv.page_size;
-        const size_t vi = kv.vec_index(page, (uint32_t)(type - 1), head, entry);
-        reinterpret_cast<uint16_t *>(kv.data + vi * 64)[lane] = (uint16_t)code;
-        if (lane == 0) {
-            __half2 pr;
-            pr.x = scale;
-            pr.y = zero;
-            kv.param[vi] = pr;
-        }
+        kv_quant_store(kv, h, (uint32_t)(type - 1), type == 1 && had_k, had_scale, b, head, kv.seq_len(b) - T + t, lane);
     }
 }
 
@@ -587,7 +525,7 @@ static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_par
                              const void *kv_indices, const void *last_page_offset, int64_t num_layers, int64_t layer_idx,
                              int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
                              int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, void *stream,
-                             int32_t *counters) {
+                             int32_t *counters, const RopeIn *rope = nullptr) {
     SR_REQUIRE(head_dim == 128, SR_ERR_INVALID, "batch_decode_i4: CHECK_EQ(head_dim, 128) failed. %lld vs 128", (long long)head_dim);
     if (batch_size == 0) return SR_OK;
     PagedKV kv;
@@ -611,7 +549,9 @@ static int batch_decode_impl(void *o, const void *q, void *kv_data, void *kv_par
     const uint32_t nc = (uint32_t)num_chunks;
     // the tensor-core kernel takes page sizes that are multiples of 16; the CUDA-core kernel the rest
     // 0: not this kernel's geometry; 1: split-KV states left in tmp; 2: output complete
-    const int took = launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters);
+    const int took = launch_decode_tc((int)G, grid, qp, kv, op, tp, nc, hadamard_q, had_scale, st, counters, rope);
+    SR_REQUIRE(took != 0 || rope == nullptr, SR_ERR_UNSUPPORTED,
+               "rope_decode_i4: the page size must be a multiple of 16 (use rope_kv_append and batch_decode_i4)");
     if (!took) switch (G) {
         case 1: decode_kernel<1><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
         case 2: decode_kernel<2><<<grid, 128, 0, st>>>(qp, kv, op, tp, nc, hadamard_q, had_scale); break;
@@ -647,6 +587,34 @@ int sr_batch_decode_i4_merged(void *o, const void *q, void *kv_data, void *kv_pa
     return batch_decode_impl(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
                              num_qo_heads, num_kv_heads, page_size, head_dim, batch_size, tmp, num_chunks, hadamard_q,
                              stream, (int32_t *)counters);
+}
+
+int sr_rope_decode_i4(void *o, const void *q, const void *k, const void *v, int64_t q_stride, int64_t k_stride,
+                      int64_t v_stride, const void *cos, const void *sin, int64_t cos_seqs, void *kv_data, void *kv_param,
+                      const void *kv_indptr, const void *kv_indices, const void *last_page_offset, int64_t num_layers,
+                      int64_t layer_idx, int64_t num_qo_heads, int64_t num_kv_heads, int64_t page_size, int64_t head_dim,
+                      int64_t batch_size, void *tmp, int64_t num_chunks, int hadamard_q, int hadamard_k, void *stream) {
+    SR_REQUIRE(q && k && v && cos && sin, SR_ERR_INVALID, "rope_decode_i4: null pointer");
+    SR_REQUIRE(cos_seqs == 1 || cos_seqs == batch_size, SR_ERR_INVALID, "rope_decode_i4: cos/sin for 1 or batch sequences");
+    SR_REQUIRE(q_stride >= num_qo_heads * 128 && k_stride >= num_kv_heads * 128 && v_stride >= num_kv_heads * 128 &&
+                   q_stride % 4 == 0 && k_stride % 4 == 0 && v_stride % 4 == 0,
+               SR_ERR_INVALID, "rope_decode_i4: bad request stride");
+    SR_REQUIRE(((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)cos | (uintptr_t)sin) % 8 == 0, SR_ERR_INVALID,
+               "rope_decode_i4: q, k, v, cos and sin must be 8-byte aligned");
+    RopeIn rope;
+    rope.q = (const __half *)q;
+    rope.k = (const __half *)k;
+    rope.v = (const __half *)v;
+    rope.q_stride = q_stride;
+    rope.k_stride = k_stride;
+    rope.v_stride = v_stride;
+    rope.cosv = (const __half *)cos;
+    rope.sinv = (const __half *)sin;
+    rope.cos_seqs = (uint32_t)cos_seqs;
+    rope.had_k = hadamard_k;
+    return batch_decode_impl(o, q, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, num_layers, layer_idx,
+                             num_qo_heads, num_kv_heads, page_size, head_dim, batch_size, tmp, num_chunks, hadamard_q,
+                             stream, nullptr, &rope);
 }
 
 // ------------------------------------------------------------------ decode-step bookkeeping on the device

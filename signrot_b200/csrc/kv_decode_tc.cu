@@ -57,7 +57,8 @@ __device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
 template <int G>
 __global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
-                 uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters, int cluster_merge) {
+                 uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters, int cluster_merge,
+                 RopeIn rope) {
     pdl_trigger();   // launched with programmatic serialization (launch_pdl); everything read here is produced upstream
     pdl_wait();
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
@@ -73,14 +74,20 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     __shared__ float sh_md[DT_WARPS][G][2];
     __shared__ float cl_part[G][HD + 4];      // cluster merge: this chunk's state per head (o[128], m, d), read by the other CTAs
 
+    const bool fused = rope.k != nullptr;     // this launch also applies the rotary embedding and appends the new K / V
     // ---- q (optionally Hadamard-rotated, kv_cache.py:157-158), one warp per q head
     const float sm_scale = 1.44269504088896340736f * 0.08838834764831845f;  // log2(e) / sqrt(128)
     for (int gg = warp; gg < G; gg += DT_WARPS) {
         const uint32_t hq = hk * G + gg;
-        const __half *qp = q + ((size_t)b * hq_total + hq) * HD + lane * 4;
+        // fused form: the projection's own q (possibly a column range), rotary embedding here, rounded to fp16 as the
+        // separate launch would store it
+        const __half *qp = fused ? rope.q + (size_t)b * rope.q_stride + (size_t)hq * HD + lane * 4
+                                 : q + ((size_t)b * hq_total + hq) * HD + lane * 4;
         const uint2 raw = *reinterpret_cast<const uint2 *>(qp);
-        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
-        float a[4] = {__half2float(h01.x), __half2float(h01.y), __half2float(h23.x), __half2float(h23.y)};
+        __half hq4[4];
+        *reinterpret_cast<uint2 *>(hq4) = raw;
+        if (fused) rope_vec(hq4, raw, rope.cosv, rope.sinv, (size_t)(rope.cos_seqs == 1 ? 0 : b) * HD + lane * 4, lane);
+        float a[4] = {__half2float(hq4[0]), __half2float(hq4[1]), __half2float(hq4[2]), __half2float(hq4[3])};
         if (had_q) {
             float t0 = a[0] + a[1], t1 = a[0] - a[1], t2 = a[2] + a[3], t3 = a[2] - a[3];
             a[0] = t0 + t2; a[1] = t1 + t3; a[2] = t0 - t2; a[3] = t1 - t3;
@@ -128,6 +135,21 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     const uint32_t last_valid = (uint32_t)kv.last_page_offset[b];
     const uint32_t blocks_per_page = kv.page_size / DT_BLOCK;
     const uint32_t num_blocks = (cp_end - cp_begin) * blocks_per_page;
+    if (fused) {
+        // The new token's K and V go into their slot (the last one of the request) before anybody reads it: only the
+        // chunk that owns the last page does, and it is this CTA that writes it.  Warp 0: K (rotary embedding, head_dim
+        // rotation, quantizer), warp 1: V (quantizer): the arithmetic of rope_kv_append_kernel.
+        const bool owner = pages_total > 0 && cp_begin <= pages_total - 1 && pages_total - 1 < cp_end;
+        if (owner && warp < 2) {
+            const __half *src = warp == 0 ? rope.k + (size_t)b * rope.k_stride : rope.v + (size_t)b * rope.v_stride;
+            const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)hk * HD + lane * 4));
+            __half h[4];
+            *reinterpret_cast<uint2 *>(h) = raw;
+            if (warp == 0) rope_vec(h, raw, rope.cosv, rope.sinv, (size_t)(rope.cos_seqs == 1 ? 0 : b) * HD + lane * 4, lane);
+            kv_quant_store(kv, h, (uint32_t)warp, warp == 0 && rope.had_k, had_scale, b, hk, kv.seq_len(b) - 1, lane);
+        }
+        __syncthreads();      // the stores above are visible to this CTA's copies below
+    }
 
     float m_run = -5e4f, d_run = 0.f, z_run = 0.f;   // head g: running max (quad-uniform), this lane's part of sum p and sum p vz
     // O^T accumulators: m-tile j = byte j of the lane's eight V bytes; slot 0,1: dim 16 g + 2 j, heads 2 qd, 2 qd + 1;
@@ -429,8 +451,10 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
 // Returns 0 when the kernel does not take the geometry, 1 when it ran and the split-KV states still have to be merged
 // (decode_merge_kernel), 2 when nothing is left to do (one chunk, or merged inside the kernel).
 int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __half *o, float *tmp, uint32_t num_chunks,
-                     int had_q, float had_scale, cudaStream_t st, int32_t *counters) {
+                     int had_q, float had_scale, cudaStream_t st, int32_t *counters, const RopeIn *rope_in) {
     if (kv.page_size % DT_BLOCK != 0) return 0;
+    RopeIn rope = {};
+    if (rope_in != nullptr) rope = *rope_in;
     // up to eight chunks (the portable cluster size): the chunks of a (request, KV head) form a cluster and merge in it
     bool cluster = counters == nullptr && num_chunks >= 2 && num_chunks <= 8;
     cudaLaunchConfig_t cfg = {};
@@ -459,12 +483,12 @@ int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __hal
         auto kfn = decode_tc_kernel<GG>;                                                                       \
         if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
             return 0;                                                                                          \
-        if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, cluster ? 1 : 0) != cudaSuccess) { \
+        if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, cluster ? 1 : 0, rope) != cudaSuccess) { \
             if (!cluster) return 0;                                                                            \
             (void)cudaGetLastError();        /* a cluster of this size does not fit: plain launch, separate merge */ \
             cluster = false;                                                                                   \
             cfg.numAttrs = na - 1;                                                                             \
-            if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, 0) != cudaSuccess) \
+            if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, 0, rope) != cudaSuccess) \
                 return 0;                                                                                      \
         }                                                                                                      \
     } while (0)

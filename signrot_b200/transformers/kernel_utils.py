@@ -176,8 +176,9 @@ def kernel_attention_forward(self, hidden_states, position_embeddings, attention
 
     if past_key_values is not None and attention_mask is None and hasattr(past_key_values, "update_with_rope") \
             and getattr(self, "fuse_rope_append", True):
+        # the callable this returns is called right below: a decode step may leave rotation and append to it
         query_states, cache_out = past_key_values.update_with_rope(query_states, key_states, value_states, cos, sin,
-                                                                   self.layer_idx)
+                                                                   self.layer_idx, defer_append=True)
     else:
         query_states, key_states = query_states.contiguous(), key_states.contiguous()
         kernel.rope_qk(query_states, key_states, cos, sin)     # in place

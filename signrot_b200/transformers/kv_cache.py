@@ -207,6 +207,35 @@ def rope_kv_append(kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, q
     return q_out, k_out
 
 
+def rope_decode_i4(o, q, k, v, cos, sin, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, layer_idx, tmp=None,
+                   num_chunks=1, hadamard_q=False, hadamard_k=True):
+    """`rope_kv_append` for one new token per request and `batch_decode_i4` in one launch, with the bits of the
+    two calls.  q [B, 1, Hq, D], k / v [B, 1, H, D] fp16 before the rotary embedding (column ranges of a fused
+    projection are fine); cos / sin fp16 [1 or B, 1, D]; o fp16 [B, Hq, D].  The page tables already count the new
+    token.  Needs page_size % 16 == 0."""
+    dev = require_cuda("rope_decode_i4", o, kv_data, kv_param, kv_indptr, kv_indices, last_page_offset, q, k, v, cos, sin,
+                       tmp, strided=(q, k, v))
+    L, H, P, D = _geometry(kv_data)
+    B, hq = q.size(0), q.size(2)
+    if q.size(1) != 1 or k.shape[:2] != (B, 1) or v.shape[:2] != (B, 1):
+        raise RuntimeError("rope_decode_i4: one new token per request")
+    qs, ks, vs = _token_stride("q", q, hq, D), _token_stride("k", k, H, D), _token_stride("v", v, H, D)
+    cos, sin = cos.contiguous(), sin.contiguous()
+    if cos.dtype != torch.float16 or cos.shape != sin.shape or cos.dim() != 3 or cos.size(1) != 1 or cos.size(2) != D \
+            or cos.size(0) not in (1, B):
+        raise RuntimeError("rope_decode_i4 expects fp16 cos/sin of shape [1 or B, 1, head_dim]")
+    if o.shape != (B, hq, D) or o.dtype != torch.float16 or not o.is_contiguous():
+        raise RuntimeError("rope_decode_i4: o must be a contiguous fp16 [B, q_heads, head_dim] tensor")
+    if tmp is not None and num_chunks > 1:
+        if tmp.dtype != torch.float32 or tmp.numel() != B * hq * num_chunks * (D + 4):
+            raise RuntimeError("tmp must be fp32 [batch, heads, chunks, head_dim + 4]")
+    else:
+        tmp, num_chunks = None, 1
+    run(dev, "sr_rope_decode_i4", ptr(o), ptr(q), ptr(k), ptr(v), qs, ks, vs, ptr(cos), ptr(sin), cos.size(0),
+        ptr(kv_data), ptr(kv_param), ptr(kv_indptr), ptr(kv_indices), ptr(last_page_offset), L, int(layer_idx), hq, H, P, D,
+        B, ptr(tmp), int(num_chunks), int(bool(hadamard_q)), int(bool(hadamard_k)))
+
+
 # ----------------------------------------------------------------------------- cache object
 
 class _AttentionStub:
@@ -231,6 +260,16 @@ class _AttentionStub:
                         hadamard_q=self.hadamard_dtype is not None, counters=self.counters)
         return out.unsqueeze(1)
 
+    def forward_rope(self, q, k, v, cos, sin, attention_kwargs, layer_idx, hadamard_k):
+        """The decode step's attention from the projections before the rotary embedding: rotary embedding, K/V
+        append and attention in one launch (`rope_decode_i4`)."""
+        bsz, q_len, hq, hd = q.shape
+        assert q_len == 1
+        out = torch.empty((bsz, hq, hd), dtype=torch.float16, device=q.device)
+        rope_decode_i4(out, q, k, v, cos, sin, **attention_kwargs, layer_idx=layer_idx, tmp=self.tmp,
+                       num_chunks=self.num_chunks, hadamard_q=self.hadamard_dtype is not None, hadamard_k=hadamard_k)
+        return out.unsqueeze(1)
+
 
 def decode_split(batch_size, kv_heads, max_pages, device):
     """Chunks per (request, KV head) of the split-KV decode: about two CTAs per SM, at most one per page."""
@@ -244,6 +283,7 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
     def __init__(self, batch_size, page_size, max_seq_len, device, n_layers, num_heads, head_dim,
                  disable_quant=False, hadamard_dtype=torch.float16, group_size=1, lac=False, decode_chunks=None):
         self.decode_chunks = decode_chunks
+        self.fuse_decode = True      # decode steps: rotary embedding + K/V append + attention in one launch (same bits as two)
         if disable_quant:
             raise NotImplementedError("the unquantized fp16 cache (a baseline knob of the reference) is not built")
         if lac:
@@ -358,14 +398,25 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
             assert added == 1
         return specs, first
 
-    def update_with_rope(self, query_states, key_states, value_states, cos, sin, layer_idx: int):
+    def update_with_rope(self, query_states, key_states, value_states, cos, sin, layer_idx: int, defer_append=False):
         """`rope_qk` + `update` in one launch (kernel_utils.py:118-141 of the reference's glue calls
         them back to back).  q/k/v are the projections BEFORE the rotary embedding, fp16
         [B, T, H, 128], possibly column ranges of one fused projection.  Returns
         (rotated q, what `update` returns: (rotated k, v) on the first call of a layer, the
-        attention callable afterwards)."""
+        attention callable afterwards).
+
+        `defer_append`: the caller promises to call the returned attention callable, with the returned q, before
+        anything else touches the cache.  A decode step then runs as ONE launch (`rope_decode_i4`): the callable
+        rotates q, appends the new K / V and attends; the q handed back is the unrotated one."""
         bsz, added, heads, hd = key_states.shape
         specs, first = self._advance(bsz, added, layer_idx)
+        if (defer_append and not first and added == 1 and self.page_size % 16 == 0 and self._stub.counters is None
+                and query_states.dtype == torch.float16 and self.fuse_decode):
+            # decode: the attention kernel rotates q, appends the new K / V and attends in one launch; the caller hands
+            # the returned q (unrotated) to the returned callable
+            return query_states, functools.partial(self._stub.forward_rope, k=key_states, v=value_states, cos=cos, sin=sin,
+                                                   attention_kwargs=specs, layer_idx=layer_idx,
+                                                   hadamard_k=self.hadamard_dtype is not None)
         q_rot, k_rot = rope_kv_append(**specs, q=query_states, k=key_states, v=value_states, cos=cos, sin=sin,
                                       layer_idx=layer_idx, hadamard_k=self.hadamard_dtype is not None, want_k=first)
         if first:

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import oracle
+from signrot_b200 import _lib
 from signrot_b200.functional import kernel
 from signrot_b200.transformers import kv_cache as kvc
 
@@ -224,3 +225,41 @@ def test_in_kernel_merge_equals_merge_pass(T, page, Hq, Hkv, chunks):
         kvc.batch_decode_i4(b, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks, hadamard_q=True, counters=counters)
         assert torch.equal(a, b)
         assert int(counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("T,page,Hq,Hkv,chunks,per_request_cos", [(2100, 256, 32, 8, None, False), (513, 128, 32, 8, 3, True),
+                                                                  (1000, 16, 8, 2, 12, False), (300, 32, 4, 4, 1, True),
+                                                                  (255, 256, 16, 2, None, False), (256, 256, 8, 8, 2, True)])
+def test_decode_step_in_one_launch_equals_two(T, page, Hq, Hkv, chunks, per_request_cos):
+    """Rotary embedding + K/V append + attention as one launch (`rope_decode_i4`) against `rope_kv_append` followed
+    by `batch_decode_i4`: same attention output, same cache bytes, for three decode steps in a row (the second and
+    third read what the first appended; T = 255 / 256 put the new token at the end of a page / on a new page), with
+    q / k / v as column ranges of one fused projection output."""
+    B, L = 3, 2
+    k, v, ref, pages = _fill(B, L, Hkv, page, T, T + 4)
+    caches = []
+    for fuse in (False, True):
+        c = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, L, Hkv, 128, group_size=Hq // Hkv, decode_chunks=chunks)
+        c.fuse_decode = fuse
+        c.pages.zero_()          # the pools come from torch.empty: make the never-written slots comparable
+        c.scales.zero_()
+        for layer in range(L):
+            c.update(k.to(DEV), v.to(DEV), layer)
+        caches.append(c)
+    g = torch.Generator().manual_seed(17)
+    for step in range(3):
+        qkv = torch.randn((B, 1, (Hq + 2 * Hkv) * 128), generator=g).half().to(DEV)
+        q = qkv[..., :Hq * 128].unflatten(-1, (Hq, 128))
+        kk = qkv[..., Hq * 128:(Hq + Hkv) * 128].unflatten(-1, (Hkv, 128))
+        vv = qkv[..., (Hq + Hkv) * 128:].unflatten(-1, (Hkv, 128))
+        ang = torch.rand((B if per_request_cos else 1, 1, 128), generator=g) * 6.28
+        cos, sin = ang.cos().half().to(DEV), ang.sin().half().to(DEV)
+        outs = []
+        for c in caches:
+            for layer in range(L):
+                q_in, attend = c.update_with_rope(q, kk, vv, cos, sin, layer, defer_append=True)
+                out = attend(q_in)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), f"step {step}"
+        assert torch.equal(caches[0].pages, caches[1].pages) and torch.equal(caches[0].scales, caches[1].scales)
+    assert _lib.device_status() == 0
