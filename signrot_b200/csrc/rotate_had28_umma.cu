@@ -27,6 +27,13 @@
 //             to even, clamp) and stores its 32 codes as 16 consecutive bytes.
 // Roles of the one CTA per SM: warp 0 TMA producer, warp 1 stage-A MMAs, warp 2 stage-C MMAs, warps 4-11 stage B,
 // warps 12-27 stage D.  Every mbarrier wait is bounded (status word, normal return).
+//
+// Rows are NOT independent in one respect: a 128-line tile of stage A holds lines of two rows (a row is 3.5 tiles),
+// and the zeros of the block-diagonal constant operand multiply the other row's lines, so a NaN or an infinity in
+// one row turns the rows that share a tile with it into NaN (0 x inf).  Finite inputs never see this.  A caller whose
+// buffer holds rows of arbitrary bits that it will not use (an expert-parallel MoE block: the rows of other ranks'
+// experts are never written) must not come here; such calls carry per-row sign tables (expert ids) and are left to
+// the mma.sync kernel, which keeps rows apart.
 #include "umma.cuh"
 #include <type_traits>
 
@@ -68,9 +75,8 @@ constexpr uint32_t SW128 = 2, SW64 = 4;
 template <bool BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __half *__restrict__ hadk,
-                               const int8_t *__restrict__ sign, const int32_t *__restrict__ expert_ids, uint32_t rows,
-                               float scale, float clip, uint8_t *__restrict__ q, __half *__restrict__ q_scale,
-                               __half *__restrict__ rotated) {
+                               const int8_t *__restrict__ sign, uint32_t rows, float scale, float clip,
+                               uint8_t *__restrict__ q, __half *__restrict__ q_scale, __half *__restrict__ rotated) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -305,25 +311,22 @@ rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const 
             uint32_t sgn[16];
 #pragma unroll
             for (int p = 0; p < 16; ++p) sgn[p] = 0;
-            // sign masks of this thread's 32 values from table row `tr` (one table row, or one per expert)
-            auto load_sign = [&](uint32_t tr) {
-                const uint4 *sp4 = reinterpret_cast<const uint4 *>(sign + (size_t)tr * N + lane * 512 + j0);
-                const uint4 s0 = __ldg(sp4), s1 = __ldg(sp4 + 1);
+            if (real && sign != nullptr) {
+                const uint4 *sp4 = reinterpret_cast<const uint4 *>(sign + lane * 512 + j0);
+                const uint4 s0 = sp4[0], s1 = sp4[1];
                 const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
                 for (int p = 0; p < 16; ++p) {
                     const uint32_t two = sw[p >> 1] >> (16 * (p & 1));          // bytes of elements 2 p and 2 p + 1
                     sgn[p] = ((two & 0x80u) ? 0x00008000u : 0u) | ((two & 0x8000u) ? 0x80000000u : 0u);
                 }
-            };
-            if (real && sign != nullptr && expert_ids == nullptr) load_sign(0);
-            pdl_wait();          // q / q_scale may still be read by the kernel before this one; expert ids come from it
+            }
+            pdl_wait();          // q / q_scale may still be read by the kernel before this one
             for (uint32_t r = 0; r < cnt; ++r) {
                 const int z = (int)(r & 1);
                 const uint32_t n = 4 * r + (uint32_t)chunk;        // this warp's chunk number in the CTA's stream
                 const int b = (int)(n & 1);
                 const uint32_t row = row_begin + r;
-                if (real && sign != nullptr && expert_ids != nullptr) load_sign((uint32_t)__ldg(expert_ids + row));   // row r uses its expert's table row
                 if (!__all_sync(0xffffffffu, mbar_wait(d2_full(chunk), r & 1, ab, 78))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 float d[32];
@@ -422,7 +425,7 @@ rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const 
 int launch_rotate_had28_umma(const RotateArgs &a, cudaStream_t st) {
     using namespace h28u;
     const bool ok = a.n == (uint32_t)N && a.K == (uint32_t)KH && a.stride == 1 && a.q != nullptr && !a.fp32_mode && !a.asym &&
-                    a.hadk != nullptr &&
+                    a.expert_ids == nullptr && a.hadk != nullptr &&
                     (a.in_dtype == SR_F16 || (a.in_dtype == SR_BF16 && a.cast_in_to_f16)) && aligned16(a.x) && aligned16(a.q) &&
                     (a.sign == nullptr || aligned16(a.sign)) && (a.out == nullptr || (a.out_dtype == SR_F16 && aligned16(a.out))) &&
                     a.rows < (1u << 22);
@@ -445,8 +448,7 @@ int launch_rotate_had28_umma(const RotateArgs &a, cudaStream_t st) {
         auto kfn = rotate_quant_had28_umma_kernel<BF>;                                                           \
         cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES); \
         if (e != cudaSuccess) return fail(SR_ERR_CUDA, "rotate_quant: %s", cudaGetErrorString(e));               \
-        launch_pdl(kfn, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, st, map, (const __half *)a.hadk, a.sign,        \
-                   a.sign != nullptr ? a.expert_ids : (const int32_t *)nullptr, a.rows,                              \
+        launch_pdl(kfn, dim3(grid), dim3(THREADS), (size_t)SMEM_BYTES, st, map, (const __half *)a.hadk, a.sign, a.rows, \
                    a.scale, a.clip, a.q, a.q_scale, (__half *)a.out);                                            \
     } while (0)
     if (a.in_dtype == SR_BF16) SR_RH(true);

@@ -181,6 +181,34 @@ def test_rotate_quant_expert_signs(n, rows, sorted_rows):
     _ulp_close(rot.cpu(), want)
 
 
+@pytest.mark.parametrize("n,with_ids", [(14336, True), (4096, True), (4096, False)])
+def test_rows_of_arbitrary_bits_do_not_touch_their_neighbours(n, with_ids):
+    """An expert-parallel MoE block hands the rotation a buffer in which the rows of other ranks' experts were never
+    written: whatever they hold (NaN, infinities), the rows in between must come out as if those rows were zeros.
+    (Calls with per-row sign tables are the ones that can see such buffers; for n = 4096 the same holds without.)"""
+    g = torch.Generator().manual_seed(31)
+    rows, E = 96, 4
+    x = _x(rows, n, 13)
+    bad = torch.zeros(rows, dtype=torch.bool)
+    bad[5:9] = True
+    bad[40] = True
+    bad[70:96:3] = True
+    clean = x.clone()
+    clean[bad] = 0
+    dirty = x.clone()
+    dirty[bad] = float("nan")
+    dirty[6, ::2] = float("inf")
+    sign = (torch.randint(0, 2, (E, n), generator=g) * 2 - 1).to(torch.int8)
+    eid = torch.sort(torch.randint(0, E, (rows,), generator=g)).values.to(torch.int32)
+    hadK, K = get_hadK(n)
+    kw = dict(sign=sign.to(DEV), expert_ids=eid.to(DEV)) if with_ids else dict(sign=sign[0].to(DEV))
+    a = kernel.rotate_quant(clean.to(DEV), hadK, K, **kw)
+    b = kernel.rotate_quant(dirty.to(DEV), hadK, K, **kw)
+    good = ~bad
+    assert torch.equal(a.quantized_x.cpu()[good], b.quantized_x.cpu()[good])
+    assert torch.equal(a.scales_x.cpu()[good], b.scales_x.cpu()[good])
+
+
 def test_rotation_is_orthogonal_at_full_size():
     """Size-independent property at the benchmark size: ||H x|| = ||x|| and H(H x) = x
     (had28 is symmetric, so the Kronecker transform is an involution as well)."""
