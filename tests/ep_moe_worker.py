@@ -39,17 +39,26 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     from signrot_b200.comm import PeerGroup
     peer = PeerGroup()
-    for (E, hidden, inter, tokens, asym) in [(8, 512, 768, 64, False), (8, 512, 768, 700, False), (4, 256, 1536, 33, True)]:
+    def poison():
+        # The rows of other ranks' experts are never written by an expert-parallel block; whatever the allocator hands
+        # out for them must not matter.  Leave NaNs in the pool so that the next torch.empty is likely to hold them.
+        t = torch.full((48 << 20,), float("nan"), dtype=torch.float16, device=dev)
+        del t
+
+    for (E, hidden, inter, tokens, asym) in [(8, 512, 768, 64, False), (8, 512, 768, 700, False), (4, 256, 1536, 33, True),
+                                             (4, 256, 14336, 40, False)]:
         full = block(E, hidden, inter, 2, 11, dev, asym)
         ep = block(E, hidden, inter, 2, 11, dev, asym).shard_experts_()
         ep_peer = block(E, hidden, inter, 2, 11, dev, asym).shard_experts_(peer=peer)   # sum through peer memory
         assert ep.w_gate.shape[0] == E // world
         x = torch.randn((1, tokens, hidden), generator=torch.Generator().manual_seed(tokens)).half().to(dev)
         want, logits_a = full(x)
+        poison()
         got, logits_b = ep(x)
         assert torch.equal(logits_a, logits_b)
         assert torch.equal(got, want), f"expert-parallel output differs at {(E, hidden, inter, tokens, asym)} on rank {rank}"
         for it in range(3):
+            poison()
             got_p, _ = ep_peer(x)
             assert torch.equal(got_p, want), f"peer-exchange expert-parallel output differs, call {it}, rank {rank}"
     if "--time" in sys.argv:
