@@ -12,8 +12,10 @@
 // One tcgen05.mma instruction costs about the same time for any N up to 128-256, so every instruction is made as
 // wide as tensor memory allows:
 //   stage A   D1 = (I8 (x) H16 / 8) X on SUPER TILES of four tiles of 128 lines side by side (kind::f16, M = 128,
-//             N = 128, K = 128: eight instructions per 512 lines).  The rows of a CTA are one stream of lines, so tiles
-//             do not care where a row ends.
+//             N = 128, K = 128: eight instructions per row).  A super tile is ONE row: the TMA map is three-
+//             dimensional (row, line, value), the fourth tile's last 64 lines lie past the row's 448 and are filled with
+//             zeros, so no tile ever holds lines of two rows and rows stay independent (the zeros of the block-diagonal
+//             constant would otherwise turn one row's NaN or infinity into its neighbour's: 0 x inf).
 //   stage B   eight warps read D1 (one line per thread), finish the 512-point transform with five butterfly stages
 //             between registers, scale, round to fp16 and store Z[k][j] (j = 32 h' + l') into shared memory: K line =
 //             segment, 128-byte swizzle, blocks of 64 j.  A warp's 32 lines are two whole segments of ONE row
@@ -27,13 +29,6 @@
 //             to even, clamp) and stores its 32 codes as 16 consecutive bytes.
 // Roles of the one CTA per SM: warp 0 TMA producer, warp 1 stage-A MMAs, warp 2 stage-C MMAs, warps 4-11 stage B,
 // warps 12-27 stage D.  Every mbarrier wait is bounded (status word, normal return).
-//
-// Rows are NOT independent in one respect: a 128-line tile of stage A holds lines of two rows (a row is 3.5 tiles),
-// and the zeros of the block-diagonal constant operand multiply the other row's lines, so a NaN or an infinity in
-// one row turns the rows that share a tile with it into NaN (0 x inf).  Finite inputs never see this.  A caller whose
-// buffer holds rows of arbitrary bits that it will not use (an expert-parallel MoE block: the rows of other ranks'
-// experts are never written) must not come here; such calls carry per-row sign tables (expert ids) and are left to
-// the mma.sync kernel, which keeps rows apart.
 #include "umma.cuh"
 #include <type_traits>
 
@@ -105,9 +100,8 @@ rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const 
     const uint32_t base_cnt = rows / gridDim.x, rem = rows % gridDim.x;
     const uint32_t row_begin = blockIdx.x * base_cnt + min(blockIdx.x, rem);
     const uint32_t cnt = base_cnt + (blockIdx.x < rem ? 1u : 0u);
-    const uint32_t portions = cnt * PORTIONS_PER_ROW;          // warp-sized groups of 32 lines
-    const uint32_t tiles = (portions + 3) / 4;                  // the last tile of an odd row count is half foreign
-    const uint32_t supers = (tiles + SUPER - 1) / SUPER;
+    const uint32_t supers = cnt;                                // one super tile (four tiles of 128 lines) per row: the last
+                                                                // 64 lines of the fourth tile lie past the row and arrive as zeros
 
     // ---- set-up
     if (tid == 0) {
@@ -183,17 +177,16 @@ rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const 
 
     if (*ab == 0) {
         if (warp == 0) {
-            // ------------------------------------------------ TMA producer: the CTA's rows as one stream of 128-line tiles
+            // ------------------------------------------------ TMA producer: one super tile (four tiles of 128 lines) per row
             if (lane == 0) {
                 pdl_wait();      // x comes from the kernel before this one
                 for (uint32_t sp = 0; sp < supers; ++sp) {
                     const int s = (int)(sp % XS);
-                    const uint32_t n_tiles = min((uint32_t)SUPER, tiles - sp * SUPER);
                     if (!mbar_wait(x_empty(s), ((sp / XS) & 1) ^ 1, ab, 71)) break;
-                    mbar_expect_tx(x_full(s), n_tiles * TILE_BYTES);   // lines past the tensor's end arrive as zeros and count
-                    for (uint32_t i = 0; i < n_tiles; ++i)
-                        tma_load_2d(base + OFF_X + (s * SUPER + i) * TILE_BYTES, &map_x, 0,
-                                    (int)(row_begin * LINES_PER_ROW + (sp * SUPER + i) * 128), x_full(s));
+                    mbar_expect_tx(x_full(s), SUPER * TILE_BYTES);     // lines past the row's end arrive as zeros and count
+                    for (uint32_t i = 0; i < (uint32_t)SUPER; ++i)
+                        tma_load_3d(base + OFF_X + (s * SUPER + i) * TILE_BYTES, &map_x, 0, (int)(i * 128),
+                                    (int)(row_begin + sp), x_full(s));
                 }
             }
         } else if (warp == 1) {
@@ -260,23 +253,23 @@ rotate_quant_had28_umma_kernel(const __grid_constant__ CUtensorMap map_x, const 
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    const uint32_t t = sp * SUPER + (uint32_t)(grp + 2 * i);
-                    const uint32_t portion = 4 * t + (uint32_t)quarter;
+                    // portion (32 lines = two segments) of row sp that this warp holds in tile grp + 2 i: 14 exist
+                    const uint32_t pr = 4u * (uint32_t)(grp + 2 * i) + (uint32_t)quarter;
                     float d[32];
-                    if (portion < portions)
+                    if (pr < (uint32_t)PORTIONS_PER_ROW)
                         tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * 128 + (grp + 2 * i) * 32), d);
                     if (i == 1) {            // both of this warp's tiles are in registers (or skipped): release the accumulator
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         __syncwarp();
                         if (lane == 0) mbar_arrive(d1_empty(a));
                     }
-                    if (portion >= portions) continue;               // lines of a row that is not this CTA's, or no lines at all
-                    const uint32_t r = portion / PORTIONS_PER_ROW, pr = portion % PORTIONS_PER_ROW;
+                    if (pr >= (uint32_t)PORTIONS_PER_ROW) continue;  // the zero padding behind the row's 448 lines
+                    const uint32_t r = sp;
                     const int z = (int)(r & 1);
                     const int k = (int)(2 * pr) + (lane >> 4), hp = lane & 15;       // segment and line h' of this thread
-                    // The Z buffer of row r was last read by the stage-C MMAs of row r - 2.  This warp takes the portions
-                    // p = 4 g + quarter (mod 8) of the stream and a row is 14 consecutive portions, so it has work in EVERY
-                    // row: it sees every phase of this barrier in order, which is what makes the parity test valid.
+                    // The Z buffer of row r was last read by the stage-C MMAs of row r - 2.  Every warp has a portion in tile
+                    // grp of EVERY row (4 grp + quarter < 14), so it sees every phase of this barrier in order, which is
+                    // what makes the parity test valid.
                     if (!__all_sync(0xffffffffu, mbar_wait(z_empty(z), ((r >> 1) & 1) ^ 1, ab, 77))) {
                         alive = false;
                         break;
@@ -433,11 +426,12 @@ int launch_rotate_had28_umma(const RotateArgs &a, cudaStream_t st) {
     umma::EncodeTiledFn fn = umma::encode_fn();
     if (fn == nullptr) return SR_ERR_UNSUPPORTED;      // the mma.sync kernel takes the call
     CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)LW, (cuuint64_t)a.rows * LINES_PER_ROW};
-    const cuuint64_t strides[1] = {(cuuint64_t)LW * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)LW, 128};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(&map, a.in_dtype == SR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+    // [row][448 lines][32 values]: a box of 128 lines never leaves its row; what lies past line 447 is filled with zeros
+    const cuuint64_t dims[3] = {(cuuint64_t)LW, (cuuint64_t)LINES_PER_ROW, (cuuint64_t)a.rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)LW * 2, (cuuint64_t)N * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)LW, 128, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(&map, a.in_dtype == SR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                     const_cast<void *>(a.x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     SR_REQUIRE(r == CUDA_SUCCESS, SR_ERR_CUDA, "rotate_quant: cuTensorMapEncodeTiled failed with code %d", (int)r);

@@ -181,11 +181,12 @@ def test_rotate_quant_expert_signs(n, rows, sorted_rows):
     _ulp_close(rot.cpu(), want)
 
 
-@pytest.mark.parametrize("n,with_ids", [(14336, True), (4096, True), (4096, False)])
+@pytest.mark.parametrize("n,with_ids", [(14336, True), (14336, False), (4096, True), (4096, False)])
 def test_rows_of_arbitrary_bits_do_not_touch_their_neighbours(n, with_ids):
     """An expert-parallel MoE block hands the rotation a buffer in which the rows of other ranks' experts were never
     written: whatever they hold (NaN, infinities), the rows in between must come out as if those rows were zeros.
-    (Calls with per-row sign tables are the ones that can see such buffers; for n = 4096 the same holds without.)"""
+    (Calls with per-row sign tables are the ones that see such buffers; the same holds without them: one request's
+    overflow must not reach another request's tokens.)"""
     g = torch.Generator().manual_seed(31)
     rows, E = 96, 4
     x = _x(rows, n, 13)
