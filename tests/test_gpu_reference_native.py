@@ -223,3 +223,45 @@ def test_paged_cache_and_decode_attention(ref, chunks):
         torch.cuda.synchronize()
         outs.append(o.float())
     assert (outs[0] - outs[1]).abs().max().item() <= 2e-3
+
+
+def test_gqa_decode_against_the_repeated_head_cache(ref):
+    """32 q heads on 8 KV heads: this library keeps every KV head once, the reference's cache repeats it for each q head
+    of its group (signrot/transformers/kv_cache.py:346-353).  Fill this library's cache, repeat its heads into the
+    reference's layout, decode with both kernels: the reference's own split-vs-unsplit bound (2e-3)."""
+    B, Hq, Hkv, D, page, T = 4, 32, 8, 128, 16, 333
+    G = Hq // Hkv
+    g = torch.Generator().manual_seed(5)
+    cache = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, 1, Hkv, D, group_size=G)
+    cache.pages.zero_()
+    cache.scales.zero_()
+    k, v = torch.randn((B, T, Hkv, D), generator=g).half().to(DEV), torch.randn((B, T, Hkv, D), generator=g).half().to(DEV)
+    cache.update(k, v, 0)
+    specs = cache.refresh_specs()
+    q = torch.randn((B, Hq, D), generator=g).half().to(DEV)
+    mine = torch.empty_like(q)
+    kvc.batch_decode_i4(mine, q, **specs, layer_idx=0, hadamard_q=False)
+    ref_data = specs["kv_data"].repeat_interleave(G, dim=3).contiguous()
+    ref_param = specs["kv_param"].repeat_interleave(G, dim=3).contiguous()
+    theirs = torch.empty_like(q)
+    ref.batch_decode_i4(theirs, q, ref_data, ref_param, specs["kv_indptr"], specs["kv_indices"], specs["last_page_offset"], 0)
+    torch.cuda.synchronize()
+    assert (mine.float() - theirs.float()).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("n,heads", [(14336, 0), (4096, 32), (768, 0)])
+def test_fused_rotation_feeds_the_reference_quantizer(ref, n, heads):
+    """The reference has no GPU rotation of its own (fast_hadamard_transform is not in the checkout), but its quantizer
+    can be run on the rotated rows this library returns beside the codes: the codes and scales of the fused kernel must
+    be what signrot._CUDA.sym_quant_dynamic makes of those rows, bit for bit."""
+    from signrot_b200.functional.hadamard import get_hadK
+    x = _acts(64, n, 3)
+    g = torch.Generator().manual_seed(4)
+    if heads:
+        pk, rot = kernel.rotate_quant(x, heads=heads, return_rotated=True)
+    else:
+        hadK, K = get_hadK(n)
+        sign = (torch.randint(0, 2, (n,), generator=g) * 2 - 1).to(torch.int8).to(DEV)
+        pk, rot = kernel.rotate_quant(x, hadK, K, sign=sign, return_rotated=True)
+    rq, rs = ref.sym_quant_dynamic(rot.contiguous(), 1.0)
+    assert _same(pk.scales_x.view(-1), rs.view(-1)) and _same(pk.quantized_x, rq)
