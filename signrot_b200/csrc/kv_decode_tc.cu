@@ -399,14 +399,27 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         for (int gg = 0; gg < G; ++gg) {
             if ((uint32_t)gg % num_chunks != chunk) continue;
             const uint32_t hq = hk * G + gg, at = (uint32_t)gg * (HD + 4);
-            float mm = -5e4f;
-            for (uint32_t c = 0; c < num_chunks; ++c) mm = fmaxf(mm, peer_ld(c, at + HD));
-            float dd = 0.f, oo = 0.f;
-            for (uint32_t c = 0; c < num_chunks; ++c) {
-                const float sc = ex2(peer_ld(c, at + HD) - mm);
-                dd += peer_ld(c, at + HD + 1) * sc;
-                oo += peer_ld(c, at + tid) * sc;
+            // all remote loads first (at most eight chunks in a cluster), so that they are in flight together
+            float mc[8], dc[8], oc[8];
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c) {
+                const bool have = c < num_chunks;
+                mc[c] = have ? peer_ld(c, at + HD) : -5e4f;
+                dc[c] = have ? peer_ld(c, at + HD + 1) : 0.f;
+                oc[c] = have ? peer_ld(c, at + tid) : 0.f;
             }
+            float mm = -5e4f;
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c)
+                if (c < num_chunks) mm = fmaxf(mm, mc[c]);
+            float dd = 0.f, oo = 0.f;
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c)
+                if (c < num_chunks) {
+                    const float sc = ex2(mc[c] - mm);
+                    dd += dc[c] * sc;
+                    oo += oc[c] * sc;
+                }
             o[((size_t)b * hq_total + hq) * HD + tid] = __float2half_rn(__fdividef(oo, dd));
         }
         // no CTA leaves while another one may still read its state
