@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
                  uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters, int cluster_merge,
                  RopeIn rope) {
-    pdl_trigger();   // launched with programmatic serialization (launch_pdl); everything read here is produced upstream
+    pdl_trigger();   // the next kernel of the stream may be scheduled early; this one is launched without the attribute
     pdl_wait();
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
     const uint32_t hq_total = gridDim.y * G;
@@ -127,19 +127,22 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         qsum = s;
     }
 
-    // ---- this chunk's token range (whole pages, as the CUDA-core kernel splits them)
+    // ---- this chunk's token range: an equal share of the request's 16-token blocks (pages are too coarse a unit: nine
+    // pages over four chunks would leave one chunk empty), so every chunk count balances
     const uint32_t page_begin = (uint32_t)kv.indptr[b], page_end = (uint32_t)kv.indptr[b + 1];
     const uint32_t pages_total = page_end - page_begin;
-    const uint32_t per_chunk = (pages_total + num_chunks - 1) / num_chunks;
-    const uint32_t cp_begin = min(chunk * per_chunk, pages_total), cp_end = min(cp_begin + per_chunk, pages_total);
     const uint32_t last_valid = (uint32_t)kv.last_page_offset[b];
     const uint32_t blocks_per_page = kv.page_size / DT_BLOCK;
-    const uint32_t num_blocks = (cp_end - cp_begin) * blocks_per_page;
+    const uint32_t total_blocks =
+        pages_total > 0 ? (pages_total - 1) * blocks_per_page + (last_valid + DT_BLOCK - 1) / DT_BLOCK : 0u;
+    const uint32_t per_chunk = (total_blocks + num_chunks - 1) / num_chunks;
+    const uint32_t cb_begin = min(chunk * per_chunk, total_blocks), cb_end = min(cb_begin + per_chunk, total_blocks);
+    const uint32_t num_blocks = cb_end - cb_begin;
     if (fused) {
         // The new token's K and V go into their slot (the last one of the request) before anybody reads it: only the
-        // chunk that owns the last page does, and it is this CTA that writes it.  Warp 0: K (rotary embedding, head_dim
+        // chunk that owns the last block does, and it is this CTA that writes it.  Warp 0: K (rotary embedding, head_dim
         // rotation, quantizer), warp 1: V (quantizer): the arithmetic of rope_kv_append_kernel.
-        const bool owner = pages_total > 0 && cp_begin <= pages_total - 1 && pages_total - 1 < cp_end;
+        const bool owner = total_blocks > 0 && cb_begin <= total_blocks - 1 && total_blocks - 1 < cb_end;
         if (owner && warp < 2) {
             const __half *src = warp == 0 ? rope.k + (size_t)b * rope.k_stride : rope.v + (size_t)b * rope.v_stride;
             const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(src + (size_t)hk * HD + lane * 4));
@@ -172,11 +175,23 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     // ring[warp][stage]: 64 x 16 B (K), then 128 x 8 B (V), then 128 x 8 B (parameters), lane-interleaved.
     uint8_t *ring = dt_smem + (size_t)warp * DT_DEPTH * DT_STAGE_BYTES;
     const uint32_t ring_u32 = (uint32_t)__cvta_generic_to_shared(ring);
-    auto issue = [&](uint32_t blk, int slot) {
-        if (blk < num_blocks) {
-            const uint32_t pi = cp_begin + blk / blocks_per_page, e0 = (blk % blocks_per_page) * DT_BLOCK;
-            const uint32_t page = (uint32_t)kv.indices[page_begin + pi];
-            const size_t kbase = kv.vec_index(page, 0, hk, e0), vbase = kv.vec_index(page, 1, hk, e0);
+    // The copies run DT_DEPTH blocks ahead of the math along the warp's blocks (every DT_WARPS-th of the chunk).  A cursor
+    // (block, page, offset in the page, base of the page's K and V rows) moves with them, so that a step costs neither a
+    // division nor a look-up in the page table unless the page changes.
+    const uint32_t seq_tokens = total_blocks > 0 ? (pages_total - 1) * kv.page_size + last_valid : 0u;
+    uint32_t i_gb = cb_begin + warp, i_pi = i_gb / blocks_per_page, i_e0 = (i_gb % blocks_per_page) * DT_BLOCK;
+    size_t i_kb = 0, i_vb = 0;
+    auto page_bases = [&]() {
+        if (i_gb < cb_end) {
+            const uint32_t page = (uint32_t)kv.indices[page_begin + i_pi];
+            i_kb = kv.vec_index(page, 0, hk, 0);
+            i_vb = kv.vec_index(page, 1, hk, 0);
+        }
+    };
+    page_bases();
+    auto issue = [&](int slot) {
+        if (i_gb < cb_end) {
+            const size_t kbase = i_kb + i_e0, vbase = i_vb + i_e0;
             // rows past the end of a partially filled page belong to the same allocation: they are read and masked
             const uint8_t *krow = kv.data + (kbase + g) * 64 + qd * 16;
             const uint8_t *vrow = kv.data + (vbase + 2 * qd) * 64 + g * 8;
@@ -192,11 +207,19 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        i_gb += DT_WARPS;
+        i_e0 += DT_WARPS * DT_BLOCK;
+        if (i_e0 >= kv.page_size) {
+            do {
+                i_e0 -= kv.page_size;
+                ++i_pi;
+            } while (i_e0 >= kv.page_size);
+            page_bases();
+        }
     };
     auto fetch = [&](uint32_t blk, int slot, Stage &s) {
-        const uint32_t pi = cp_begin + blk / blocks_per_page, e0 = (blk % blocks_per_page) * DT_BLOCK;
-        const uint32_t valid_page = (pi == pages_total - 1) ? last_valid : kv.page_size;
-        s.valid = valid_page > e0 ? min(valid_page - e0, (uint32_t)DT_BLOCK) : 0u;
+        const uint32_t t0 = (cb_begin + blk) * DT_BLOCK;      // first token of the block, counted along the request
+        s.valid = seq_tokens > t0 ? min(seq_tokens - t0, (uint32_t)DT_BLOCK) : 0u;
         const uint8_t *src = ring + (size_t)slot * DT_STAGE_BYTES;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
@@ -311,7 +334,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
     };
 
 #pragma unroll 1
-    for (int d = 0; d < DT_DEPTH; ++d) issue(warp + d * DT_WARPS, d);
+    for (int d = 0; d < DT_DEPTH; ++d) issue(d);
     int slot = 0;
 #pragma unroll 1
     for (uint32_t blk = warp; blk < num_blocks; blk += DT_WARPS) {
@@ -319,7 +342,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         Stage st;
         fetch(blk, slot, st);
         process(st);
-        issue(blk + DT_DEPTH * DT_WARPS, slot);   // after the math that consumed the slot
+        issue(slot);   // after the math that consumed the slot
         slot = slot + 1 == DT_DEPTH ? 0 : slot + 1;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -468,8 +491,10 @@ int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __hal
     if (kv.page_size % DT_BLOCK != 0) return 0;
     RopeIn rope = {};
     if (rope_in != nullptr) rope = *rope_in;
-    // up to eight chunks (the portable cluster size): the chunks of a (request, KV head) form a cluster and merge in it
-    bool cluster = counters == nullptr && num_chunks >= 2 && num_chunks <= 8;
+    // two or four chunks: the chunks of a (request, KV head) form a cluster and merge in it.  Measured on B200 (batch 8,
+    // 8 KV heads, context 2048, launches back to back): clusters of 2 and 4 cost nothing to place and the merge inside
+    // them 1.0 us (the separate merge launch: 2.2 us); clusters of 5 and 8 take 3.4 us and more just to be placed.
+    bool cluster = counters == nullptr && (num_chunks == 2 || num_chunks == 4);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(DT_WARPS * 32);
@@ -477,11 +502,10 @@ int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __hal
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     int na = 0;
-    if (pdl_enabled()) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
+    // Not launched with programmatic serialization, although the kernel before it is: CTAs that become resident while
+    // the projection GEMM still fills every SM are placed wherever one of its CTAs happens to retire first, up to
+    // three on one SM and none on others, and the attention then runs at the pace of the crowded SMs.  Measured on
+    // B200 (Llama-3-8B, batch 8, context 2100): 2.20 ms per decode step with the attribute, 2.03 ms without.
     if (cluster) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = 1;
