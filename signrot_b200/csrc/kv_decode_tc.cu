@@ -4,8 +4,8 @@
 // request against a quantized paged cache) with the same workspace format as the CUDA-core kernel in
 // kv_cache.cu: per (request, q head, chunk) 128 unnormalised outputs, the running maximum and the sum.
 //
-// grid (batch, kv heads, chunks), 4 warps; a warp takes blocks of 16 cached tokens (block index
-// = warp, warp + 4, ... inside the chunk's pages) and keeps the flash-decoding state of all q heads
+// grid (batch, kv heads, chunks), 8 warps; a warp takes blocks of 16 cached tokens (block index
+// = warp, warp + 8, ... inside the chunk's range) and keeps the flash-decoding state of all q heads
 // of the group (rows of an m16 tile; rows >= G stay zero).
 //
 // The 4-bit codes never become numbers on the CUDA cores.  A code n masked into the low bits of an
@@ -27,13 +27,13 @@ namespace sr {
 
 namespace {
 
-constexpr int DT_WARPS = 4;
+constexpr int DT_WARPS = 8;    // the step is a chain of dependent instructions: the schedulers need warps to switch between
 constexpr int DT_BLOCK = 16;   // cached tokens per warp iteration
-constexpr int DT_DEPTH = 4;    // blocks in flight per warp
+constexpr int DT_DEPTH = 3;    // blocks in flight per warp (two CTAs and their rings fit one SM)
 constexpr int DT_STAGE_BYTES = 3072;   // per warp and block: 2 KB of codes + 1 KB of parameter pairs (tokens repeat across lanes)
 constexpr int DT_RING_BYTES = DT_WARPS * DT_DEPTH * DT_STAGE_BYTES;
 #ifndef DT_MIN_CTAS
-#define DT_MIN_CTAS 4
+#define DT_MIN_CTAS 2
 #endif
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -371,8 +371,8 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         }
     }
     __syncthreads();
-    // thread t finalises dim t (HD == blockDim) for every head of the group
-    for (int gg = 0; gg < G; ++gg) {
+    // thread t < HD finalises dim t for every head of the group
+    for (int gg = 0; gg < G && tid < HD; ++gg) {
         float mm = sh_md[0][gg][0];
 #pragma unroll
         for (int w = 1; w < DT_WARPS; ++w) mm = fmaxf(mm, sh_md[w][gg][0]);
@@ -419,7 +419,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
                 : "memory");
             return v;
         };
-        for (int gg = 0; gg < G; ++gg) {
+        for (int gg = 0; gg < G && tid < HD; ++gg) {
             if ((uint32_t)gg % num_chunks != chunk) continue;
             const uint32_t hq = hk * G + gg, at = (uint32_t)gg * (HD + 4);
             // all remote loads first (at most eight chunks in a cluster), so that they are in flight together
@@ -465,7 +465,7 @@ decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ 
         __syncthreads();
         if (is_last) {
             __threadfence();
-            for (int gg = 0; gg < G; ++gg) {
+            for (int gg = 0; gg < G && tid < HD; ++gg) {
                 const uint32_t hq = hk * G + gg;
                 const float *src = tmp + ((size_t)b * hq_total + hq) * num_chunks * (HD + 4);
                 float mm = -5e4f;

@@ -276,7 +276,7 @@ def decode_split(batch_size, kv_heads, max_pages, device):
     (the kernel shares a request's 16-token blocks out evenly, whatever the count)."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     per_sm = int(os.environ.get("SIGNROT_B200_DECODE_CTAS_PER_SM", "2"))
-    chunks = max(1, -(-per_sm * sms // (batch_size * kv_heads)))
+    chunks = max(1, per_sm * sms // (batch_size * kv_heads))     # two 8-warp CTAs fit an SM: no second wave
     if chunks < 8:
         # 2 or 4 chunks merge inside a thread-block cluster (no second launch); other cluster sizes are slow to place
         chunks = 1 << (chunks.bit_length() - 1)
