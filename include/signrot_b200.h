@@ -323,10 +323,11 @@ int sr_rope_decode_i4(void *o, const void *q, const void *k, const void *v, int6
 /* o, q fp16 [batch, num_qo_heads, 128]; one new token per request attends to its cached
  * sequence.  num_qo_heads is a multiple (1, 2, 4, 8) of num_kv_heads: q head h reads KV head
  * h / (num_qo_heads / num_kv_heads).  tmp fp32 [batch, num_qo_heads, num_chunks, 132] is the
- * split-KV workspace (NULL or num_chunks <= 1: no split).  With 2 .. 8 chunks (and a page size
- * that is a multiple of 16) the chunks of a (request, KV head) run as one thread-block cluster and
- * merge through distributed shared memory: tmp must still be given, it is left untouched; with
- * more chunks the states go through tmp and a second launch merges them.  The result is the same
+ * split-KV workspace (NULL or num_chunks <= 1: no split); a chunk is an equal share of the request's
+ * 16-token blocks.  With 2 or 4 chunks (and a page size that is a multiple of 16) the chunks of a
+ * (request, KV head) run as one thread-block cluster and merge through distributed shared memory:
+ * tmp must still be given, it is left untouched; with any other count the states go through tmp
+ * and a second launch merges them.  The result is the same
  * bits either way.  hadamard_q applies H_128/sqrt(128)
  * to q first (kv_cache.py:157-158).  Replaces _CUDA.batch_decode_i4 (bindings.cpp:508-559,
  * flashinfer.cu:11-55, include/flashinfer/decode.cuh:481-751). */

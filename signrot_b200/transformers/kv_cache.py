@@ -338,7 +338,7 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
         if chunks > 1:
             self._stub.tmp = torch.empty((self.batch_size, self.num_heads * self.group_size, chunks,
                                           self.head_dim + 4), dtype=torch.float32, device=self.device)
-            # measured on B200 (batch 8, context 2100, 5 chunks): the in-kernel merge costs 5 us per layer
+            # measured on B200 (batch 8, context 2100): the counter-based in-kernel merge costs 5 us per layer
             # more than the separate merge launch (one CTA merges four heads one after the other behind
             # device-wide fences), so it is opt-in
             if os.environ.get("SIGNROT_B200_DECODE_MERGE", "separate") == "fused":
