@@ -229,11 +229,13 @@ def test_in_kernel_merge_equals_merge_pass(T, page, Hq, Hkv, chunks):
 
 @pytest.mark.parametrize("T,page,Hq,Hkv,chunks,per_request_cos", [(2100, 256, 32, 8, None, False), (513, 128, 32, 8, 3, True),
                                                                   (1000, 16, 8, 2, 12, False), (300, 32, 4, 4, 1, True),
-                                                                  (255, 256, 16, 2, None, False), (256, 256, 8, 8, 2, True)])
+                                                                  (255, 256, 16, 2, None, False), (256, 256, 8, 8, 2, True),
+                                                                  (40, 16, 8, 2, 4, False), (70, 64, 8, 8, 4, True)])
 def test_decode_step_in_one_launch_equals_two(T, page, Hq, Hkv, chunks, per_request_cos):
     """Rotary embedding + K/V append + attention as one launch (`rope_decode_i4`) against `rope_kv_append` followed
     by `batch_decode_i4`: same attention output, same cache bytes, for three decode steps in a row (the second and
-    third read what the first appended; T = 255 / 256 put the new token at the end of a page / on a new page), with
+    third read what the first appended; T = 255 / 256 put the new token at the end of a page / on a new page; T = 40 and
+    70 with 4 chunks leave the last chunk of the cluster without a block, so the new token belongs to the third), with
     q / k / v as column ranges of one fused projection output."""
     B, L = 3, 2
     k, v, ref, pages = _fill(B, L, Hkv, page, T, T + 4)
