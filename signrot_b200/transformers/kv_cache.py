@@ -327,7 +327,8 @@ class MultiLayerPagedKVCache4Bit(_HFCache):
 
     def _configure_decode_split(self, max_pages):
         """Fixed number of sequence chunks per (request, KV head) so that about two CTAs per SM
-        are in flight; bounded by the page count (a chunk is a page range).  `decode_chunks`
+        are in flight; bounded by the page count (a chunk is an equal share of the request's 16-token blocks; a page range in the
+        CUDA-core kernel that takes page sizes which are not multiples of 16).  `decode_chunks`
         pins the number (a tensor-parallel shard uses the split of the unsharded head count, so
         that its fp32 merge order, and with it every output bit, is that of one GPU)."""
         if self.decode_chunks is not None:
