@@ -86,6 +86,18 @@ int sr_matmul_i4_ld(const void *A, int64_t lda_bytes, const void *B, int64_t M, 
 int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
                    const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *stream);
 
+/* sr_w4a4_linear with a scratch buffer for the long-K shapes whose 256 x 256 output tiles would leave at least half
+ * of the GPU idle (e.g. M = 256, K = 14336, N = 4096: 16 tiles for 74 CTA pairs): the K dimension of every tile is
+ * split over 2 or 4 CTA pairs, the int32 partial sums meet in `ws` and are added there, so the result is the bit
+ * pattern of sr_w4a4_linear.  sr_w4a4_linear_ws_bytes gives the size `ws` needs (0: this shape does not split; then
+ * ws may be NULL and the call is sr_w4a4_linear).  `counters`: 1024 int32 in device memory, zero before the first
+ * call and never written by anybody else (they only grow, by the number of k-ranges per launch); one buffer serves
+ * all calls of a stream, calls that may run at the same time need their own.  ws 16-byte aligned. */
+int sr_w4a4_linear_ws_bytes(int64_t M, int64_t N, int64_t K, int64_t *bytes);
+int sr_w4a4_linear_ws(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                      const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *ws,
+                      int64_t ws_bytes, void *counters, void *stream);
+
 /* Fused edge of the path for decode: gate_proj and up_proj of a SwiGLU MLP and the activation in
  * one launch.  W = [2N, K/2]: the N gate rows followed by the N up rows (w_scale [2N], w_sum [2N]
  * and bias [2N] likewise); out[M, N] fp16 = rn_h(rn_h(silu(gate)) * up) with gate/up the fp16

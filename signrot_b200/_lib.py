@@ -32,6 +32,8 @@ _SIGNATURES = {
     "sr_matmul_i4": [_P, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_matmul_i4_ld": [_P, _I64, _P, _I64, _I64, _I64, _I, _P, _P],
     "sr_w4a4_linear": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
+    "sr_w4a4_linear_ws_bytes": [_I64, _I64, _I64, _P],
+    "sr_w4a4_linear_ws": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _I64, _P, _P],
     "sr_w4a4_swiglu": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
     "sr_grouped_linear": [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _P, _P],
     "sr_matmul_grouped": [_P, _I64, _P, _P, _P, _P, _P, _P, _I, _I64, _P],

@@ -16,7 +16,8 @@ static bool decode_regime(int64_t M, int64_t N) { return M <= 32 || (M <= 64 && 
 static int64_t max_k(bool a_unsigned) { return a_unsigned ? 65536 : 131040; }
 
 static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t K, int a_unsigned,
-                    const Epilogue &ep, void *stream, const char *who) {
+                    const Epilogue &ep, void *stream, const char *who, void *ws = nullptr, int64_t ws_bytes = 0,
+                    void *split_cnt = nullptr) {
     SR_REQUIRE(M >= 0 && N >= 0 && K >= 0, SR_ERR_INVALID, "%s: negative size", who);
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "%s: A.shape[-1]: %lld must be multiplication of 32", who, (long long)K);
     if (M == 0 || N == 0) return SR_OK;
@@ -28,7 +29,8 @@ static int run_gemm(const void *A, const void *B, int64_t M, int64_t N, int64_t 
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "%s: operands must be 16-byte aligned", who);
     if (decode_regime(M, N))
         return launch_gemm_skinny((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
-    return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream));
+    return launch_gemm_tc3((const uint8_t *)A, (const uint8_t *)B, M, N, K, a_unsigned != 0, ep, as_stream(stream),
+                           (int32_t *)ws, ws_bytes, (int32_t *)split_cnt);
 }
 
 }  // namespace sr
@@ -75,6 +77,30 @@ int sr_w4a4_linear(const void *A, const void *a_scale, const void *a_zero, const
     ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
     ep.bias = (const __half *)bias;
     return run_gemm(A, W, M, N, K, a_zero != nullptr, ep, stream, "w4a4_linear");
+}
+
+int sr_w4a4_linear_ws_bytes(int64_t M, int64_t N, int64_t K, int64_t *bytes) {
+    SR_REQUIRE(bytes != nullptr, SR_ERR_INVALID, "w4a4_linear_ws_bytes: null pointer");
+    *bytes = (M <= 0 || N <= 0 || K <= 0 || decode_regime(M, N)) ? 0 : gemm_tc3_splitk_bytes(M, N, K);
+    return SR_OK;
+}
+
+int sr_w4a4_linear_ws(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,
+                      const void *w_sum, const void *bias, int64_t M, int64_t N, int64_t K, void *out, void *ws,
+                      int64_t ws_bytes, void *counters, void *stream) {
+    SR_REQUIRE(M == 0 || N == 0 || (out && a_scale && w_scale), SR_ERR_INVALID, "w4a4_linear: null pointer");
+    SR_REQUIRE(a_zero == nullptr || w_sum != nullptr, SR_ERR_INVALID,
+               "w4a4_linear: asymmetric activations need the int4 row sums of the weight");
+    SR_REQUIRE(ws_bytes >= 0 && (ws_bytes == 0 || (ws && counters)), SR_ERR_INVALID, "w4a4_linear: workspace without counters");
+    Epilogue ep = {};
+    ep.mode = 1;
+    ep.out = (__half *)out;
+    ep.a_scale = (const __half *)a_scale;
+    ep.w_scale = (const __half *)w_scale;
+    ep.a_zero = (const int8_t *)a_zero;
+    ep.w_sum = a_zero ? (const int32_t *)w_sum : nullptr;
+    ep.bias = (const __half *)bias;
+    return run_gemm(A, W, M, N, K, a_zero != nullptr, ep, stream, "w4a4_linear", ws, ws_bytes, counters);
 }
 
 int sr_w4a4_swiglu(const void *A, const void *a_scale, const void *a_zero, const void *W, const void *w_scale,

@@ -144,8 +144,11 @@ int launch_gemm_skinny_swiglu(const uint8_t *A, const uint8_t *B, int64_t M, int
                               const Epilogue &ep, cudaStream_t st);
 int launch_gemm_skinny_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
                                const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st);
+// ws / ws_bytes / split_cnt: optional split-K workspace (gemm_tc3_splitk_bytes) and its zeroed, self-resetting counters
 int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                    const Epilogue &ep, cudaStream_t st);
+                    const Epilogue &ep, cudaStream_t st, int32_t *ws = nullptr, int64_t ws_bytes = 0,
+                    int32_t *split_cnt = nullptr);
+int64_t gemm_tc3_splitk_bytes(int64_t M, int64_t N, int64_t K);   // 0: the launch would not split K
 int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,
                             const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st);
 int launch_gemm_tc3_ptr_array(const int32_t *sizes, int64_t P, const int64_t *ptr_a, const int64_t *ptr_b,

@@ -21,6 +21,13 @@
 // Cross-CTA signalling uses mbarrier arrives on the leader's barriers through mapa addresses.
 // Every wait is bounded by a cycle limit; on expiry the CTA aborts, both CTAs fall through to
 // the cluster barrier at the end, TMEM is released and the device status word records the code.
+//
+// Split K (dense launches with a caller-provided workspace, problems with so few tiles that at least half of the
+// CTA pairs would idle and K is long, e.g. M = 256, K = 14336, N = 4096: 16 tiles for 74 pairs): an item is (tile, k-range),
+// S = 2 or 4 ranges per tile, tiles * S <= pairs, so every item of the launch is resident at the same time.  A
+// pair's epilogue warps write their int32 accumulator to the workspace, count themselves in, wait (bounded) for the
+// other ranges of the tile, and then each range sums and finishes 1 / S of the tile's columns: integer addition,
+// so the result is the bit pattern of the unsplit product.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cuda.h>
@@ -50,6 +57,7 @@ constexpr int BAR_BYTES = 512;
 constexpr int MAX_EXPERTS = 512;                    // grouped launches: first m-tile of every expert, in shared memory
 constexpr int SCHED_BYTES = (MAX_EXPERTS + 4) * 4;
 constexpr int EPI_STAGE_BYTES = 4 * 2560;           // one 32 x 80-byte output staging area per epilogue warp
+constexpr int SPLIT_COUNTERS = 1024;                // int32 words of the split-K counters: two banks (S = 2, 4)
 constexpr int MAX_SMEM = 226 * 1024;   // dynamic part; the kernel also has a few static words
 __host__ __device__ constexpr int smem_bytes(int sp, int su) {
     return su * (UN_A + UN_B) + sp * (PK_A + PK_B) + BAR_BYTES + SCHED_BYTES + EPI_STAGE_BYTES + 1024;
@@ -128,14 +136,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Tile -> coordinates.  Dense: tile = m_tile * tiles_n + n_tile over one [M, N] problem.
@@ -148,7 +156,97 @@ struct TileCoord {
     uint32_t n0;        // first output column
     uint32_t row_end;   // rows >= row_end are not stored
     uint32_t bn;        // output columns of this item: 256, or 128 for the halves of the last wave's tiles
+    uint32_t kb0;       // first k-block of this item (split K; 0 otherwise)
+    uint32_t ks;        // which k-range of its tile this item is
+    uint32_t tile;      // tile index (split K: the counter the ranges of a tile meet at)
 };
+
+// Epilogue of one split-K item (see the header): the warp's 32 accumulator rows go to the workspace, the warp meets
+// the warps of the same rows in the other k-ranges' pairs on a counter of its own (tile, CTA rank, quarter), then
+// sums and finishes the chunks c = ks, ks + S, ... of the tile.  Not inlined: the unsplit path keeps its registers.
+__device__ __noinline__ bool splitk_epilogue(const Epilogue ep, int32_t *__restrict__ ws, int32_t *__restrict__ split_cnt,
+                                             uint32_t tmem_rows, uint32_t acc_empty_bar, const TileCoord tc, uint32_t S,
+                                             uint32_t m_pad, uint32_t n_pad, uint32_t row0, int lane, uint32_t rank,
+                                             uint32_t quarter, uint32_t N, bool small, uint8_t *stage, volatile int *ab) {
+    const int chunks = (int)(tc.bn / 32);
+    // The workspace is not a matrix: the warp that reads a piece is the warp of the same (tile, CTA rank, quarter) in
+    // another pair, with the same lane on the same row, so a piece is stored where the 32 lanes of one store (or load)
+    // instruction touch 512 consecutive bytes: ws[k-range][tile][rank][quarter][chunk][j][lane] in units of int4.
+    const size_t slab = (size_t)m_pad * n_pad;                            // int32 words per k-range
+    const size_t at = ((((size_t)tc.tile * 2 + rank) * 4 + quarter) * 8) * 8 * 32 * 4 + (size_t)lane * 4;
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+        int v[32];
+        tmem_ld32(tmem_rows + (uint32_t)(c * 32), v);
+        if (c == chunks - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty_bar, 0);
+        }
+        int4 *dst = reinterpret_cast<int4 *>(ws + (size_t)tc.ks * slab + at + (size_t)c * 8 * 32 * 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j * 32] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    __threadfence();                                                    // this lane's partial sums are visible device-wide
+    __syncwarp();
+    // The counter only ever grows: every launch adds S to it, so the arrivals of this launch are old .. old + S - 1 with
+    // old a multiple of S, and everybody waits for the next multiple.  One bank of counters per S (a counter that has
+    // served S = 4 need not hold a multiple of 8), nothing to put back at the end.
+    const uint32_t bank = S == 2 ? 0u : 1u;
+    int32_t *cnt = split_cnt + bank * (SPLIT_COUNTERS / 2) + ((2 * tc.tile + rank) * 4 + quarter);
+    int gave_up = 0;
+    if (lane == 0) {
+        const uint32_t old = (uint32_t)atomicAdd(cnt, 1);
+        const uint32_t target = (old / S + 1) * S;
+        const long long t0 = clock64();
+        while ((int32_t)((uint32_t)*reinterpret_cast<volatile int32_t *>(cnt) - target) < 0) {
+            if (*ab != 0) {
+                gave_up = 1;
+                break;
+            }
+            if (clock64() - t0 > WAIT_BUDGET) {                          // a k-range never arrived: give up, keep the context
+                atomicCAS(&g_status, 0, 47);
+                *ab = 47;
+                gave_up = 1;
+                break;
+            }
+        }
+    }
+    gave_up = __shfl_sync(0xffffffffu, gave_up, 0);
+    __threadfence();
+    if (gave_up) return false;
+#pragma unroll 1
+    for (int c = (int)tc.ks; c < chunks; c += (int)S) {
+        int v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0;
+        // four int4 of every k-range at a time (S <= 4): sixteen loads in flight, two trips to L2 per chunk
+        const int4 *src = reinterpret_cast<const int4 *>(ws + at + (size_t)c * 8 * 32 * 4);
+#pragma unroll
+        for (int j = 0; j < 8; j += 4) {
+            int4 q[4][4];
+#pragma unroll
+            for (uint32_t r = 0; r < 4; ++r)
+                if (r < S) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) q[r][i] = __ldcg(src + r * (slab / 4) + (j + i) * 32);
+                }
+#pragma unroll
+            for (uint32_t r = 0; r < 4; ++r)
+                if (r < S) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        v[4 * (j + i)] += q[r][i].x;
+                        v[4 * (j + i) + 1] += q[r][i].y;
+                        v[4 * (j + i) + 2] += q[r][i].z;
+                        v[4 * (j + i) + 3] += q[r][i].w;
+                    }
+                }
+        }
+        store_acc_chunk_warp(ep, row0, lane, tc.n0 + c * 32, v, tc.row_end, N, small, stage);
+    }
+    return true;
+}
 
 // A grouped launch whose sizes the host never sees (the pointer-array entry matmul_grouped): everything the kernel
 // takes from its arguments in the other modes (sizes, row offsets, both tensor maps, the output) is written here by
@@ -166,11 +264,13 @@ struct GroupPlan {
 constexpr int PLAN_SLOTS = 16;        // one per stream that calls the entry (see plan_slot)
 __device__ GroupPlan g_plans[PLAN_SLOTS];
 
-template <bool A_UNSIGNED, int G, bool PLAN>
+// SPLITK: the instantiation that may split K (dense launches with a workspace); the others carry none of its code.
+template <bool A_UNSIGNED, int G, bool PLAN, bool SPLITK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
                 uint32_t N_arg, uint32_t K_arg, int SP, int SU, const int32_t *__restrict__ row_off_arg,
-                int num_experts_arg, Epilogue ep_arg, const GroupPlan *__restrict__ plan) {
+                int num_experts_arg, Epilogue ep_arg, const GroupPlan *__restrict__ plan, int ksplit,
+                int32_t *__restrict__ ws, int32_t *__restrict__ split_cnt) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -266,18 +366,25 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // Work items.  Tiles are dealt round-robin to the clusters; when the last round would leave at least half of
     // the clusters idle, its tiles are split into two 256 x 128 halves so that the round costs half a tile.
     // (A problem with so few tiles that even the halves leave clusters idle is split entirely.)
+    // Split K (S > 1; the host has checked tiles * S <= clusters and num_kb % S == 0): item = tile * S + k-range.
+    const uint32_t S = (!SPLITK || PLAN || grouped || ksplit < 1) ? 1u : (uint32_t)ksplit;
+    const uint32_t kbs = num_kb / S;                      // k-blocks of one item
     const uint32_t rem = num_tiles % clusters;
-    const uint32_t split = (2 * num_tiles <= clusters) ? num_tiles : ((rem != 0 && 2 * rem <= clusters) ? rem : 0u);
-    const uint32_t full_items = num_tiles - split, num_items = num_tiles + split;
+    const uint32_t split = S > 1 ? 0u
+                                 : ((2 * num_tiles <= clusters) ? num_tiles : ((rem != 0 && 2 * rem <= clusters) ? rem : 0u));
+    const uint32_t full_items = (num_tiles - split) * S, num_items = (num_tiles + split) * S;
     auto coord = [&](uint32_t item) {
         TileCoord c;
-        uint32_t tile = item, half = 0;
+        uint32_t tile = item / S, half = 0;
+        c.ks = item % S;
+        c.kb0 = c.ks * kbs;
         c.bn = BN;
         if (item >= full_items) {
             tile = full_items + ((item - full_items) >> 1);
             half = (item - full_items) & 1;
             c.bn = BN / 2;
         }
+        c.tile = tile;
         const uint32_t mt = tile / tiles_n, nt = tile % tiles_n;
         c.n0 = nt * BN + half * (BN / 2);
         if (!grouped) {
@@ -315,13 +422,13 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const TileCoord tc = coord(item);
                     const int ya = (int)(tc.a_row + rank * BMC);
                     const int yb = (int)(tc.b_row + rank * (tc.bn / 2));   // a half tile uses the first 64 rows of the box
-                    for (uint32_t kb = 0; kb < num_kb; ++kb, pr.next(SP)) {
+                    for (uint32_t kb = 0; kb < kbs; ++kb, pr.next(SP)) {
                         const int s = pr.s;
                         ok = mbar_wait(pk_empty(s), pr.ph ^ 1, ab, 41);
                         if (!ok) break;
                         mbar_expect_tx(pk_full(s), PK_A + PK_B);
-                        tma_load_2d(base + off_pk_a + s * PK_A, pmap_a, (int)(kb * PK_ROW), ya, pk_full(s));
-                        tma_load_2d(base + off_pk_b + s * PK_B, pmap_b, (int)(kb * PK_ROW), yb, pk_full(s));
+                        tma_load_2d(base + off_pk_a + s * PK_A, pmap_a, (int)((tc.kb0 + kb) * PK_ROW), ya, pk_full(s));
+                        tma_load_2d(base + off_pk_b + s * PK_B, pmap_b, (int)((tc.kb0 + kb) * PK_ROW), yb, pk_full(s));
                     }
                 }
             }
@@ -340,7 +447,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t d_tmem = tmem_acc + buf * BN;
-                    for (uint32_t kb = 0; kb < num_kb; ++kb, ur.next(SU)) {
+                    for (uint32_t kb = 0; kb < kbs; ++kb, ur.next(SU)) {
                         const int s = ur.s;
                         ok = mbar_wait(un_full(s), ur.ph, ab, 43);
                         if (!ok) break;
@@ -372,6 +479,12 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t row0 = m0 + quarter * 32;
                 uint8_t *stage = epi_stage + quarter * 2560;
+                if (SPLITK && S > 1) {
+                    ok = splitk_epilogue(ep, ws, split_cnt, tmem_acc + ((quarter * 32u) << 16) + buf * BN, acc_empty(buf), tc, S,
+                                         tiles_m * 2 * BMC, tiles_n * BN, row0, lane, rank, quarter, N, small, stage, ab);
+                    if (!ok) break;
+                    continue;
+                }
 #pragma unroll 1
                 for (int c = 0; c < chunks; ++c) {
                     int v[32];
@@ -401,7 +514,7 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t st_off = (uint32_t)((r0 >> 3) * 1024 + (r0 & 7) * 128);
             const uint32_t sw_e = (uint32_t)(((2 * qd) ^ (r0 & 7)) << 4), sw_o = (uint32_t)(((2 * qd + 1) ^ (r0 & 7)) << 4);
             const uint32_t my_items = (num_items > cluster) ? ((num_items - cluster - 1) / clusters + 1) : 0;
-            const uint32_t total = my_items * num_kb;
+            const uint32_t total = my_items * kbs;
             bool ok = true;
             Ring pr, ur;
             for (int i = 0; i < grp; ++i) {
@@ -411,8 +524,8 @@ gemm_tc3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // position of k-block g in the item sequence: a half tile needs only the first 64 rows of B
             uint32_t cur_item = cluster, kb_pos = (uint32_t)grp;
             for (uint32_t g = grp; g < total && ok; g += G, kb_pos += G) {
-                while (kb_pos >= num_kb) {
-                    kb_pos -= num_kb;
+                while (kb_pos >= kbs) {
+                    kb_pos -= kbs;
                     cur_item += clusters;
                 }
                 const int b_steps = cur_item >= full_items ? STEPS / 4 : STEPS / 2;
@@ -627,8 +740,30 @@ group_plan_kernel(const __grid_constant__ CUtensorMap tmpl_small, const __grid_c
 // Shared launcher.  row_off == null: one dense [M, N] problem.  Otherwise M is the total number
 // of (expert-sorted) rows, B holds num_experts stacked [N, K/2] weights and row_off[num_experts + 1]
 // lives on the device, so the grid is sized for the worst case (every expert adds a partial tile).
+// K ranges per tile of a dense launch (1 = no split): 4 or 2, every item with its own CTA pair and at least sixteen
+// k-blocks, for long-K problems whose tiles would leave half of the pairs idle.
+static int tc3_ksplit(int64_t M, int64_t N, int64_t K, int sm_count) {
+    using namespace tc3;
+    const int64_t tiles = cdiv<int64_t>(N, BN) * cdiv<int64_t>(M, 2 * BMC), clusters = sm_count / 2;
+    const int64_t num_kb = cdiv<int64_t>(K, BK);
+    // measured on B200 at M = 256: meeting in the workspace costs about 10 us per launch, so the split pays for long K
+    // only ((K, N) = (14336, 4096): 42 -> 27 us with four ranges; (4096, 4096): 16 -> 20 us, left alone)
+    if (2 * tiles > clusters || num_kb < 64) return 1;
+    for (int s = 4; s >= 2; s >>= 1)
+        if (tiles * s <= clusters && num_kb % s == 0 && num_kb / s >= 16) return s;
+    return 1;
+}
+
+int64_t gemm_tc3_splitk_bytes(int64_t M, int64_t N, int64_t K) {
+    using namespace tc3;
+    const int s = tc3_ksplit(M, N, K, current_sm_count());
+    if (s == 1) return 0;
+    return (int64_t)s * cdiv<int64_t>(M, 2 * BMC) * 2 * BMC * cdiv<int64_t>(N, BN) * BN * 4;
+}
+
 static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                      const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st) {
+                      const Epilogue &ep, const int32_t *row_off, int num_experts, cudaStream_t st,
+                      int32_t *ws = nullptr, int64_t ws_bytes = 0, int32_t *split_cnt = nullptr) {
     using namespace tc3;
     SR_REQUIRE(aligned16(A) && aligned16(B), SR_ERR_INVALID, "matmul: operands must be 16-byte aligned");
     SR_REQUIRE(K % 32 == 0, SR_ERR_INVALID, "matmul: K = %lld must be a multiple of 32", (long long)K);
@@ -644,19 +779,27 @@ static int launch_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, 
     const int64_t m_tiles = row_off ? cdiv<int64_t>(M, 2 * BMC) + num_experts : cdiv<int64_t>(M, 2 * BMC);
     const int64_t tiles = cdiv<int64_t>(N, BN) * m_tiles;
     int64_t clusters = sm_count / 2;
-    if (2 * tiles <= clusters) clusters = 2 * tiles;   // every tile is split into two halves (see the kernel)
+    int ksplit = 1;
+    if (!row_off && ws != nullptr && split_cnt != nullptr) {
+        ksplit = tc3_ksplit(M, N, K, sm_count);
+        if (ksplit > 1 && (ws_bytes < gemm_tc3_splitk_bytes(M, N, K) || !aligned16(ws) || 2 * tiles * 4 > SPLIT_COUNTERS / 2))
+            ksplit = 1;
+    }
+    if (ksplit > 1) clusters = tiles * ksplit;         // every k-range of every tile has its own pair
+    else if (2 * tiles <= clusters) clusters = 2 * tiles;   // every tile is split into two halves (see the kernel)
     else if (tiles < clusters) clusters = tiles;
     // ring depths: packed (TMA) stages, unpacked int8 stages, unpack warp groups (a group may run at most one
     // pass ahead of a ring's barriers, so groups <= both depths)
     constexpr int sp = 5, su = 4, groups = 4;
     static_assert(groups <= sp && groups <= su, "unpack groups exceed a ring depth");
     void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, const int32_t *, int,
-                Epilogue, const GroupPlan *);
-    kfn = a_unsigned ? gemm_tc3_kernel<true, groups, false> : gemm_tc3_kernel<false, groups, false>;
+                Epilogue, const GroupPlan *, int, int32_t *, int32_t *);
+    if (ksplit > 1) kfn = a_unsigned ? gemm_tc3_kernel<true, groups, false, true> : gemm_tc3_kernel<false, groups, false, true>;
+    else kfn = a_unsigned ? gemm_tc3_kernel<true, groups, false> : gemm_tc3_kernel<false, groups, false>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     launch_pdl(kfn, dim3((unsigned)(2 * clusters)), dim3(THREADS), smem_bytes(sp, su), st, ma, mb, (uint32_t)M, (uint32_t)N,
-               (uint32_t)K, sp, su, row_off, num_experts, ep, (const GroupPlan *)nullptr);
+               (uint32_t)K, sp, su, row_off, num_experts, ep, (const GroupPlan *)nullptr, ksplit, ws, split_cnt);
     return check_launch("gemm_tc3");
 }
 
@@ -702,7 +845,7 @@ int launch_gemm_tc3_ptr_array(const int32_t *sizes, int64_t P, const int64_t *pt
     if (rc) return rc;
     constexpr int sp = 5, su = 4, groups = 4;
     void (*kfn)(const CUtensorMap, const CUtensorMap, uint32_t, uint32_t, uint32_t, int, int, const int32_t *, int,
-                Epilogue, const GroupPlan *);
+                Epilogue, const GroupPlan *, int, int32_t *, int32_t *);
     kfn = a_unsigned ? gemm_tc3_kernel<true, groups, true> : gemm_tc3_kernel<false, groups, true>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
     if (e != cudaSuccess) return fail(SR_ERR_CUDA, "matmul_grouped: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -710,14 +853,14 @@ int launch_gemm_tc3_ptr_array(const int32_t *sizes, int64_t P, const int64_t *pt
     ep.mode = 0;
     const int clusters = current_sm_count() / 2;
     launch_pdl(kfn, dim3((unsigned)(2 * clusters)), dim3(THREADS), smem_bytes(sp, su), st, tmpl, tmpl, 0u, 0u, 0u, sp, su,
-               (const int32_t *)nullptr, 0, ep, (const GroupPlan *)plan);
+               (const int32_t *)nullptr, 0, ep, (const GroupPlan *)plan, 1, (int32_t *)nullptr, (int32_t *)nullptr);
     *use_tc_flag = &plan->use_tc;
     return check_launch("gemm_tc3 (pointer array)");
 }
 
 int launch_gemm_tc3(const uint8_t *A, const uint8_t *B, int64_t M, int64_t N, int64_t K, bool a_unsigned,
-                    const Epilogue &ep, cudaStream_t st) {
-    return launch_tc3(A, B, M, N, K, a_unsigned, ep, nullptr, 0, st);
+                    const Epilogue &ep, cudaStream_t st, int32_t *ws, int64_t ws_bytes, int32_t *split_cnt) {
+    return launch_tc3(A, B, M, N, K, a_unsigned, ep, nullptr, 0, st, ws, ws_bytes, split_cnt);
 }
 
 int launch_gemm_tc3_grouped(const uint8_t *A, const uint8_t *B, int64_t rows, int64_t N, int64_t K, bool a_unsigned,

@@ -444,6 +444,32 @@ def grouped_linear(packed: PackedQuantizedTensor, expert_ids, row_offsets, weigh
     return out
 
 
+_WS_BYTES = {}          # (M, N, K) -> bytes of split-K scratch the tensor-core GEMM wants for this shape (0: none)
+_SPLIT_COUNTERS = {}    # (device index, stream) -> the zeroed, self-resetting counters of that stream's split-K launches
+
+
+def _splitk_scratch(dev, M, N, K):
+    """(workspace, bytes, counters) for `sr_w4a4_linear_ws`, or (None, 0, None) when the shape does not split K.
+    The workspace comes from the caching allocator per call; the counters are one small buffer per stream."""
+    import ctypes
+    key = (M, N, K)
+    need = _WS_BYTES.get(key)
+    if need is None:
+        out = ctypes.c_int64(0)
+        from .._lib import call_nostream
+        call_nostream("sr_w4a4_linear_ws_bytes", M, N, K, ctypes.byref(out))
+        need = _WS_BYTES[key] = int(out.value)
+    if need == 0:
+        return None, 0, None
+    ckey = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
+    cnt = _SPLIT_COUNTERS.get(ckey)
+    if cnt is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None, 0, None        # first use inside a capture: no zero-fill there; this call runs unsplit
+        cnt = _SPLIT_COUNTERS[ckey] = torch.zeros(1024, dtype=torch.int32, device=dev)
+    return torch.empty(need, dtype=torch.uint8, device=dev), need, cnt
+
+
 def w4a4_linear(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum=None, bias=None):
     """fp16 `dequant(packed @ weight.T) (+ bias)`: the GEMM, the asymmetric zero correction
     and the dequant of `Linear4bit.forward` (signrot/nn/linear.py:36-50) in one kernel.
@@ -473,6 +499,13 @@ def w4a4_linear(packed: PackedQuantizedTensor, weight, weight_scales, weight_sum
     if bias is not None:
         _check_dtype("w4a4_linear", bias, torch.float16)
     out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    scratch, scratch_bytes, counters = _splitk_scratch(dev, M, N, K)
+    if scratch is not None:
+        # few output tiles for the GPU (e.g. 256 rows against a 4096-wide weight): K split over CTA pairs, same bits
+        run(dev, "sr_w4a4_linear_ws", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
+            ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out), ptr(scratch), scratch_bytes,
+            ptr(counters))
+        return out.view(*lead, N)
     run(dev, "sr_w4a4_linear", ptr(q2), ptr(sx), ptr(zx), ptr(weight), ptr(ws),
         ptr(weight_sum) if zx is not None else None, ptr(bias), M, N, K, ptr(out))
     return out.view(*lead, N)

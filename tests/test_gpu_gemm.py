@@ -125,6 +125,49 @@ def test_w4a4_linear_fused_epilogue(M, K, N, asym, bias):
     assert torch.equal(lin.forward_unfused(pk).cpu(), want)
 
 
+@pytest.mark.parametrize("M,K,N,asym,bias", [(256, 14336, 4096, False, False), (130, 8192, 512, True, True),
+                                             (512, 14336, 4096, False, False), (300, 14336, 2048, True, False)])
+def test_w4a4_linear_split_k_same_bits(M, K, N, asym, bias):
+    """Long-K shapes with few output tiles split K over CTA pairs and meet in a workspace (`sr_w4a4_linear_ws`): the
+    bits of the unsplit launch and of the oracle's row subset, call after call (the counters only grow) and from a
+    replayed graph."""
+    import ctypes
+    from signrot_b200._lib import call_nostream, ptr, run
+    g = torch.Generator().manual_seed(M + N)
+    a = _codes(M, K, 3, 0 if asym else -8, 16 if asym else 8)
+    w = _codes(N, K, 4)
+    A, W = oracle.pack_codes(a).to(DEV), oracle.pack_i4(w).to(DEV)
+    sa = (torch.rand((M,), generator=g) * 0.5 + 0.05).half().to(DEV)
+    sw = (torch.rand((N,), generator=g) * 0.009 + 0.001).half().to(DEV)
+    za = torch.randint(0, 16, (M,), generator=g).to(torch.int8).to(DEV) if asym else None
+    bs = torch.randn((N,), generator=g).half().to(DEV) if bias else None
+    wsum = kernel.sum_i4(W).reshape(-1) if asym else None
+    need = ctypes.c_int64(0)
+    call_nostream("sr_w4a4_linear_ws_bytes", M, N, K, ctypes.byref(need))
+    assert need.value > 0, "this shape is expected to split K"
+    plain = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    run(torch.device(DEV, 0), "sr_w4a4_linear", ptr(A), ptr(sa), ptr(za), ptr(W), ptr(sw), ptr(wsum), ptr(bs), M, N, K, ptr(plain))
+    rows = torch.randperm(M, generator=g)[:24]
+    want = oracle.w4a4_linear(A[rows].cpu(), sa[rows].cpu().view(-1, 1), W.cpu(), sw.cpu().view(-1, 1),
+                              za[rows].cpu().view(-1, 1) if asym else None, wsum.cpu().view(-1, 1) if asym else None,
+                              bs.cpu() if bias else None)
+    assert torch.equal(plain[rows.to(DEV)].cpu(), want)
+    pk = kernel.PackedQuantizedTensor(A, sa, za)
+    for _ in range(3):                                   # the wrapper takes the split route by itself
+        got = kernel.w4a4_linear(pk, W, sw, wsum, bs)
+        assert torch.equal(got, plain)
+    key = (0, torch.cuda.current_stream().cuda_stream)
+    assert int(kernel._SPLIT_COUNTERS[key].sum()) > 0, "the split-K entry was not used"
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        out = kernel.w4a4_linear(pk, W, sw, wsum, bs)
+    for _ in range(2):
+        out.zero_()
+        gr.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, plain)
+
+
 def test_asym_symm_linear():
     M, K, N = 9, 256, 48
     g = torch.Generator().manual_seed(0)
