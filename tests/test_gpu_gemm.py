@@ -158,14 +158,25 @@ def test_w4a4_linear_split_k_same_bits(M, K, N, asym, bias):
         assert torch.equal(got, plain)
     key = (0, torch.cuda.current_stream().cuda_stream)
     assert int(kernel._SPLIT_COUNTERS[key].sum()) > 0, "the split-K entry was not used"
+    # captured on a stream that has its counters already (a first call inside a capture runs unsplit: nothing may be
+    # zero-filled there), replayed twice
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        assert torch.equal(kernel.w4a4_linear(pk, W, sw, wsum, bs), plain)
+    side.synchronize()
+    skey = (0, side.cuda_stream)
+    before = int(kernel._SPLIT_COUNTERS[skey].sum())
     gr = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(gr):
+    with torch.cuda.graph(gr, stream=side):
         out = kernel.w4a4_linear(pk, W, sw, wsum, bs)
     for _ in range(2):
         out.zero_()
+        torch.cuda.synchronize()
         gr.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, plain)
+    assert int(kernel._SPLIT_COUNTERS[skey].sum()) > before, "the captured launch did not split K"
 
 
 def test_asym_symm_linear():
