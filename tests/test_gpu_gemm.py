@@ -126,7 +126,8 @@ def test_w4a4_linear_fused_epilogue(M, K, N, asym, bias):
 
 
 @pytest.mark.parametrize("M,K,N,asym,bias", [(256, 14336, 4096, False, False), (130, 8192, 512, True, True),
-                                             (512, 14336, 4096, False, False), (300, 14336, 2048, True, False)])
+                                             (512, 14336, 4096, False, False), (300, 14336, 2048, True, False),
+                                             (200, 8192, 264, True, True), (65, 16384, 1032, False, True)])
 def test_w4a4_linear_split_k_same_bits(M, K, N, asym, bias):
     """Long-K shapes with few output tiles split K over CTA pairs and meet in a workspace (`sr_w4a4_linear_ws`): the
     bits of the unsplit launch and of the oracle's row subset, call after call (the counters only grow) and from a
