@@ -163,8 +163,8 @@ struct TileCoord {
 
 // Epilogue of one split-K item (see the header): the warp's 32 accumulator rows go to the workspace, the warp meets
 // the warps of the same rows in the other k-ranges' pairs on a counter of its own (tile, CTA rank, quarter), then
-// sums and finishes the chunks c = ks, ks + S, ... of the tile.  Not inlined: the unsplit path keeps its registers.
-__device__ __noinline__ bool splitk_epilogue(const Epilogue ep, int32_t *__restrict__ ws, int32_t *__restrict__ split_cnt,
+// sums and finishes the chunks c = ks, ks + S, ... of the tile.  Only the SPLITK instantiation of the kernel contains it.
+__device__ __forceinline__ bool splitk_epilogue(const Epilogue ep, int32_t *__restrict__ ws, int32_t *__restrict__ split_cnt,
                                              uint32_t tmem_rows, uint32_t acc_empty_bar, const TileCoord tc, uint32_t S,
                                              uint32_t m_pad, uint32_t n_pad, uint32_t row0, int lane, uint32_t rank,
                                              uint32_t quarter, uint32_t N, bool small, uint8_t *stage, volatile int *ab) {
