@@ -570,8 +570,8 @@ def run_ours(args, rank, world, local_rank):
             "frac": round(gemm_ach / int8_peak, 4),
             "peak_source": "measured live: torch._int_mm 8192^3 int8, best of 10 (MEASURED_PEAKS.json has no int8 figure)",
             "peak_bf16_x2": round(2 * pk_["bf16_tflops"], 1), "frac_of_bf16_x2": round(gemm_ach / (2 * pk_["bf16_tflops"]), 4),
-            "traffic": 106.75e6,
-            "traffic_note": "bytes of DRAM traffic (read + write) of one M=4096 K=4096 N=14336 launch, from one ncu capture "
+            "traffic": 123.3e6,
+            "traffic_note": "bytes of DRAM traffic (42.0 MB read + 81.3 MB written) of one M=4096 K=4096 N=14336 launch, from one ncu capture "
                             "(profiles/gemm_tc3_kernel_m4096_k4096_n14336.md), not from this run; the launch's algorithmic "
                             "bytes are 155 MB: part of the fp16 output is still in L2 when the kernel ends",
             "per_shape_ms": [round(v, 4) for v in gemm_ms],
