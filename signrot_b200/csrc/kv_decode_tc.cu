@@ -4,8 +4,8 @@
 // request against a quantized paged cache) with the same workspace format as the CUDA-core kernel in
 // kv_cache.cu: per (request, q head, chunk) 128 unnormalised outputs, the running maximum and the sum.
 //
-// grid (batch, kv heads, chunks), 8 warps; a warp takes blocks of 16 cached tokens (block index
-// = warp, warp + 8, ... inside the chunk's range) and keeps the flash-decoding state of all q heads
+// grid (batch, kv heads, chunks), 8 or 4 warps; a warp takes blocks of 16 cached tokens (block index
+// = warp, warp + warps, ... inside the chunk's range) and keeps the flash-decoding state of all q heads
 // of the group (rows of an m16 tile; rows >= G stay zero).
 //
 // The 4-bit codes never become numbers on the CUDA cores.  A code n masked into the low bits of an
@@ -27,14 +27,13 @@ namespace sr {
 
 namespace {
 
-constexpr int DT_WARPS = 8;    // the step is a chain of dependent instructions: the schedulers need warps to switch between
+// Warps per CTA: 8 (two CTAs per SM: the step is a chain of dependent instructions and the schedulers need warps to
+// switch between) unless the grid has more CTAs than fit the GPU at two per SM: then 4 warps and four CTAs per SM, so
+// that large batches still run as one wave.
 constexpr int DT_BLOCK = 16;   // cached tokens per warp iteration
-constexpr int DT_DEPTH = 3;    // blocks in flight per warp (two CTAs and their rings fit one SM)
 constexpr int DT_STAGE_BYTES = 3072;   // per warp and block: 2 KB of codes + 1 KB of parameter pairs (tokens repeat across lanes)
-constexpr int DT_RING_BYTES = DT_WARPS * DT_DEPTH * DT_STAGE_BYTES;
-#ifndef DT_MIN_CTAS
-#define DT_MIN_CTAS 2
-#endif
+__host__ __device__ constexpr int dt_depth(int) { return 3; }   // blocks in flight per warp: two 8-warp or four 4-warp CTAs and their rings fit one SM
+__host__ __device__ constexpr int dt_ring_bytes(int warps) { return warps * dt_depth(warps) * DT_STAGE_BYTES; }
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {
@@ -54,13 +53,14 @@ __device__ __forceinline__ int k_dim(int ks, int qd, int reg, int h) {
     return 32 * qd + 8 * w + i + 4 * h;
 }
 
-template <int G>
-__global__ void __launch_bounds__(DT_WARPS * 32, DT_MIN_CTAS)
+template <int G, int DT_WARPS>
+__global__ void __launch_bounds__(DT_WARPS * 32, DT_WARPS == 8 ? 2 : 4)
 decode_tc_kernel(const __half *__restrict__ q, PagedKV kv, __half *__restrict__ o, float *__restrict__ tmp,
                  uint32_t num_chunks, int had_q, float had_scale, int32_t *__restrict__ counters, int cluster_merge,
                  RopeIn rope) {
     pdl_trigger();   // the next kernel of the stream may be scheduled early; this one is launched without the attribute
     pdl_wait();
+    constexpr int DT_DEPTH = dt_depth(DT_WARPS);
     const uint32_t b = blockIdx.x, hk = blockIdx.y, chunk = blockIdx.z;
     const uint32_t hq_total = gridDim.y * G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -497,8 +497,11 @@ int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __hal
     bool cluster = counters == nullptr && (num_chunks == 2 || num_chunks == 4);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(DT_WARPS * 32);
-    cfg.dynamicSmemBytes = DT_RING_BYTES;
+    // 8 warps per CTA while the whole grid fits the GPU at two CTAs per SM, 4 warps (four CTAs per SM) beyond that
+    // (measured, context 1024-2048: batch 128 50.3 against 56.0 us, batch 64 54.2 against 55.6 us)
+    const int warps = (size_t)grid.x * grid.y * grid.z > 2 * (size_t)current_sm_count() ? 4 : 8;
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = warps == 8 ? dt_ring_bytes(8) : dt_ring_bytes(4);
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -517,8 +520,8 @@ int launch_decode_tc(int G, dim3 grid, const __half *q, const PagedKV &kv, __hal
     cfg.numAttrs = na;
 #define SR_DT(GG)                                                                                              \
     do {                                                                                                       \
-        auto kfn = decode_tc_kernel<GG>;                                                                       \
-        if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_RING_BYTES) != cudaSuccess) \
+        auto kfn = warps == 8 ? decode_tc_kernel<GG, 8> : decode_tc_kernel<GG, 4>;                             \
+        if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes) != cudaSuccess) \
             return 0;                                                                                          \
         if (cudaLaunchKernelEx(&cfg, kfn, q, kv, o, tmp, num_chunks, had_q, had_scale, counters, cluster ? 1 : 0, rope) != cudaSuccess) { \
             if (!cluster) return 0;                                                                            \
