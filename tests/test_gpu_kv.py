@@ -227,6 +227,53 @@ def test_in_kernel_merge_equals_merge_pass(T, page, Hq, Hkv, chunks):
         assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("chunks", [1, 2, 4, 3])
+def test_large_batch_takes_the_four_warp_form(chunks):
+    """More CTAs than fit the GPU at two per SM (batch 40 x 8 KV heads x chunks): the kernel runs with four warps per
+    CTA.  Against fp32 attention over the dequantized cache, split against unsplit, cluster merge against the counter
+    merge, and the one-launch decode step against its two launches."""
+    B, L, Hq, Hkv, page, T = 40, 1, 32, 8, 64, 200
+    k, v, ref, pages = _fill(B, L, Hkv, page, T, T + 1)
+    ref.append(0, k, v)
+    caches = []
+    for fuse in (False, True):
+        c = kvc.MultiLayerPagedKVCache4Bit(B, page, T + 8, DEV, L, Hkv, 128, group_size=Hq // Hkv, decode_chunks=chunks)
+        c.fuse_decode = fuse
+        c.pages.zero_()
+        c.scales.zero_()
+        c.update(k.to(DEV), v.to(DEV), 0)
+        caches.append(c)
+    specs = caches[0].refresh_specs()
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn((B, Hq, 128), generator=g).half().to(DEV)
+    kf, vf = ref.dense(0)
+    want = oracle.decode_attention_ref(q.cpu(), kf, vf, hadamard_q=True)
+    one = torch.empty_like(q)
+    kvc.batch_decode_i4(one, q, **specs, layer_idx=0, hadamard_q=True)
+    assert (one.float().cpu() - want).abs().max().item() <= 3e-2
+    if chunks > 1:
+        tmp = torch.empty((B, Hq, chunks, 132), dtype=torch.float32, device=DEV)
+        counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+        a, b = torch.empty_like(q), torch.empty_like(q)
+        kvc.batch_decode_i4(a, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks, hadamard_q=True)
+        kvc.batch_decode_i4(b, q, **specs, layer_idx=0, tmp=tmp, num_chunks=chunks, hadamard_q=True, counters=counters)
+        assert torch.equal(a, b) and int(counters.abs().sum()) == 0
+        assert (a.float() - one.float()).abs().max().item() <= 2e-3
+    qkv = torch.randn((B, 1, (Hq + 2 * Hkv) * 128), generator=g).half().to(DEV)
+    q1 = qkv[..., :Hq * 128].unflatten(-1, (Hq, 128))
+    k1 = qkv[..., Hq * 128:(Hq + Hkv) * 128].unflatten(-1, (Hkv, 128))
+    v1 = qkv[..., (Hq + Hkv) * 128:].unflatten(-1, (Hkv, 128))
+    ang = torch.rand((1, 1, 128), generator=g) * 6.28
+    cos, sin = ang.cos().half().to(DEV), ang.sin().half().to(DEV)
+    outs = []
+    for c in caches:
+        q_in, attend = c.update_with_rope(q1, k1, v1, cos, sin, 0, defer_append=True)
+        outs.append(attend(q_in))
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(caches[0].pages, caches[1].pages) and torch.equal(caches[0].scales, caches[1].scales)
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize("T,page,Hq,Hkv,chunks,per_request_cos", [(2100, 256, 32, 8, None, False), (513, 128, 32, 8, 3, True),
                                                                   (1000, 16, 8, 2, 12, False), (300, 32, 4, 4, 1, True),
                                                                   (255, 256, 16, 2, None, False), (256, 256, 8, 8, 2, True),
