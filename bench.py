@@ -624,11 +624,13 @@ def run_kernel_case(name: str):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     M = M_TOKENS
-    if name in ("gemm", "gemm_small"):
-        k, n = 4096, 14336
-        m = M if name == "gemm" else 16
+    if name in ("gemm", "gemm_small", "gemm_mid"):
+        # gemm_mid: 256 rows against the (14336 -> 4096) projection: the CTA-pair kernel with K split four ways
+        k, n = (14336, 4096) if name == "gemm_mid" else (4096, 14336)
+        m = M if name == "gemm" else (256 if name == "gemm_mid" else 16)
         c = make_linear_case(m, k, n)
-        pk = kernel.rotate_quant(c["x"].to(dev), None, 1, sign=c["sign"].to(dev))
+        hadK, K = get_hadK(k)
+        pk = kernel.rotate_quant(c["x"].to(dev), hadK, K, sign=c["sign"].to(dev))
         w, ws = c["w_packed"].to(dev), c["w_scale"].to(dev)
         for _ in range(5):
             kernel.w4a4_linear(pk, w, ws)
@@ -953,7 +955,7 @@ def main():
     ap.add_argument("--sweep", action="store_true",
                     help="secondary measurements of the other configurations (JSON lines)")
     ap.add_argument("--kernel-case", default=None,
-                    help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | rotate4096 | decode_layer | "
+                    help="run a few launches of one kernel and exit (for ncu): gemm | gemm_small | gemm_mid | rotate4096 | decode_layer | "
                          "rotate14336 | decode")
     args = ap.parse_args()
     if args.kernel_case == "decode_model_small":
