@@ -7,9 +7,11 @@
 
 namespace sr {
 
-// Kernel choice by shape.  The weight-streaming kernel's mma.sync rate bounds it at about 32 rows; wide outputs go to
-// the tensor-core kernel earlier.
-static bool decode_regime(int64_t M, int64_t N) { return M <= 32 || (M <= 64 && N <= 8192); }
+// Kernel choice by shape.  The weight-streaming kernel's mma.sync rate bounds it at about 32 rows.  With 33 .. 64 rows
+// it runs two CTAs per SM, one block of 16 weight rows each, and still wins while all blocks are one round of the grid
+// (measured at 64 rows, K = 4096: N = 4096 11.6 us against 15.0 us on the tensor-core kernel; N = 5120, two rounds,
+// 20.3 against 15.6 us).
+static bool decode_regime(int64_t M, int64_t N) { return M <= 32 || (M <= 64 && N <= 32ll * current_sm_count()); }
 
 // |a * b| <= 64 for signed codes and <= 120 for unsigned activation codes; the tensor-core kernel carries every product
 // times 256 in its int32 accumulator, so K is bounded by 2^31 / (256 * 64) resp. 2^31 / (256 * 120).

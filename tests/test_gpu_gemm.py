@@ -1,4 +1,4 @@
-"""int4 GEMM kernels (weight-streaming mma.sync kernel of the decode regime: M <= 32, or M <= 64 with N <= 8192;
+"""int4 GEMM kernels (weight-streaming mma.sync kernel of the decode regime: M <= 32, or M <= 64 with N <= 32 x the SM count;
 CTA-pair tcgen05 kernel above it) against the integer oracle: int32 accumulators bit-exact, fused dequant
 epilogue bit-exact.  The shapes below reach both kernels."""
 import pytest
